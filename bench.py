@@ -1,0 +1,348 @@
+"""Benchmark of the W4A4 fused-linear hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload decode|prefill]
+
+One step = one pass of the hot path over the workload's linears (activation
+quantisation + fused dense/residual GEMM each).  The default workload is the
+decode sweep: the four Llama-3-8B linear shapes (qkv 4096->6144, o 4096->4096,
+gate_up 4096->28672, down 14336->4096) at M = 1, 4 and 16 tokens with a 5 %
+block-sparse residual - twelve linears per step.  Inputs are seeded synthetic
+tensors; weights rotate through several distinct copies so that a step never
+finds its weights in L2.
+
+Printed JSON (one line, rank 0): `value` = effective TOPS (2*M*K*N per linear,
+dense ops only) with inputs resident in HBM and the step replayed as a CUDA
+graph; `e2e` = the same metric through the public module call with pinned host
+activations copied in and results copied out every step; `roofline` = HBM
+bytes/s of the GEMM kernel launches alone; `cpu_baseline` = the CPU oracle's
+dequantise->matmul route on the host cores.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LLAMA3_8B = [("qkv", 4096, 6144), ("o", 4096, 4096), ("gate_up", 4096, 28672), ("down", 14336, 4096)]
+DENSITY = 0.05
+L2_BYTES = 126 * 1024 * 1024
+
+
+def workload_items(name):
+    if name == "decode":
+        return [(f"{n}_M{m}", m, k, o) for m in (1, 4, 16) for (n, k, o) in LLAMA3_8B]
+    if name == "prefill":
+        return [(f"{n}_M{m}", m, k, o) for m in (2048,) for (n, k, o) in LLAMA3_8B]
+    if name == "cfg0":
+        return [("o_M16", 16, 4096, 4096)]
+    raise SystemExit(f"unknown workload {name}")
+
+
+# ----------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thr = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                try:
+                    mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                except Exception:
+                    mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                for bit, nm in names.items():
+                    if mask & bit:
+                        self.reasons.add(nm)
+            except Exception:
+                pass
+            time.sleep(0.02)
+
+    def __enter__(self):
+        if self.nv:
+            self._thr = threading.Thread(target=self._run, daemon=True)
+            self._thr.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thr:
+            self._thr.join()
+
+    def summary(self):
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons)}
+
+
+# ----------------------------------------------------------------------------- helpers
+def measured_hbm_peak():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+def build_inputs(items, device, n_sets):
+    """Per item: host activations (pinned), and n_sets distinct device copies of the weights."""
+    from zip_kernel_b200 import synth
+    cache, out = {}, []
+    for name, M, K, N in items:
+        if (K, N) not in cache:
+            W = synth.make_container(N, K, DENSITY, seed=synth.shape_seed(0, K, N))
+            cache[(K, N)] = [W.to(device)] + [None] * (n_sets - 1)
+            for r in range(1, n_sets):
+                cache[(K, N)][r] = W.to(device)      # a distinct allocation per set
+        X = synth.make_activations(M, K, seed=synth.shape_seed(M, K, N) + 1).pin_memory()
+        out.append(dict(name=name, M=M, K=K, N=N, X_host=X, W=cache[(K, N)]))
+    return out
+
+
+def alg_bytes_gemm(it):
+    """Bytes one GEMM launch must move: weights, scales/zeros, residual blocks and
+    index, quantised activations with their scales and group sums, output."""
+    M, K, N = it["M"], it["K"], it["N"]
+    nnz = it["W"][0].n_hp_blocks
+    ng, nbr = K // 128, (N + 127) // 128
+    b_w = K * N // 2 + 4 * N * ng + 8192 * nnz + 4 * (nbr + 1) + 4 * nnz
+    return b_w + (M * K // 2 + 2 * M + 4 * M * ng) + 2 * M * N
+
+
+# ----------------------------------------------------------------------------- reference arm
+def run_reference(args, items):
+    """CPU arm: the oracle's restatement of the reference's dequantise -> fp32
+    matmul route, all host threads, on a bounded sample of the workload."""
+    from oracle import w4a4_oracle as O
+    from zip_kernel_b200 import synth
+    torch.set_num_threads(os.cpu_count() or 1)
+    # bounded sample: the M=16 linears of the two smaller shapes
+    sample = [it for it in items if it[1] == max(i[1] for i in items)][:2]
+    data = []
+    for name, M, K, N in sample:
+        W = synth.make_container(N, K, DENSITY, seed=synth.shape_seed(0, K, N))
+        X = synth.make_activations(M, K, seed=synth.shape_seed(M, K, N) + 1)
+        Wt = dict(W_low_packed=W.W_low_packed, W_high_blocks_packed=W.W_high_blocks_packed,
+                  scale_u4=W.scale_u4, zero_u4=W.zero_u4, hp_row_offsets=W.hp_row_offsets,
+                  hp_col_indices=W.hp_col_indices, d_out=N, d_in=K)
+        data.append((X, W.perm, Wt, 2 * M * K * N))
+    def step():
+        for X, perm, Wt, _ in data:
+            O.cpu_reference_path(X, perm, Wt)
+    for _ in range(max(1, min(args.warmup, 2))):
+        step()
+    steps = max(1, min(args.steps, 5))
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    ops = sum(d[3] for d in data)
+    val = ops / dt / 1e12
+    desc = "+".join(n for n, *_ in sample)
+    return {
+        "impl": "reference", "metric": "w4a4_fused_linear_effective_tops", "value": val, "unit": "TOPS",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s4xs4->s32",
+        "data": "synthetic", "config": {"workload": args.workload_desc, "sample": desc},
+        "cpu_baseline": {"value": val, "unit": "TOPS", "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": f"{desc}: quantise + dequantise->fp32 matmul, {steps} passes"},
+        "e2e": {"value": val, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+
+
+# ----------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="decode")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    items = workload_items(args.workload)
+    args.workload_desc = {
+        "decode": "Llama-3-8B linears (qkv,o,gate_up,down) x M in {1,4,16}, 5% residual blocks",
+        "prefill": "Llama-3-8B linears (qkv,o,gate_up,down) x M=2048, 5% residual blocks",
+        "cfg0": "single linear 4096->4096, M=16, 5% residual blocks",
+    }[args.workload]
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args, items)), flush=True)
+        return
+
+    import torch.distributed as dist
+    from zip_kernel_b200 import ops, v9_linear
+
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    w_bytes = sum(k * n // 2 for _, k, n in {(i[2], i[3]): (0, i[2], i[3]) for i in items}.values())
+    n_sets = max(2, -(-2 * L2_BYTES // max(w_bytes, 1)) + 1)
+    data = build_inputs(items, device, n_sets)
+    for it in data:
+        it["X_dev"] = it["X_host"].to(device)
+        it["Y_host"] = torch.empty((it["M"], it["N"]), dtype=torch.float16).pin_memory()
+        ops.reserve_workspace(device, it["M"], it["K"], it["N"], it["W"][0].n_hp_blocks)
+
+    def device_step(r):
+        for it in data:
+            W = it["W"][r]
+            it["Y"] = ops.fused_dense_sparse_e2e_cuda(
+                it["X_dev"], W.perm, W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
+                W.hp_col_indices, W.scale_u4, W.zero_u4, W.d_out, W.d_in, token_major=True)
+
+    def gemm_only_step(r):
+        for it in data:
+            W = it["W"][r]
+            q = it["q"]
+            ops.fused_dense_sparse_cuda(W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
+                                        W.hp_col_indices, q[0], W.scale_u4, W.zero_u4, q[2], q[1],
+                                        W.d_out, W.d_in, token_major=True)
+
+    def e2e_step(r):
+        ys = []
+        for it in data:
+            x = it["X_host"].to(device, non_blocking=True)
+            y = v9_linear.v9_linear_forward(x, it["W"][r])
+            it["Y_host"].copy_(y, non_blocking=True)
+            ys.append(y)
+        torch.cuda.current_stream().synchronize()
+
+    # eager warm-up (also sizes every workspace before capture)
+    for it in data:
+        it["q"] = ops.activation_quant_cuda(it["X_dev"], it["W"][0].perm)
+    for r in range(n_sets):
+        device_step(r)
+        gemm_only_step(r)
+    torch.cuda.synchronize()
+
+    def capture(fn):
+        graphs = []
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for r in range(n_sets):
+                from zip_kernel_b200 import _lib
+                for it in data:   # the workspace is keyed by stream: allocate on the capture stream
+                    ops.reserve_workspace(device, it["M"], it["K"], it["N"], it["W"][0].n_hp_blocks)
+                fn(r)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    fn(r)
+                graphs.append(g)
+        torch.cuda.synchronize()
+        return graphs
+
+    step_graphs = capture(device_step)
+    gemm_graphs = capture(gemm_only_step)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(run, steps, warmup):
+        for i in range(warmup):
+            run(i % n_sets)
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(steps):
+            run((warmup + i) % n_sets)
+        e1.record()
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    warmup = max(3, args.warmup)
+    with ClockSampler(local_rank) as clk:
+        ms_dev = timed(lambda r: step_graphs[r].replay(), args.steps, warmup)
+        ms_gemm = timed(lambda r: gemm_graphs[r].replay(), args.steps, warmup)
+    ms_e2e = timed(e2e_step, max(10, args.steps // 5), 3)
+    e2e_steps = max(10, args.steps // 5)
+
+    from zip_kernel_b200 import _lib
+    dev_err = _lib.device_error(device)
+
+    ops_step = sum(2 * it["M"] * it["K"] * it["N"] for it in data)
+    bytes_gemm = sum(alg_bytes_gemm(it) for it in data)
+    peak, peak_kind = measured_hbm_peak()
+    gemm_s = ms_gemm / 1e3 / args.steps
+    achieved = bytes_gemm / gemm_s / 1e9
+    value = world * ops_step / (ms_dev / 1e3 / args.steps) / 1e12
+    e2e_val = world * ops_step / (ms_e2e / 1e3 / e2e_steps) / 1e12
+
+    out = {
+        "metric": "w4a4_fused_linear_effective_tops", "value": value, "unit": "TOPS",
+        "n_gpus": world, "steps": args.steps, "warmup": warmup, "ms_per_step": ms_dev / args.steps,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "s4xs4->s32",
+        "data": "synthetic",
+        "config": {"workload": args.workload_desc, "linears_per_step": len(data),
+                   "l2": f"weights rotate through {n_sets} distinct copies (> 2x L2)",
+                   "step": "CUDA-graph replay of quant+GEMM per linear", "parallelism": f"replicated x{world}"},
+        "us_per_linear": ms_dev / args.steps / len(data) * 1e3,
+        "e2e": {"value": e2e_val, "unit": "TOPS",
+                "h2d_bytes_per_step": sum(it["X_host"].numel() * 2 for it in data),
+                "d2h_bytes_per_step": sum(it["Y_host"].numel() * 2 for it in data),
+                "ms_per_step": ms_e2e / e2e_steps},
+        "gpu_launches": args.steps * len(data) * 2,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                     "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                     "kernel": "decode_gemm_kernel", "us_per_launch": gemm_s / len(data) * 1e6,
+                     "bytes_per_launch": bytes_gemm / len(data)},
+        "clocks": clk.summary(),
+        "device_error_word": dev_err,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        ref = run_reference(argparse.Namespace(**{**vars(args), "steps": 3, "warmup": 1}), items)
+        out["cpu_baseline"] = ref["cpu_baseline"]
+    if rank == 0:
+        print(json.dumps(out), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

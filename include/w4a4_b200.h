@@ -1,0 +1,127 @@
+/*
+ * C ABI of the B200 (sm_100a) W4A4 fused-linear library  (libw4a4_b200.so).
+ *
+ * These entry points are what the reference project's operator layer would bind
+ * in place of its pybind11 module `hkust_v9_cuda`
+ * (cuda_kernel/csrc/bindings.cc:110-252, called from cuda_kernel/ops.py).
+ * Plain pointers and sizes only; all pointers are DEVICE pointers unless a
+ * comment says host.  Every call is stream-ordered on `stream` (a cudaStream_t
+ * passed as void*), never synchronises, and never allocates: scratch memory is
+ * passed in by the caller (query its size with w4a4_workspace_bytes).  Inputs
+ * are borrowed until the stream work completes.
+ *
+ * Shapes: T tokens, K = d_in (multiple of 128), N = d_out (any), ng = K/128,
+ * nnz residual blocks.  Tensors are dense row-major:
+ *   X        (T, K)  fp16, row stride ldx elements
+ *   perm     (K)     int32 or NULL for identity
+ *   X_s4     (T, K/2) int8   two codes per byte, even element in the low nibble
+ *   scale_x  (T)     fp16
+ *   sum_X    (T, ng) int32
+ *   W_low    (N, K/2) int8   nibbles = u4 - 8
+ *   W_high   (nnz, 128, 64) int8
+ *   scale_u4, zero_u4 (N, ng) fp16   (zero already shifted by -8)
+ *   hp_row_offsets (ceil(N/128)+1) int32, hp_col_indices (nnz) int32
+ *   Y        (N, T) fp16, or (T, N) with W4A4_FLAG_OUT_TOKEN_MAJOR
+ *
+ * Return value: 0 on success, otherwise one of the W4A4_ERR_* codes;
+ * w4a4_last_error() gives a host-side message for the calling thread.
+ */
+#ifndef W4A4_B200_H_
+#define W4A4_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define W4A4_ABI_VERSION 1
+
+enum {
+  W4A4_OK = 0,
+  W4A4_ERR_BAD_ARG = 1,      /* null pointer, bad size, K % 128 != 0 ...           */
+  W4A4_ERR_ALIGNMENT = 2,    /* a pointer or stride misses the alignment it needs  */
+  W4A4_ERR_WORKSPACE = 3,    /* workspace NULL or smaller than w4a4_workspace_bytes */
+  W4A4_ERR_LAUNCH = 4,       /* CUDA reported an error at launch                   */
+  W4A4_ERR_DEVICE = 5,       /* a bounded device-side wait gave up (see w4a4_device_error) */
+  W4A4_ERR_UNSUPPORTED = 6   /* shape outside what the selected kernel supports    */
+};
+
+/* flags for the GEMM entry points */
+#define W4A4_FLAG_OUT_TOKEN_MAJOR 0x1  /* write Y as (T, N) instead of (N, T)          */
+#define W4A4_FLAG_FORCE_STREAM    0x2  /* force the weight-streaming split-K kernel     */
+#define W4A4_FLAG_FORCE_TENSOR    0x4  /* force the tcgen05 tensor-core kernel          */
+
+int w4a4_abi_version(void);
+const char* w4a4_status_string(int status);
+const char* w4a4_last_error(void);
+
+/* Reads and clears the device error word of the current device (synchronises
+ * `stream`).  *word == 0 means no bounded wait has given up since the last call. */
+int w4a4_device_error(int* word /* host */, void* stream);
+
+/* Replaces activation_quant_launch (bindings.cc:113-122; kernel
+ * cuda_kernel/csrc/activation_quant/activation_quant.cu:699-865).
+ * No workspace. */
+int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4,
+                          void* scale_x, int32_t* sum_X, int T, int K, void* stream);
+
+/* Scratch bytes the GEMM entry points below need for (T, K, N, nnz); the same
+ * size serves all of them.  The first W4A4_WORKSPACE_COUNTER_BYTES bytes hold
+ * arrival counters that must be zero before the first use (w4a4_workspace_init
+ * or a memset); the kernels leave them zero again. */
+#define W4A4_WORKSPACE_COUNTER_BYTES 65536
+size_t w4a4_workspace_bytes(int T, int K, int N, int nnz);
+int w4a4_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces fused_dense_sparse_mma_int4_launch, fused_gemv_decode_launch and
+ * fused_gemv_smallT_launch (bindings.cc:187-235; kernels
+ * fused_dense_sparse_mma_int4.cu:184-1190, fused_gemv_decode.cu:54-191,
+ * fused_gemv_smallT.cu:47-221).  nnz may be 0 (W_high/hp_col_indices then unused). */
+int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                            const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
+                            const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y,
+                            int T, int K, int N, int nnz, int flags, void* workspace,
+                            size_t workspace_bytes, void* stream);
+
+/* Replaces dense_gemm_mma_int4_launch and dense_gemv_decode_launch
+ * (bindings.cc:124-148; dense_gemm_mma_int4.cu:39-431, dense_gemv_decode.cu:86-182). */
+int w4a4_dense_gemm(const void* W_low, const void* X_s4, const void* scale_u4, const void* zero_u4,
+                    const int32_t* sum_X, const void* scale_x, void* Y_low, int T, int K, int N,
+                    int flags, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Replaces sparse_gemm_mma_int4_launch (bindings.cc:150-161;
+ * sparse_gemm_mma_int4.cu:25-253): Y_high = sx * sum_blk s[n,bc] * acc_hi, WITHOUT the
+ * factor 16 (the caller applies it, triton_kernel/v9_linear.py:148).  Rows of
+ * block-rows without blocks are written as zero. */
+int w4a4_sparse_gemm(const void* W_high, const int32_t* hp_row_offsets, const int32_t* hp_col_indices,
+                     const void* X_s4, const void* scale_u4, const void* scale_x, void* Y_high, int T,
+                     int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes,
+                     void* stream);
+
+/* Replaces fused_quant_gemv_launch and fused_quant_dense_sparse_mma_int4_launch
+ * (bindings.cc:204-251; fused_quant_gemv.cu:64-266,
+ * fused_quant_dense_sparse_mma_int4.cu:179-483): fp16 activations in, fp16 out.
+ * Quantisation and GEMM are two launches chained with programmatic dependent
+ * launch so the weight prefetch overlaps the quantisation. */
+int w4a4_fused_quant_dense_sparse(const void* X, long long ldx, const int32_t* perm, const void* W_low,
+                                  const void* W_high, const int32_t* hp_row_offsets,
+                                  const int32_t* hp_col_indices, const void* scale_u4,
+                                  const void* zero_u4, void* Y, int T, int K, int N, int nnz,
+                                  int flags, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Parity aid with no counterpart in the reference's bindings: runs the same
+ * MMA path as w4a4_fused_dense_sparse and stores the exact int32 accumulators,
+ * acc (ng, N, T) per group (the workspace the reference defines in
+ * fused_dense_sparse/cutlass_dequant.cu:7-16) and acc_hi (nnz, 128, T) per residual
+ * block.  Either output may be NULL. */
+int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                           const int32_t* hp_col_indices, const void* X_s4, int32_t* acc,
+                           int32_t* acc_hi, int T, int K, int N, int nnz, int flags, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W4A4_B200_H_ */

@@ -1,0 +1,127 @@
+"""ctypes binding of libw4a4_b200.so (the C ABI declared in include/w4a4_b200.h).
+
+There is no fallback: if the library has not been built, importing the operator
+layer raises.  ``python -m zip_kernel_b200.build`` (or ``__graft_entry__.build``)
+produces it.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from typing import Dict, Tuple
+
+import torch
+
+from .build import LIB_PATH
+
+_c = ctypes
+_PTR = _c.c_void_p
+_INT = _c.c_int
+_LL = _c.c_longlong
+_SZ = _c.c_size_t
+
+# name -> (restype, argtypes); must list every symbol of include/w4a4_b200.h
+SIGNATURES = {
+    "w4a4_abi_version": (_INT, []),
+    "w4a4_status_string": (_c.c_char_p, [_INT]),
+    "w4a4_last_error": (_c.c_char_p, []),
+    "w4a4_device_error": (_INT, [_c.POINTER(_INT), _PTR]),
+    "w4a4_activation_quant": (_INT, [_PTR, _LL, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _PTR]),
+    "w4a4_workspace_bytes": (_SZ, [_INT, _INT, _INT, _INT]),
+    "w4a4_workspace_init": (_INT, [_PTR, _SZ, _PTR]),
+    "w4a4_fused_dense_sparse": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_dense_gemm": (_INT, [_PTR] * 7 + [_INT] * 4 + [_PTR, _SZ, _PTR]),
+    "w4a4_sparse_gemm": (_INT, [_PTR] * 7 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_fused_quant_dense_sparse": (_INT, [_PTR, _LL] + [_PTR] * 8 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_dump_accumulators": (_INT, [_PTR] * 7 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+}
+
+FLAG_OUT_TOKEN_MAJOR = 0x1
+FLAG_FORCE_STREAM = 0x2
+FLAG_FORCE_TENSOR = 0x4
+
+_lib = None
+
+
+class W4A4Error(RuntimeError):
+    """A C-ABI call returned a non-zero status."""
+
+    def __init__(self, status: int, where: str, detail: str):
+        self.status = status
+        super().__init__(f"{where} failed with status {status}: {detail}")
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once and attach the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python -m zip_kernel_b200.build` "
+            "(needs nvcc; there is no CPU fallback)"
+        )
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)
+        fn.restype = res
+        fn.argtypes = args
+    if lib.w4a4_abi_version() != 1:
+        raise RuntimeError("libw4a4_b200.so ABI version mismatch")
+    _lib = lib
+    return lib
+
+
+def check(status: int, where: str) -> None:
+    """Translate a status code into the exception class the reference raises:
+    argument problems become ValueError, everything else RuntimeError."""
+    if status == 0:
+        return
+    lib = load()
+    detail = (lib.w4a4_last_error() or b"").decode() or lib.w4a4_status_string(status).decode()
+    if status == 1:
+        raise ValueError(f"{where}: {detail}")
+    raise W4A4Error(status, where, detail)
+
+
+def ptr(t) -> int:
+    """Device pointer of a tensor (None -> NULL)."""
+    return None if t is None else t.data_ptr()
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+# ---------------------------------------------------------------------------
+# workspace cache: one zero-initialised buffer per (device, stream), grown on
+# demand.  Calls issued on one stream are ordered, so they can share scratch.
+# ---------------------------------------------------------------------------
+_workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+
+
+def workspace(device: torch.device, T: int, K: int, N: int, nnz: int) -> torch.Tensor:
+    lib = load()
+    need = int(lib.w4a4_workspace_bytes(T, K, N, nnz))
+    key = (device.index if device.index is not None else torch.cuda.current_device(),
+           stream_ptr(device))
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < need:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                "the W4A4 workspace must be allocated before CUDA-graph capture: "
+                "run the shape once eagerly (or call zip_kernel_b200.ops.reserve_workspace)"
+            )
+        grow = max(need, int(buf.numel() * 1.5) if buf is not None else 0)
+        buf = torch.zeros(grow, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def device_error(device) -> int:
+    """Read and clear the device error word (synchronises the current stream)."""
+    lib = load()
+    word = _INT(0)
+    lib.w4a4_device_error(ctypes.byref(word), stream_ptr(device))
+    return int(word.value)

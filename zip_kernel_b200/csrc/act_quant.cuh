@@ -1,0 +1,138 @@
+// Kernel 1: per-token symmetric s4 activation quantisation.
+//
+// Contract (reference: cuda_kernel/csrc/activation_quant/activation_quant.cu:6-12,
+// oracle tools/parity/quant_reference.py:82-112):
+//   Xp = X[t, perm[:]];  scale_x[t] = fp16(max|Xp| / 7);  s = fp32(scale_x[t])
+//   q  = clamp(rint(Xp / s), -8, 7)  (all zero when s == 0)
+//   X_s4 packs two codes per byte (even element in the low nibble)
+//   sum_X[t, g] = sum of the 128 codes of group g
+// The division is the IEEE one (div.rn) and rint is round-half-even: codes are
+// bit-identical to the oracle.  The reference's optimised kernel deviates here
+// with an approximate division (activation_quant.cu:76-92); its naive kernel and
+// its oracle do not (csrc_naive/activation_quant_naive.cu:132-133).
+//
+// One CTA per token.  The row is read from HBM exactly once with 128-bit loads
+// (or gathered through perm), parked in shared memory as fp16 while the CTA
+// reduces max|x| with warp shuffles, then quantised from shared memory; a thread
+// owns 8 consecutive codes = one 32-bit packed word, and 16 neighbouring lanes
+// own one group, so sum_X is a 4-step shuffle reduction.
+#pragma once
+
+#include "common.cuh"
+
+namespace w4a4 {
+
+constexpr int QUANT_THREADS = 256;
+
+struct QuantParams {
+  const __half* X;        // (T, K) fp16, row stride ldx elements
+  long long ldx;
+  const int* perm;        // (K) or nullptr for identity
+  int8_t* X_s4;           // (T, K/2)
+  __half* scale_x;        // (T)
+  int* sum_X;             // (T, K/128)
+  int8_t* X_s8;           // optional (T, K) expanded codes for the tensor-core path, or nullptr
+  int T, K;
+  int vec_ok;             // 1 when every row start is 16-byte aligned
+};
+
+__device__ __forceinline__ float half_abs_max8(const uint4& v, float m) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 f = __half22float2(__habs2(h[i]));
+    m = fmaxf(m, fmaxf(f.x, f.y));
+  }
+  return m;
+}
+
+__global__ void __launch_bounds__(QUANT_THREADS)
+act_quant_kernel(const QuantParams p) {
+  extern __shared__ __align__(16) unsigned char quant_smem[];
+  uint4* row = reinterpret_cast<uint4*>(quant_smem);          // K/8 chunks of 8 halfs
+  __shared__ float warp_max[QUANT_THREADS / 32];
+
+  // Let a dependent GEMM kernel start its weight prefetch while this one runs.
+  grid_launch_dependents();
+
+  const int t = blockIdx.x;
+  const int tid = threadIdx.x;
+  const int nchunk = p.K >> 3;
+  const __half* xrow = p.X + (long long)t * p.ldx;
+
+  float m = 0.f;
+  if (p.perm == nullptr && p.vec_ok) {
+    const uint4* src = reinterpret_cast<const uint4*>(xrow);
+    for (int c = tid; c < nchunk; c += QUANT_THREADS) {
+      uint4 v = __ldg(src + c);
+      row[c] = v;
+      m = half_abs_max8(v, m);
+    }
+  } else {
+    for (int c = tid; c < nchunk; c += QUANT_THREADS) {
+      __align__(16) __half h[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        int k = c * 8 + j;
+        int src = p.perm ? __ldg(p.perm + k) : k;
+        h[j] = xrow[src];
+      }
+      uint4 v = *reinterpret_cast<uint4*>(h);
+      row[c] = v;
+      m = half_abs_max8(v, m);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((tid & 31) == 0) warp_max[tid >> 5] = m;
+  __syncthreads();
+  m = warp_max[0];
+#pragma unroll
+  for (int w = 1; w < QUANT_THREADS / 32; ++w) m = fmaxf(m, warp_max[w]);
+
+  const __half scale16 = __float2half_rn(__fdiv_rn(m, 7.0f));
+  const float s = __half2float(scale16);
+  const bool zero_row = !(s > 0.f);
+  const float s_safe = zero_row ? 1.0f : s;
+  if (tid == 0) p.scale_x[t] = scale16;
+
+  uint32_t* out = reinterpret_cast<uint32_t*>(p.X_s4 + (long long)t * (p.K >> 1));
+  int* sums = p.sum_X + (long long)t * (p.K >> 7);
+  // All lanes of a warp run the same number of iterations (nchunk is a multiple
+  // of 16 and lanes are consecutive), so the shuffles below are convergent for
+  // every 16-lane half that holds a live group.
+  for (int c0 = 0; c0 < nchunk; c0 += QUANT_THREADS) {
+    const int c = c0 + tid;
+    const bool live = c < nchunk;
+    uint32_t word = 0;
+    int sum = 0;
+    if (live) {
+      uint4 v = row[c];
+      const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float2 f = __half22float2(h[i]);
+        float q0 = fminf(fmaxf(rintf(__fdiv_rn(f.x, s_safe)), -8.f), 7.f);
+        float q1 = fminf(fmaxf(rintf(__fdiv_rn(f.y, s_safe)), -8.f), 7.f);
+        int i0 = zero_row ? 0 : (int)q0;
+        int i1 = zero_row ? 0 : (int)q1;
+        sum += i0 + i1;
+        word |= (uint32_t)(i0 & 0xF) << (8 * i);
+        word |= (uint32_t)(i1 & 0xF) << (8 * i + 4);
+      }
+      out[c] = word;
+      if (p.X_s8) {
+        // expanded copy, one byte per code: every 32 codes (16 packed bytes)
+        // become 16 bytes of even-indexed codes followed by 16 bytes of odd ones
+        uint32_t* e = reinterpret_cast<uint32_t*>(p.X_s8 + (long long)t * p.K) + (c >> 2) * 8 + (c & 3);
+        e[0] = nib_lo_s8(word);
+        e[4] = nib_hi_s8(word);
+      }
+    }
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (live && (tid & 15) == 0) sums[c >> 4] = sum;
+  }
+}
+
+}  // namespace w4a4

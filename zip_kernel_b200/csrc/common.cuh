@@ -1,0 +1,118 @@
+// Shared device helpers for the sm_100a W4A4 kernels: mbarrier / TMA / tcgen05
+// PTX wrappers, bounded waits, nibble unpacking and the device error word.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace w4a4 {
+
+constexpr int BROW = 128;   // residual block rows  (reference: csrc/common/arch.cuh:30)
+constexpr int BCOL = 128;   // quantisation group / residual block columns (arch.cuh:31)
+constexpr int GROUP_BYTES = BCOL / 2;   // packed bytes of one group of one row
+
+// Every device-side wait polls at most this many times, then records an error
+// and gives up, so a logic error can never leave the GPU spinning.
+constexpr uint32_t WAIT_POLL_LIMIT = 1u << 22;
+
+// Device error word: 0 = ok.  Non-zero = (site id << 8) | detail of the first
+// wait that gave up.  Read and cleared by w4a4_device_error().
+__device__ int g_error_word = 0;
+
+__device__ __forceinline__ void record_error(int site, int detail) {
+  atomicCAS(&g_error_word, 0, (site << 8) | (detail & 0xff) | 0x40000000);
+}
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---------------------------------------------------------------- mbarrier
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false (after recording the site) when the phase never
+// completed; callers then stop using the pipeline and fall through to the exit.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int site) {
+  for (uint32_t i = 0; i < WAIT_POLL_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 1024) __nanosleep(64);
+  }
+  record_error(site, parity);
+  return false;
+}
+
+// ---------------------------------------------------------------- proxies / PDL
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+// Programmatic dependent launch: wait until the preceding kernel in the stream
+// has completed and its writes are visible (no-op without the launch attribute).
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+// ---------------------------------------------------------------- TMA (no multicast anywhere)
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, int c0, int c1,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1),
+        "r"(smem_u32(bar))
+      : "memory");
+}
+
+// ---------------------------------------------------------------- nibble helpers
+// A packed word holds 8 signed nibbles: byte b = elements 2b (low) and 2b+1 (high).
+// Even elements scaled by 16 as four s8 lanes.
+__device__ __forceinline__ uint32_t nib_lo_x16(uint32_t w) { return (w << 4) & 0xF0F0F0F0u; }
+// Odd elements scaled by 16 as four s8 lanes.
+__device__ __forceinline__ uint32_t nib_hi_x16(uint32_t w) { return w & 0xF0F0F0F0u; }
+// Sign-extend four 4-bit values sitting in the low nibble of each byte.
+__device__ __forceinline__ uint32_t sext4_bytes(uint32_t x) {
+  return x | ((x & 0x08080808u) * 0x1Eu);
+}
+__device__ __forceinline__ uint32_t nib_lo_s8(uint32_t w) { return sext4_bytes(w & 0x0F0F0F0Fu); }
+__device__ __forceinline__ uint32_t nib_hi_s8(uint32_t w) { return sext4_bytes((w >> 4) & 0x0F0F0F0Fu); }
+
+// ---------------------------------------------------------------- legacy int8 MMA (decode path)
+// D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
+__device__ __forceinline__ void mma_m16n8k32_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                                uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+}  // namespace w4a4

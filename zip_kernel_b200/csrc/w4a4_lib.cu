@@ -1,0 +1,444 @@
+// extern "C" entry points of libw4a4_b200.so: argument validation, tensor-map
+// construction, kernel selection and launch.  The contract of every function
+// is documented in include/w4a4_b200.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/w4a4_b200.h"
+#include "act_quant.cuh"
+#include "common.cuh"
+#include "decode_gemm.cuh"
+#include "prefill_gemm.cuh"
+
+namespace {
+
+thread_local std::string t_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  t_last_error = buf;
+  return code;
+}
+
+#define CHECK_ARG(cond, ...) \
+  do {                       \
+    if (!(cond)) return fail(W4A4_ERR_BAD_ARG, __VA_ARGS__); \
+  } while (0)
+
+inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
+inline size_t round_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// ------------------------------------------------------------------ device info
+struct DeviceInfo {
+  int sm_count = 0;
+  bool attrs_set = false;
+};
+std::mutex g_mutex;
+DeviceInfo g_dev[64];
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+
+int current_device(DeviceInfo** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(W4A4_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  DeviceInfo& d = g_dev[dev];
+  if (d.sm_count == 0) {
+    e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+  }
+  if (!g_encode) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+    if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn)
+      return fail(W4A4_ERR_LAUNCH, "cuTensorMapEncodeTiled entry point unavailable");
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  }
+  *out = &d;
+  return W4A4_OK;
+}
+
+// 2-D byte tensor map: `rows` rows of `row_bytes` bytes (pitch = row_bytes), box
+// box_bytes x box_rows.  Out-of-range rows read as zero.
+int make_map(CUtensorMap* m, const void* ptr, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes,
+             uint32_t box_rows, CUtensorMapSwizzle swz) {
+  cuuint64_t dims[2] = {row_bytes, rows ? rows : 1};
+  cuuint64_t strides[1] = {row_bytes};
+  cuuint32_t box[2] = {box_bytes, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(W4A4_ERR_LAUNCH, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  return W4A4_OK;
+}
+
+// ------------------------------------------------------------------ workspace layout
+constexpr size_t WS_PARTIAL_BYTES = 8u << 20;   // split-K partial sums (<= 1024 row-tile slices)
+struct WsLayout {
+  size_t counters, partial, x_s4, scale_x, sum_x, x_s8, total;
+};
+WsLayout ws_layout(int T, int K) {
+  WsLayout w;
+  size_t off = 0;
+  w.counters = off; off += W4A4_WORKSPACE_COUNTER_BYTES;
+  w.partial = off;  off += WS_PARTIAL_BYTES;
+  w.x_s4 = off;     off += round_up((size_t)T * (K / 2), 256);
+  w.scale_x = off;  off += round_up((size_t)T * 2, 256);
+  w.sum_x = off;    off += round_up((size_t)T * (K / 128) * 4, 256);
+  w.x_s8 = off;     off += round_up((size_t)T * K, 1024);
+  w.total = off;
+  return w;
+}
+
+// ------------------------------------------------------------------ plans
+struct DecodePlan {
+  int S, split_k, slices_per_cta, row_tiles, tok_tiles;
+};
+DecodePlan plan_decode(int T, int K, int N, int sm_count, bool allow_split) {
+  using namespace w4a4;
+  DecodePlan p;
+  const int ng = K / BCOL;
+  p.row_tiles = (N + dec::ROWS - 1) / dec::ROWS;
+  p.tok_tiles = (T + dec::TOK - 1) / dec::TOK;
+  const long long base = (long long)p.row_tiles * p.tok_tiles;
+  const long long target = 2LL * sm_count;
+  p.S = ng < dec::S_MAX ? ng : dec::S_MAX;
+  p.split_k = 1;
+  if (allow_split && base < target && ng > 1) {
+    int want = (int)((target + base - 1) / base);
+    int S = (ng + want - 1) / want;
+    if (S < 1) S = 1;
+    if (S > dec::S_MAX) S = dec::S_MAX;
+    int slices = (ng + S - 1) / S;
+    if (slices > 1 && base * slices <= 1024) {
+      p.S = S;
+      p.split_k = slices;
+    }
+  }
+  const int n_slices = (ng + p.S - 1) / p.S;
+  p.slices_per_cta = p.split_k > 1 ? 1 : n_slices;
+  return p;
+}
+
+struct GemmArgs {
+  const void* W_low;
+  const void* W_high;
+  const int32_t* hp_row_offsets;
+  const int32_t* hp_col_indices;
+  const void* X_s4;
+  const void* X_s8;        // expanded activations when already available, else NULL
+  const void* scale_u4;
+  const void* zero_u4;
+  const int32_t* sum_X;
+  const void* scale_x;
+  void* Y;
+  int32_t* acc_dump;
+  int32_t* acc_hi_dump;
+  int T, K, N, nnz, flags;
+  bool do_dense;
+  float sparse_weight;
+  bool pdl;                // launch as programmatic dependent of the preceding kernel
+  void* ws;
+  size_t ws_bytes;
+  cudaStream_t stream;
+};
+
+int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
+  using namespace w4a4;
+  const bool dump = a.acc_dump || a.acc_hi_dump;
+  DecodePlan plan = plan_decode(a.T, a.K, a.N, dev->sm_count, !dump);
+  const WsLayout wl = ws_layout(a.T, a.K);
+  if (plan.split_k > 1 && (a.ws == nullptr || a.ws_bytes < wl.x_s4))
+    return fail(W4A4_ERR_WORKSPACE, "split-K needs a workspace of at least %zu bytes", wl.x_s4);
+
+  CUtensorMap tm_low, tm_high;
+  const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
+  if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
+  // the operand that is switched off borrows the other one's map and is never read
+  int rc = make_map(&tm_low, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
+                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, dec::ROWS,
+                    CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  rc = make_map(&tm_high, has_sparse ? a.W_high : a.W_low, has_sparse ? 64 : (uint64_t)a.K / 2,
+                has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, dec::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+
+  dec::Params p;
+  p.hp_row_offsets = a.hp_row_offsets;
+  p.hp_col_indices = a.hp_col_indices;
+  p.X_s4 = static_cast<const int8_t*>(a.X_s4);
+  p.scale_u4 = static_cast<const __half*>(a.scale_u4);
+  p.zero_u4 = static_cast<const __half*>(a.zero_u4);
+  p.sum_X = a.sum_X;
+  p.scale_x = static_cast<const __half*>(a.scale_x);
+  p.Y = static_cast<__half*>(a.Y);
+  if (a.flags & W4A4_FLAG_OUT_TOKEN_MAJOR) {
+    p.y_stride_n = 1;
+    p.y_stride_t = a.N;
+  } else {
+    p.y_stride_n = a.T;
+    p.y_stride_t = 1;
+  }
+  p.partial = a.ws ? reinterpret_cast<float*>(static_cast<char*>(a.ws) + wl.partial) : nullptr;
+  p.counters = a.ws ? reinterpret_cast<int*>(static_cast<char*>(a.ws) + wl.counters) : nullptr;
+  p.acc_dump = a.acc_dump;
+  p.acc_hi_dump = a.acc_hi_dump;
+  p.T = a.T; p.K = a.K; p.N = a.N; p.ng = a.K / BCOL; p.nnz = has_sparse ? a.nnz : 0;
+  p.S = plan.S;
+  p.split_k = plan.split_k;
+  p.slices_per_cta = plan.slices_per_cta;
+  p.do_dense = a.do_dense ? 1 : 0;
+  p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
+
+  const size_t smem = dec::smem_bytes(plan.S);
+  const bool nt2 = a.T > 8;
+  void (*kern)(const CUtensorMap, const CUtensorMap, const dec::Params) =
+      dump ? (nt2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
+           : (nt2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(decode): %s", cudaGetErrorString(e));
+
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = dim3(plan.row_tiles, plan.split_k, plan.tok_tiles);
+  cfg.blockDim = dim3(dec::THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = a.stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = a.pdl ? 1 : 0;
+  e = cudaLaunchKernelEx(&cfg, kern, tm_low, tm_high, p);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
+int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x, int32_t* sum_X,
+                 void* X_s8, int T, int K, cudaStream_t stream) {
+  using namespace w4a4;
+  QuantParams q;
+  q.X = static_cast<const __half*>(X);
+  q.ldx = ldx;
+  q.perm = perm;
+  q.X_s4 = static_cast<int8_t*>(X_s4);
+  q.scale_x = static_cast<__half*>(scale_x);
+  q.sum_X = sum_X;
+  q.X_s8 = static_cast<int8_t*>(X_s8);
+  q.T = T;
+  q.K = K;
+  q.vec_ok = (aligned(X, 16) && (ldx % 8 == 0)) ? 1 : 0;
+  const size_t smem = (size_t)K * 2;
+  if (smem > 200 * 1024) return fail(W4A4_ERR_UNSUPPORTED, "K=%d exceeds the quantisation kernel's row buffer", K);
+  static bool attr_done = false;
+  if (smem > 48 * 1024 || !attr_done) {
+    cudaError_t e = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(quant): %s", cudaGetErrorString(e));
+    attr_done = true;
+  }
+  act_quant_kernel<<<T, QUANT_THREADS, smem, stream>>>(q);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "quant kernel launch: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
+int check_common(int T, int K, int N, int nnz) {
+  CHECK_ARG(T >= 1, "T must be >= 1, got %d", T);
+  CHECK_ARG(K >= 128 && K % 128 == 0, "d_in (%d) must be a positive multiple of 128", K);
+  CHECK_ARG(N >= 1, "d_out must be >= 1, got %d", N);
+  CHECK_ARG(nnz >= 0, "nnz must be >= 0, got %d", nnz);
+  CHECK_ARG((long long)T <= 16LL * 65535, "T=%d exceeds the grid limit", T);
+  return W4A4_OK;
+}
+
+int run_gemm(GemmArgs& a) {
+  int rc = check_common(a.T, a.K, a.N, a.nnz);
+  if (rc) return rc;
+  CHECK_ARG(a.X_s4 != nullptr, "X_s4 is NULL");
+  CHECK_ARG(a.scale_u4 != nullptr || (a.acc_dump || a.acc_hi_dump), "scale_u4 is NULL");
+  CHECK_ARG(!a.do_dense || a.W_low != nullptr, "W_low is NULL");
+  CHECK_ARG(a.nnz == 0 || (a.W_high && a.hp_row_offsets && a.hp_col_indices), "residual arrays are NULL with nnz=%d", a.nnz);
+  if (!aligned(a.W_low, 16) || !aligned(a.W_high, 16))
+    return fail(W4A4_ERR_ALIGNMENT, "weight pointers must be 16-byte aligned");
+  if (!aligned(a.X_s4, 4)) return fail(W4A4_ERR_ALIGNMENT, "X_s4 must be 4-byte aligned");
+  DeviceInfo* dev = nullptr;
+  rc = current_device(&dev);
+  if (rc) return rc;
+  const bool dump = a.acc_dump || a.acc_hi_dump;
+  bool tensor_path = w4a4::pre::supported(a.T, a.K, a.N) && a.T > 16;
+  if (a.flags & W4A4_FLAG_FORCE_STREAM) tensor_path = false;
+  if (a.flags & W4A4_FLAG_FORCE_TENSOR) {
+    if (!w4a4::pre::supported(a.T, a.K, a.N))
+      return fail(W4A4_ERR_UNSUPPORTED, "tensor-core path does not support T=%d K=%d N=%d", a.T, a.K, a.N);
+    tensor_path = true;
+  }
+  (void)dump;
+  if (tensor_path) return fail(W4A4_ERR_UNSUPPORTED, "tensor-core path not built");
+  return launch_decode(a, dev);
+}
+
+}  // namespace
+
+// ===================================================================== C ABI
+extern "C" {
+
+int w4a4_abi_version(void) { return W4A4_ABI_VERSION; }
+
+const char* w4a4_status_string(int status) {
+  switch (status) {
+    case W4A4_OK: return "ok";
+    case W4A4_ERR_BAD_ARG: return "bad argument";
+    case W4A4_ERR_ALIGNMENT: return "misaligned pointer or stride";
+    case W4A4_ERR_WORKSPACE: return "workspace missing or too small";
+    case W4A4_ERR_LAUNCH: return "CUDA launch error";
+    case W4A4_ERR_DEVICE: return "device-side wait gave up";
+    case W4A4_ERR_UNSUPPORTED: return "unsupported shape";
+    default: return "unknown status";
+  }
+}
+
+const char* w4a4_last_error(void) { return t_last_error.c_str(); }
+
+int w4a4_device_error(int* word, void* stream) {
+  CHECK_ARG(word != nullptr, "word is NULL");
+  int zero = 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemcpyFromSymbolAsync(word, w4a4::g_error_word, sizeof(int), 0, cudaMemcpyDeviceToHost, s);
+  if (e == cudaSuccess) e = cudaMemcpyToSymbolAsync(w4a4::g_error_word, &zero, sizeof(int), 0, cudaMemcpyHostToDevice, s);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "w4a4_device_error: %s", cudaGetErrorString(e));
+  return *word ? W4A4_ERR_DEVICE : W4A4_OK;
+}
+
+int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x,
+                          int32_t* sum_X, int T, int K, void* stream) {
+  int rc = check_common(T, K, 1, 0);
+  if (rc) return rc;
+  CHECK_ARG(X && X_s4 && scale_x && sum_X, "NULL tensor pointer");
+  CHECK_ARG(ldx >= K, "ldx (%lld) must be >= K (%d)", ldx, K);
+  if (!aligned(X, 2) || !aligned(X_s4, 4) || !aligned(sum_X, 4) || !aligned(scale_x, 2))
+    return fail(W4A4_ERR_ALIGNMENT, "activation_quant pointer alignment");
+  return launch_quant(X, ldx, perm, X_s4, scale_x, sum_X, nullptr, T, K, static_cast<cudaStream_t>(stream));
+}
+
+size_t w4a4_workspace_bytes(int T, int K, int N, int nnz) {
+  (void)N;
+  (void)nnz;
+  if (T < 1 || K < 128) return 0;
+  return ws_layout(T, K).total;
+}
+
+int w4a4_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
+  CHECK_ARG(workspace != nullptr, "workspace is NULL");
+  if (workspace_bytes < W4A4_WORKSPACE_COUNTER_BYTES)
+    return fail(W4A4_ERR_WORKSPACE, "workspace smaller than the counter block");
+  cudaError_t e = cudaMemsetAsync(workspace, 0, W4A4_WORKSPACE_COUNTER_BYTES, static_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
+int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                            const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
+                            const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y, int T, int K,
+                            int N, int nnz, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  CHECK_ARG(Y && zero_u4 && sum_X && scale_x, "NULL tensor pointer");
+  GemmArgs a{};
+  a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
+  a.X_s4 = X_s4; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.sum_X = sum_X; a.scale_x = scale_x; a.Y = Y;
+  a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
+  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = false;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
+  return run_gemm(a);
+}
+
+int w4a4_dense_gemm(const void* W_low, const void* X_s4, const void* scale_u4, const void* zero_u4,
+                    const int32_t* sum_X, const void* scale_x, void* Y_low, int T, int K, int N, int flags,
+                    void* workspace, size_t workspace_bytes, void* stream) {
+  CHECK_ARG(Y_low && zero_u4 && sum_X && scale_x, "NULL tensor pointer");
+  GemmArgs a{};
+  a.W_low = W_low; a.X_s4 = X_s4; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.sum_X = sum_X;
+  a.scale_x = scale_x; a.Y = Y_low;
+  a.T = T; a.K = K; a.N = N; a.nnz = 0; a.flags = flags;
+  a.do_dense = true; a.sparse_weight = 0.f; a.pdl = false;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
+  return run_gemm(a);
+}
+
+int w4a4_sparse_gemm(const void* W_high, const int32_t* hp_row_offsets, const int32_t* hp_col_indices,
+                     const void* X_s4, const void* scale_u4, const void* scale_x, void* Y_high, int T, int K, int N,
+                     int nnz, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  CHECK_ARG(Y_high && scale_x, "NULL tensor pointer");
+  if (nnz == 0) {   // empty block-CSR: the product is zero (reference: cuda_kernel/ops.py:367-369)
+    int rc0 = check_common(T, K, N, nnz);
+    if (rc0) return rc0;
+    cudaError_t e = cudaMemsetAsync(Y_high, 0, (size_t)N * T * 2, static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    return W4A4_OK;
+  }
+  GemmArgs a{};
+  a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
+  a.X_s4 = X_s4; a.scale_u4 = scale_u4; a.scale_x = scale_x; a.Y = Y_high;
+  a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
+  a.do_dense = false; a.sparse_weight = 1.f; a.pdl = false;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
+  return run_gemm(a);
+}
+
+int w4a4_fused_quant_dense_sparse(const void* X, long long ldx, const int32_t* perm, const void* W_low,
+                                  const void* W_high, const int32_t* hp_row_offsets, const int32_t* hp_col_indices,
+                                  const void* scale_u4, const void* zero_u4, void* Y, int T, int K, int N, int nnz,
+                                  int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  int rc = check_common(T, K, N, nnz);
+  if (rc) return rc;
+  CHECK_ARG(X && Y && zero_u4, "NULL tensor pointer");
+  CHECK_ARG(ldx >= K, "ldx (%lld) must be >= K (%d)", ldx, K);
+  const WsLayout wl = ws_layout(T, K);
+  if (workspace == nullptr || workspace_bytes < wl.total)
+    return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, workspace_bytes);
+  char* ws = static_cast<char*>(workspace);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  rc = launch_quant(X, ldx, perm, ws + wl.x_s4, ws + wl.scale_x, reinterpret_cast<int32_t*>(ws + wl.sum_x), nullptr,
+                    T, K, s);
+  if (rc) return rc;
+  GemmArgs a{};
+  a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
+  a.X_s4 = ws + wl.x_s4; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4;
+  a.sum_X = reinterpret_cast<int32_t*>(ws + wl.sum_x); a.scale_x = ws + wl.scale_x; a.Y = Y;
+  a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
+  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = true;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = s;
+  return run_gemm(a);
+}
+
+int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                           const int32_t* hp_col_indices, const void* X_s4, int32_t* acc, int32_t* acc_hi, int T,
+                           int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  CHECK_ARG(acc || acc_hi, "both outputs are NULL");
+  GemmArgs a{};
+  a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
+  a.X_s4 = X_s4; a.acc_dump = acc; a.acc_hi_dump = acc_hi;
+  a.T = T; a.K = K; a.N = N; a.nnz = acc_hi ? nnz : 0; a.flags = flags;
+  a.do_dense = acc != nullptr; a.sparse_weight = 16.f; a.pdl = false;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
+  return run_gemm(a);
+}
+
+}  // extern "C"

@@ -1,0 +1,357 @@
+"""Operator layer: the entry points of the reference's ``cuda_kernel/ops.py``
+(``__all__`` at :750-775) with the same names, positional order, return shapes
+and error behaviour, implemented on the C ABI of ``libw4a4_b200.so``.
+
+Differences that follow from the B200 design (results are unaffected):
+
+* one shape-aware kernel family backs every GEMM entry point, so the ``*_int4``,
+  ``*_decode`` and ``*_smallT`` names are aliases of the same call;
+* the quant kernel uses IEEE division and therefore equals the reference's
+  oracle (``tools/parity/quant_reference.py``) bit for bit;
+* there is no Triton or CPU fallback: a missing library raises at import.
+"""
+
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .pack_utils import BCOL, BROW
+
+_L = _lib.load()
+
+
+def reserve_workspace(device, T: int, d_in: int, d_out: int, n_hp_blocks: int = 0) -> None:
+    """Allocate the scratch buffer for a shape up front (needed before CUDA-graph
+    capture, where allocation is not allowed)."""
+    _lib.workspace(torch.device(device), int(T), int(d_in), int(d_out), int(n_hp_blocks))
+
+
+# ---------------------------------------------------------------------------
+# activation_quant   (reference: cuda_kernel/ops.py:223-260)
+# ---------------------------------------------------------------------------
+
+def activation_quant_cuda(
+    X_fp16: torch.Tensor,
+    perm: torch.Tensor,
+    bcol: int = BCOL,
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Per-token s4 quantisation: returns ``(X_s4 (T, D/2) int8, scale_x (T,)
+    fp16, sum_X (T, D/128) int32)``."""
+    assert X_fp16.is_cuda, "activation_quant_cuda requires a CUDA tensor"
+    assert X_fp16.dtype == torch.float16, "X must be fp16"
+    assert perm.dtype in (torch.int32, torch.int64), "perm must be int32/int64"
+    shape = X_fp16.shape
+    if X_fp16.dim() == 3:
+        T, D = shape[0] * shape[1], shape[2]
+    elif X_fp16.dim() == 2:
+        T, D = shape
+    else:
+        raise ValueError(f"X must be 2D or 3D, got shape {shape}")
+    if bcol != BCOL:
+        raise ValueError(f"bcol must be {BCOL}, got {bcol}")
+    if D % bcol != 0:
+        raise ValueError(f"d_in ({D}) must be divisible by bcol ({bcol})")
+    X_2d = X_fp16.reshape(T, D).contiguous()
+    perm_i32 = perm.to(device=X_2d.device, dtype=torch.int32).contiguous()
+    dev = X_2d.device
+    X_s4 = torch.empty((T, D // 2), dtype=torch.int8, device=dev)
+    scale_x = torch.empty((T,), dtype=torch.float16, device=dev)
+    sum_X = torch.empty((T, D // bcol), dtype=torch.int32, device=dev)
+    if T == 0:
+        return X_s4, scale_x, sum_X
+    with torch.cuda.device(dev):
+        _lib.check(_L.w4a4_activation_quant(
+            X_2d.data_ptr(), X_2d.stride(0), perm_i32.data_ptr(), X_s4.data_ptr(),
+            scale_x.data_ptr(), sum_X.data_ptr(), int(T), int(D), _lib.stream_ptr(dev),
+        ), "activation_quant")
+    return X_s4, scale_x, sum_X
+
+
+# ---------------------------------------------------------------------------
+# argument preparation shared by the GEMM entry points (ops.py:268-298,419-460)
+# ---------------------------------------------------------------------------
+
+def _prep_dense(W_low_packed, X_s4, scale_u4, zero_u4, sum_X, scale_x):
+    assert W_low_packed.is_cuda and X_s4.is_cuda
+    assert W_low_packed.dtype == torch.int8 and X_s4.dtype == torch.int8
+    d_out, d_in_half = W_low_packed.shape
+    T = X_s4.shape[0]
+    d_in = d_in_half * 2
+    ng = d_in // BCOL
+    assert X_s4.shape == (T, d_in_half)
+    assert scale_u4.shape == (d_out, ng)
+    assert zero_u4.shape == (d_out, ng)
+    assert sum_X.shape == (T, ng)
+    assert scale_x.shape == (T,)
+    return (W_low_packed.contiguous(), X_s4.contiguous(),
+            scale_u4.contiguous().to(torch.float16), zero_u4.contiguous().to(torch.float16),
+            sum_X.contiguous().to(torch.int32), scale_x.contiguous().to(torch.float16),
+            int(T), int(d_in), int(d_out))
+
+
+def _flags(token_major: bool, force: Optional[str]) -> int:
+    f = _lib.FLAG_OUT_TOKEN_MAJOR if token_major else 0
+    if force == "stream":
+        f |= _lib.FLAG_FORCE_STREAM
+    elif force == "tensor":
+        f |= _lib.FLAG_FORCE_TENSOR
+    elif force is not None:
+        raise ValueError(f"force must be None, 'stream' or 'tensor', got {force!r}")
+    return f
+
+
+def _out(d_out: int, T: int, device, token_major: bool) -> torch.Tensor:
+    shape = (T, d_out) if token_major else (d_out, T)
+    return torch.empty(shape, dtype=torch.float16, device=device)
+
+
+def dense_gemm_cuda_int4(W_low_packed, X_s4, scale_u4, zero_u4, sum_X, scale_x,
+                         *, token_major: bool = False, force: Optional[str] = None) -> torch.Tensor:
+    """Dense u4 x s4 GEMM: ``Y_low (d_out, T)`` fp16 (ops.py:314-320)."""
+    W, X, s, z, sm, sx, T, K, N = _prep_dense(W_low_packed, X_s4, scale_u4, zero_u4, sum_X, scale_x)
+    Y = _out(N, T, W.device, token_major)
+    if T == 0:
+        return Y
+    with torch.cuda.device(W.device):
+        ws = _lib.workspace(W.device, T, K, N, 0)
+        _lib.check(_L.w4a4_dense_gemm(
+            W.data_ptr(), X.data_ptr(), s.data_ptr(), z.data_ptr(), sm.data_ptr(), sx.data_ptr(),
+            Y.data_ptr(), T, K, N, _flags(token_major, force), ws.data_ptr(), ws.numel(),
+            _lib.stream_ptr(W.device)), "dense_gemm")
+    return Y
+
+
+# T-specialised names of the reference map onto the same shape-aware launcher.
+dense_gemv_cuda_decode = dense_gemm_cuda_int4
+dense_gemm_cuda = dense_gemm_cuda_int4
+
+
+def dense_gemm_cuda_int8(*args, **kwargs):
+    """Archived in the reference (ops.py:306-311); kept as a raising stub."""
+    raise RuntimeError(
+        "dense_gemm_cuda_int8 is archived; use dense_gemm_cuda_int4 (the production path)."
+    )
+
+
+def sparse_gemm_cuda_int4(W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+                          X_s4, scale_u4, scale_x, d_out, d_in,
+                          *, token_major: bool = False, force: Optional[str] = None) -> torch.Tensor:
+    """Block-CSR s4 x s4 GEMM: ``Y_high (d_out, T)`` fp16 WITHOUT the factor 16;
+    zeros (and no launch) for an empty block list (ops.py:360-408)."""
+    assert X_s4.is_cuda
+    T = int(X_s4.shape[0])
+    d_out, d_in = int(d_out), int(d_in)
+    dev = X_s4.device
+    nnz = int(W_high_blocks_packed.shape[0])
+    if nnz == 0 or T == 0:
+        return torch.zeros((T, d_out) if token_major else (d_out, T), dtype=torch.float16, device=dev)
+    Wh = W_high_blocks_packed.contiguous()
+    ro = hp_row_offsets.contiguous().to(torch.int32)
+    ci = hp_col_indices.contiguous().to(torch.int32)
+    X = X_s4.contiguous()
+    s = scale_u4.contiguous().to(torch.float16)
+    sx = scale_x.contiguous().to(torch.float16)
+    _check_bsr(ro, ci, d_out, d_in, nnz)
+    Y = _out(d_out, T, dev, token_major)
+    with torch.cuda.device(dev):
+        ws = _lib.workspace(dev, T, d_in, d_out, nnz)
+        _lib.check(_L.w4a4_sparse_gemm(
+            Wh.data_ptr(), ro.data_ptr(), ci.data_ptr(), X.data_ptr(), s.data_ptr(), sx.data_ptr(),
+            Y.data_ptr(), T, d_in, d_out, nnz, _flags(token_major, force), ws.data_ptr(), ws.numel(),
+            _lib.stream_ptr(dev)), "sparse_gemm")
+    return Y
+
+
+sparse_gemm_cuda = sparse_gemm_cuda_int4
+
+
+def sparse_gemm_cuda_int8(*args, **kwargs):
+    """Archived in the reference (ops.py:386-391); kept as a raising stub."""
+    raise RuntimeError("sparse_gemm_cuda_int8 is archived; use sparse_gemm_cuda_int4.")
+
+
+def _check_bsr(hp_row_offsets, hp_col_indices, d_out, d_in, nnz):
+    nbr = (d_out + BROW - 1) // BROW
+    if hp_row_offsets.numel() != nbr + 1:
+        raise RuntimeError(
+            f"hp_row_offsets must have ceil(d_out/128)+1 = {nbr + 1} entries, got {hp_row_offsets.numel()}"
+        )
+    if hp_col_indices.numel() != nnz:
+        raise RuntimeError(f"hp_col_indices must have {nnz} entries, got {hp_col_indices.numel()}")
+    if d_in % BCOL != 0:
+        raise RuntimeError(f"d_in ({d_in}) must be divisible by {BCOL}")
+
+
+def _prep_fused(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+                X_s4, scale_u4, zero_u4, sum_X, scale_x, d_out, d_in):
+    assert W_low_packed.is_cuda and X_s4.is_cuda
+    assert W_low_packed.dtype == torch.int8 and X_s4.dtype == torch.int8
+    d_out, d_in = int(d_out), int(d_in)
+    T = int(X_s4.shape[0])
+    ng = d_in // BCOL
+    assert X_s4.shape == (T, d_in // 2)
+    assert scale_u4.shape == (d_out, ng)
+    assert zero_u4.shape == (d_out, ng)
+    assert sum_X.shape == (T, ng)
+    assert scale_x.shape == (T,)
+    if W_high_blocks_packed.numel() == 0:
+        W_high_blocks_packed = torch.zeros((0, BROW, BCOL // 2), dtype=torch.int8,
+                                           device=W_low_packed.device)
+    ro = hp_row_offsets.contiguous().to(torch.int32)
+    ci = hp_col_indices.contiguous().to(torch.int32)
+    _check_bsr(ro, ci, d_out, d_in, int(W_high_blocks_packed.shape[0]))
+    return (W_low_packed.contiguous(), W_high_blocks_packed.contiguous(), ro, ci, X_s4.contiguous(),
+            scale_u4.contiguous().to(torch.float16), zero_u4.contiguous().to(torch.float16),
+            sum_X.contiguous().to(torch.int32), scale_x.contiguous().to(torch.float16), T, d_in, d_out)
+
+
+def fused_dense_sparse_cuda_int4(
+    W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+    X_s4, scale_u4, zero_u4, sum_X, scale_x, d_out, d_in,
+    *, token_major: bool = False, force: Optional[str] = None,
+) -> torch.Tensor:
+    """Fused dense + 16 x residual GEMM: ``Y_total (d_out, T)`` fp16 (ops.py:471-481)."""
+    (W, Wh, ro, ci, X, s, z, sm, sx, T, K, N) = _prep_fused(
+        W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+        X_s4, scale_u4, zero_u4, sum_X, scale_x, d_out, d_in)
+    Y = _out(N, T, W.device, token_major)
+    if T == 0:
+        return Y
+    nnz = int(Wh.shape[0])
+    with torch.cuda.device(W.device):
+        ws = _lib.workspace(W.device, T, K, N, nnz)
+        _lib.check(_L.w4a4_fused_dense_sparse(
+            W.data_ptr(), Wh.data_ptr() if nnz else None, ro.data_ptr(), ci.data_ptr() if nnz else None,
+            X.data_ptr(), s.data_ptr(), z.data_ptr(), sm.data_ptr(), sx.data_ptr(), Y.data_ptr(),
+            T, K, N, nnz, _flags(token_major, force), ws.data_ptr(), ws.numel(),
+            _lib.stream_ptr(W.device)), "fused_dense_sparse")
+    return Y
+
+
+fused_gemv_cuda_decode = fused_dense_sparse_cuda_int4
+fused_gemv_cuda_smallT = fused_dense_sparse_cuda_int4
+fused_dense_sparse_cuda = fused_dense_sparse_cuda_int4
+
+
+def fused_dense_sparse_cuda_int8(*args, **kwargs):
+    """Archived in the reference (ops.py:463-468); kept as a raising stub."""
+    raise RuntimeError(
+        "fused_dense_sparse_cuda_int8 is archived; use fused_dense_sparse_cuda_int4."
+    )
+
+
+def fused_dense_sparse_e2e_cuda(
+    X_fp16, perm,
+    W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+    scale_u4, zero_u4, d_out, d_in,
+    *, token_major: bool = False, force: Optional[str] = None,
+) -> torch.Tensor:
+    """fp16 activations in, ``Y (d_out, T)`` fp16 out: quantisation and GEMM are
+    chained inside one C-ABI call (ops.py:707-747)."""
+    assert X_fp16.is_cuda and X_fp16.dtype == torch.float16
+    assert perm.dtype in (torch.int32, torch.int64)
+    assert W_low_packed.is_cuda and W_low_packed.dtype == torch.int8
+    d_out, d_in = int(d_out), int(d_in)
+    if X_fp16.shape[-1] != d_in:
+        raise ValueError(f"X last dim ({X_fp16.shape[-1]}) must match d_in ({d_in})")
+    X2 = X_fp16.reshape(-1, d_in).contiguous()
+    T = int(X2.shape[0])
+    dev = W_low_packed.device
+    W = W_low_packed.contiguous()
+    Wh = W_high_blocks_packed.contiguous()
+    nnz = int(Wh.shape[0]) if Wh.numel() else 0
+    ro = hp_row_offsets.contiguous().to(torch.int32)
+    ci = hp_col_indices.contiguous().to(torch.int32)
+    _check_bsr(ro, ci, d_out, d_in, nnz)
+    s = scale_u4.contiguous().to(torch.float16)
+    z = zero_u4.contiguous().to(torch.float16)
+    perm_i32 = perm.to(device=dev, dtype=torch.int32).contiguous()
+    Y = _out(d_out, T, dev, token_major)
+    if T == 0:
+        return Y
+    with torch.cuda.device(dev):
+        ws = _lib.workspace(dev, T, d_in, d_out, nnz)
+        _lib.check(_L.w4a4_fused_quant_dense_sparse(
+            X2.data_ptr(), X2.stride(0), perm_i32.data_ptr(), W.data_ptr(),
+            Wh.data_ptr() if nnz else None, ro.data_ptr(), ci.data_ptr() if nnz else None,
+            s.data_ptr(), z.data_ptr(), Y.data_ptr(), T, d_in, d_out, nnz,
+            _flags(token_major, force), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)),
+            "fused_quant_dense_sparse")
+    return Y
+
+
+def fused_quant_gemv_cuda(
+    X_fp16, perm,
+    W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+    scale_u4, zero_u4, d_out, d_in,
+) -> torch.Tensor:
+    """T == 1 fused quant + GEMV (ops.py:484-517); any d_in is accepted here."""
+    T = X_fp16.shape[0]
+    if T != 1:
+        raise ValueError(f"fused_quant_gemv_cuda requires T == 1, got {T}")
+    return fused_dense_sparse_e2e_cuda(X_fp16, perm, W_low_packed, W_high_blocks_packed,
+                                       hp_row_offsets, hp_col_indices, scale_u4, zero_u4, d_out, d_in)
+
+
+def fused_quant_dense_sparse_cuda_int4(
+    X_fp16, perm,
+    W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+    scale_u4, zero_u4, d_out, d_in,
+) -> torch.Tensor:
+    """T >= 2 fused quant + GEMM (ops.py:558-622); the residual is supported."""
+    T = X_fp16.shape[0] if X_fp16.dim() == 2 else X_fp16.shape[0] * X_fp16.shape[1]
+    if T < 2:
+        raise ValueError(
+            f"fused_quant_dense_sparse_cuda_int4 requires T >= 2, got {T}; "
+            f"use fused_quant_gemv_cuda for T=1."
+        )
+    return fused_dense_sparse_e2e_cuda(X_fp16, perm, W_low_packed, W_high_blocks_packed,
+                                       hp_row_offsets, hp_col_indices, scale_u4, zero_u4, d_out, d_in)
+
+
+def dump_accumulators(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices, X_s4,
+                      d_out, d_in, *, force: Optional[str] = None):
+    """Parity aid: the exact int32 accumulators of the MMA path, ``acc (ng, d_out,
+    T)`` per group and ``acc_hi (nnz, 128, T)`` per residual block."""
+    d_out, d_in = int(d_out), int(d_in)
+    T = int(X_s4.shape[0])
+    dev = X_s4.device
+    nnz = int(W_high_blocks_packed.shape[0]) if W_high_blocks_packed is not None else 0
+    acc = torch.zeros((d_in // BCOL, d_out, T), dtype=torch.int32, device=dev)
+    acc_hi = torch.zeros((nnz, BROW, T), dtype=torch.int32, device=dev)
+    W = W_low_packed.contiguous()
+    X = X_s4.contiguous()
+    with torch.cuda.device(dev):
+        ws = _lib.workspace(dev, T, d_in, d_out, nnz)
+        _lib.check(_L.w4a4_dump_accumulators(
+            W.data_ptr(), W_high_blocks_packed.contiguous().data_ptr() if nnz else None,
+            hp_row_offsets.contiguous().to(torch.int32).data_ptr() if nnz else None,
+            hp_col_indices.contiguous().to(torch.int32).data_ptr() if nnz else None,
+            X.data_ptr(), acc.data_ptr(), acc_hi.data_ptr() if nnz else None, T, d_in, d_out, nnz,
+            _flags(False, force), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)), "dump_accumulators")
+    return acc, acc_hi
+
+
+__all__ = [
+    "activation_quant_cuda",
+    "dense_gemm_cuda",
+    "sparse_gemm_cuda",
+    "fused_dense_sparse_cuda",
+    "dense_gemm_cuda_int8",
+    "sparse_gemm_cuda_int8",
+    "fused_dense_sparse_cuda_int8",
+    "dense_gemm_cuda_int4",
+    "sparse_gemm_cuda_int4",
+    "fused_dense_sparse_cuda_int4",
+    "dense_gemv_cuda_decode",
+    "fused_gemv_cuda_decode",
+    "fused_gemv_cuda_smallT",
+    "fused_quant_gemv_cuda",
+    "fused_quant_dense_sparse_cuda_int4",
+    "fused_dense_sparse_e2e_cuda",
+    "dump_accumulators",
+    "reserve_workspace",
+]

@@ -1,0 +1,91 @@
+"""Module-level forward of the W4A4 linear.
+
+Interface of the reference's ``triton_kernel/v9_linear.py`` (``v9_linear_forward``
+:374-436, ``v9_linear_forward_decode`` :439-465, ``v9_linear_forward_prefill``
+:468-484, ``reconstruct_w_fakequant_fp16`` :491-534, ``v9_linear_fakequant``
+:537-562, ``DECODE_T_THRESHOLD`` :206) and of ``backend/dispatcher.py:271-338``.
+
+The reference runs quant -> dense (+ sparse) -> combine + transpose as separate
+launches.  Here one C-ABI call chains the quantisation kernel and a fused GEMM
+that writes the ``(T, d_out)`` layout directly, so there is no combine/transpose
+pass; decode and prefill differ only in which GEMM kernel the library selects.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from . import ops
+from .pack_utils import BCOL, V9WeightContainer, unpack_s4_le
+
+DECODE_T_THRESHOLD = 128
+
+
+def _forward(X_fp16: torch.Tensor, W: V9WeightContainer, force=None) -> torch.Tensor:
+    assert X_fp16.is_cuda and X_fp16.dtype == torch.float16
+    d_in, d_out = W.d_in, W.d_out
+    if X_fp16.shape[-1] != d_in:
+        raise ValueError(f"X last dim ({X_fp16.shape[-1]}) must match d_in ({d_in})")
+    X_2d = X_fp16.reshape(-1, d_in)
+    Y = ops.fused_dense_sparse_e2e_cuda(
+        X_2d, W.perm, W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
+        W.hp_col_indices, W.scale_u4, W.zero_u4, d_out, d_in, token_major=True, force=force)
+    return Y.reshape(X_fp16.shape[:-1] + (d_out,))
+
+
+def v9_linear_forward(X_fp16: torch.Tensor, W: V9WeightContainer) -> torch.Tensor:
+    """``Y (..., d_out)`` fp16 for ``X (..., d_in)`` fp16."""
+    return _forward(X_fp16, W)
+
+
+def v9_linear_forward_decode(X_fp16: torch.Tensor, W: V9WeightContainer) -> torch.Tensor:
+    """Explicit decode entry; any T is accepted (same result as the dispatcher)."""
+    return _forward(X_fp16, W)
+
+
+def v9_linear_forward_prefill(X_fp16: torch.Tensor, W: V9WeightContainer) -> torch.Tensor:
+    """Explicit prefill entry; any T is accepted (same result as the dispatcher)."""
+    return _forward(X_fp16, W)
+
+
+def reconstruct_w_fakequant_fp16(W: V9WeightContainer) -> torch.Tensor:
+    """Dequantised ``(d_out, d_in)`` fp16 weight in permuted column order:
+    ``(w_low - zero) * scale + 16 * w_high * scale`` on the residual blocks."""
+    d_out, d_in = W.d_out, W.d_in
+    scale = W.scale_u4.to(torch.float32)
+    w = (unpack_s4_le(W.W_low_packed).to(torch.float32)
+         - W.zero_u4.to(torch.float32).repeat_interleave(BCOL, dim=1)) * scale.repeat_interleave(BCOL, dim=1)
+    if W.n_hp_blocks > 0:
+        tiles = unpack_s4_le(W.W_high_blocks_packed).to(torch.float32)
+        offs = W.hp_row_offsets.cpu().tolist()
+        cols = W.hp_col_indices.cpu().tolist()
+        brow, bcol = W.block_shape
+        for br in range(len(offs) - 1):
+            r0, r1 = br * brow, min((br + 1) * brow, d_out)
+            for b in range(offs[br], offs[br + 1]):
+                c0 = cols[b] * bcol
+                w[r0:r1, c0:c0 + bcol] += 16.0 * tiles[b, : r1 - r0] * scale[r0:r1, cols[b]:cols[b] + 1]
+    return w.to(torch.float16)
+
+
+def v9_linear_fakequant(X_fp16: torch.Tensor, W: V9WeightContainer) -> torch.Tensor:
+    """fp16 reference forward on the dequantised weight with fake-quantised
+    activations (a correctness cross-check, not a fast path)."""
+    X_2d = X_fp16.reshape(-1, W.d_in)
+    Xp = X_2d[:, W.perm.to(torch.long)]
+    W_fp = reconstruct_w_fakequant_fp16(W)
+    max_abs = Xp.abs().amax(dim=-1, keepdim=True).clamp(min=1e-12)
+    scale_x = (max_abs / 7.0).to(torch.float16).to(torch.float32)
+    q = torch.clamp(torch.round(Xp.to(torch.float32) / scale_x), -8.0, 7.0)
+    Y = (q * scale_x).to(torch.float16) @ W_fp.t()
+    return Y.reshape(X_fp16.shape[:-1] + (W.d_out,))
+
+
+__all__ = [
+    "v9_linear_forward",
+    "v9_linear_forward_decode",
+    "v9_linear_forward_prefill",
+    "v9_linear_fakequant",
+    "reconstruct_w_fakequant_fp16",
+    "DECODE_T_THRESHOLD",
+]

@@ -248,11 +248,9 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   q.vec_ok = (aligned(X, 16) && (ldx % 8 == 0)) ? 1 : 0;
   const size_t smem = (size_t)K * 2;
   if (smem > 200 * 1024) return fail(W4A4_ERR_UNSUPPORTED, "K=%d exceeds the quantisation kernel's row buffer", K);
-  static bool attr_done = false;
-  if (smem > 48 * 1024 || !attr_done) {
+  if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(quant): %s", cudaGetErrorString(e));
-    attr_done = true;
   }
   act_quant_kernel<<<T, QUANT_THREADS, smem, stream>>>(q);
   cudaError_t e = cudaGetLastError();

@@ -131,12 +131,13 @@ def build_inputs(items, device, n_sets):
 
 def alg_bytes_gemm(it):
     """Bytes one GEMM launch must move: weights, scales/zeros, residual blocks and
-    index, quantised activations with their scales and group sums, output."""
+    index, expanded activation codes (one byte each) with their scales and group
+    sums, output."""
     M, K, N = it["M"], it["K"], it["N"]
     nnz = it["W"][0].n_hp_blocks
     ng, nbr = K // 128, (N + 127) // 128
     b_w = K * N // 2 + 4 * N * ng + 8192 * nnz + 4 * (nbr + 1) + 4 * nnz
-    return b_w + (M * K // 2 + 2 * M + 4 * M * ng) + 2 * M * N
+    return b_w + (M * K + 2 * M + 4 * M * ng) + 2 * M * N
 
 
 # ----------------------------------------------------------------------------- reference arm
@@ -233,9 +234,9 @@ def main():
         for it in data:
             W = it["W"][r]
             q = it["q"]
-            ops.fused_dense_sparse_cuda(W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
-                                        W.hp_col_indices, q[0], W.scale_u4, W.zero_u4, q[2], q[1],
-                                        W.d_out, W.d_in, token_major=True)
+            ops.fused_dense_sparse_expanded_cuda(W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
+                                                 W.hp_col_indices, it["XE"], it["sumxf"], W.scale_u4,
+                                                 W.zero_u4, q[1], W.d_out, W.d_in, token_major=True)
 
     def e2e_step(r):
         ys = []
@@ -249,6 +250,7 @@ def main():
     # eager warm-up (also sizes every workspace before capture)
     for it in data:
         it["q"] = ops.activation_quant_cuda(it["X_dev"], it["W"][0].perm)
+        it["XE"], it["sumxf"] = ops.expand_activations_cuda(it["q"][0], it["q"][2])
     for r in range(n_sets):
         device_step(r)
         gemm_only_step(r)

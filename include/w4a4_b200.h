@@ -85,6 +85,24 @@ int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t
                             int T, int K, int N, int nnz, int flags, void* workspace,
                             size_t workspace_bytes, void* stream);
 
+/* Activations in the layout the GEMM kernels consume ("expanded"): XE (T, K) int8,
+ * one byte per code, every packed 32-bit word of X_s4 turned into its four
+ * even-indexed codes followed by its four odd-indexed ones; sumxf
+ * [ceil(T/16)][K/128][16] float = sum_X transposed per 16-token tile.
+ * w4a4_fused_dense_sparse builds both internally on every call; a caller that
+ * feeds several linears from one activation (q/k/v, gate/up) can build them once
+ * with w4a4_expand_activations and call w4a4_fused_dense_sparse_expanded.  No
+ * counterpart in the reference's bindings (its kernels read X_s4 directly). */
+size_t w4a4_expanded_codes_bytes(int T, int K);
+size_t w4a4_expanded_sums_bytes(int T, int K);
+int w4a4_expand_activations(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
+                            void* stream);
+int w4a4_fused_dense_sparse_expanded(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                                     const int32_t* hp_col_indices, const void* XE, const float* sumxf,
+                                     const void* scale_u4, const void* zero_u4, const void* scale_x, void* Y,
+                                     int T, int K, int N, int nnz, int flags, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+
 /* Replaces dense_gemm_mma_int4_launch and dense_gemv_decode_launch
  * (bindings.cc:124-148; dense_gemm_mma_int4.cu:39-431, dense_gemv_decode.cu:86-182). */
 int w4a4_dense_gemm(const void* W_low, const void* X_s4, const void* scale_u4, const void* zero_u4,

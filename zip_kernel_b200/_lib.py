@@ -31,6 +31,10 @@ SIGNATURES = {
     "w4a4_workspace_bytes": (_SZ, [_INT, _INT, _INT, _INT]),
     "w4a4_workspace_init": (_INT, [_PTR, _SZ, _PTR]),
     "w4a4_fused_dense_sparse": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_expanded_codes_bytes": (_SZ, [_INT, _INT]),
+    "w4a4_expanded_sums_bytes": (_SZ, [_INT, _INT]),
+    "w4a4_expand_activations": (_INT, [_PTR] * 4 + [_INT, _INT, _PTR]),
+    "w4a4_fused_dense_sparse_expanded": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_dense_gemm": (_INT, [_PTR] * 7 + [_INT] * 4 + [_PTR, _SZ, _PTR]),
     "w4a4_sparse_gemm": (_INT, [_PTR] * 7 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_fused_quant_dense_sparse": (_INT, [_PTR, _LL] + [_PTR] * 8 + [_INT] * 5 + [_PTR, _SZ, _PTR]),

@@ -28,13 +28,16 @@ struct QuantParams {
   const __half* X;        // (T, K) fp16, row stride ldx elements
   long long ldx;
   const int* perm;        // (K) or nullptr for identity
-  int8_t* X_s4;           // (T, K/2)
+  int8_t* X_s4;           // (T, K/2) or nullptr
   __half* scale_x;        // (T)
-  int* sum_X;             // (T, K/128)
-  int8_t* X_s8;           // optional (T, K) expanded codes for the tensor-core path, or nullptr
+  int* sum_X;             // (T, K/128) or nullptr
+  int8_t* XE;             // optional (T, K) expanded codes (see expand_word), or nullptr
+  float* sumxf;           // optional [ceil(T/16)][K/128][16] float group sums, or nullptr
   int T, K;
   int vec_ok;             // 1 when every row start is 16-byte aligned
 };
+
+__device__ __forceinline__ uint2 expand_word(uint32_t w) { return make_uint2(nib_lo_s8(w), nib_hi_s8(w)); }
 
 __device__ __forceinline__ float half_abs_max8(const uint4& v, float m) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
@@ -64,7 +67,7 @@ act_quant_kernel(const QuantParams p) {
   if (p.perm == nullptr && p.vec_ok) {
     const uint4* src = reinterpret_cast<const uint4*>(xrow);
     for (int c = tid; c < nchunk; c += QUANT_THREADS) {
-      uint4 v = __ldg(src + c);
+      uint4 v = ld_plain(src + c);
       row[c] = v;
       m = half_abs_max8(v, m);
     }
@@ -74,7 +77,7 @@ act_quant_kernel(const QuantParams p) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         int k = c * 8 + j;
-        int src = p.perm ? __ldg(p.perm + k) : k;
+        int src = p.perm ? ld_plain(p.perm + k) : k;
         h[j] = xrow[src];
       }
       uint4 v = *reinterpret_cast<uint4*>(h);
@@ -96,8 +99,10 @@ act_quant_kernel(const QuantParams p) {
   const float s_safe = zero_row ? 1.0f : s;
   if (tid == 0) p.scale_x[t] = scale16;
 
-  uint32_t* out = reinterpret_cast<uint32_t*>(p.X_s4 + (long long)t * (p.K >> 1));
-  int* sums = p.sum_X + (long long)t * (p.K >> 7);
+  uint32_t* out = p.X_s4 ? reinterpret_cast<uint32_t*>(p.X_s4 + (long long)t * (p.K >> 1)) : nullptr;
+  int* sums = p.sum_X ? p.sum_X + (long long)t * (p.K >> 7) : nullptr;
+  const int ng = p.K >> 7;
+  float* sumsf = p.sumxf ? p.sumxf + ((long long)(t >> 4) * ng) * 16 + (t & 15) : nullptr;
   // All lanes of a warp run the same number of iterations (nchunk is a multiple
   // of 16 and lanes are consecutive), so the shuffles below are convergent for
   // every 16-lane half that holds a live group.
@@ -120,18 +125,48 @@ act_quant_kernel(const QuantParams p) {
         word |= (uint32_t)(i0 & 0xF) << (8 * i);
         word |= (uint32_t)(i1 & 0xF) << (8 * i + 4);
       }
-      out[c] = word;
-      if (p.X_s8) {
-        // expanded copy, one byte per code: every 32 codes (16 packed bytes)
-        // become 16 bytes of even-indexed codes followed by 16 bytes of odd ones
-        uint32_t* e = reinterpret_cast<uint32_t*>(p.X_s8 + (long long)t * p.K) + (c >> 2) * 8 + (c & 3);
-        e[0] = nib_lo_s8(word);
-        e[4] = nib_hi_s8(word);
-      }
+      if (out) out[c] = word;
+      if (p.XE) reinterpret_cast<uint2*>(p.XE + (long long)t * p.K)[c] = expand_word(word);
     }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (live && (tid & 15) == 0) sums[c >> 4] = sum;
+    if (live && (tid & 15) == 0) {
+      if (sums) sums[c >> 4] = sum;
+      if (sumsf) sumsf[(c >> 4) * 16] = (float)sum;
+    }
+  }
+}
+
+// Expanded activation layout ("XE") consumed by both GEMM kernels: one byte per
+// code, and every packed 32-bit word (8 codes) becomes 8 bytes - its four
+// even-indexed codes, then its four odd-indexed ones, each sign-extended to s8.
+// The weights are permuted the same way when their nibbles are expanded, so the
+// dot products pair up.  This kernel builds XE and the transposed float group
+// sums from already-quantised activations (the operator-level entry points that
+// receive X_s4 / sum_X from the caller).
+struct ExpandParams {
+  const int8_t* X_s4;   // (T, K/2)
+  const int* sum_X;     // (T, K/128) or nullptr
+  int8_t* XE;           // (T, K)
+  float* sumxf;         // [ceil(T/16)][K/128][16]
+  int T, K;
+};
+
+__global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandParams p) {
+  grid_launch_dependents();
+  const long long words = (long long)p.T * (p.K >> 3);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const uint32_t* src = reinterpret_cast<const uint32_t*>(p.X_s4);
+  uint2* dst = reinterpret_cast<uint2*>(p.XE);
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride)
+    dst[i] = expand_word(ld_plain(src + i));
+  if (p.sum_X) {
+    const int ng = p.K >> 7;
+    const long long n = (long long)p.T * ng;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+      const int t = (int)(i / ng), g = (int)(i - (long long)t * ng);
+      p.sumxf[((long long)(t >> 4) * ng + g) * 16 + (t & 15)] = (float)ld_plain(p.sum_X + i);
+    }
   }
 }
 

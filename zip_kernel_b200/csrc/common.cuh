@@ -28,6 +28,13 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
 
+// Plain (non-speculatable) global load.  The __ldg intrinsic is a non-volatile
+// asm statement that the compiler may hoist above the branch that guards it, so
+// a load whose address is only valid under a condition (a nullable operand, a
+// ragged tail) must not use it: a hoisted __ldg on a null pointer faults.
+template <typename T>
+__device__ __forceinline__ T ld_plain(const T* p) { return *p; }
+
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
@@ -88,6 +95,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const void* tmap, in
       " [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1),
         "r"(smem_u32(bar))
+      : "memory");
+}
+
+// 1-D bulk copy global -> shared; both addresses and the size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
 

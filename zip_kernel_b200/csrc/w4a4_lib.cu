@@ -91,50 +91,54 @@ int make_map(CUtensorMap* m, const void* ptr, uint64_t row_bytes, uint64_t rows,
 }
 
 // ------------------------------------------------------------------ workspace layout
-constexpr size_t WS_PARTIAL_BYTES = 8u << 20;   // split-K partial sums (<= 1024 row-tile slices)
+constexpr size_t WS_PARTIAL_TILES = 1024;                                   // shared block-row pieces
+constexpr size_t WS_PARTIAL_BYTES = WS_PARTIAL_TILES * 128 * 16 * 4;       // 8 MiB
 struct WsLayout {
-  size_t counters, partial, x_s4, scale_x, sum_x, x_s8, total;
+  size_t counters, partial, x_s4, scale_x, sum_x, xe, sumxf, total;
 };
 WsLayout ws_layout(int T, int K) {
   WsLayout w;
+  const size_t ng = K / 128, tok_tiles = (T + 15) / 16;
   size_t off = 0;
   w.counters = off; off += W4A4_WORKSPACE_COUNTER_BYTES;
   w.partial = off;  off += WS_PARTIAL_BYTES;
   w.x_s4 = off;     off += round_up((size_t)T * (K / 2), 256);
   w.scale_x = off;  off += round_up((size_t)T * 2, 256);
-  w.sum_x = off;    off += round_up((size_t)T * (K / 128) * 4, 256);
-  w.x_s8 = off;     off += round_up((size_t)T * K, 1024);
+  w.sum_x = off;    off += round_up((size_t)T * ng * 4, 256);
+  w.xe = off;       off += round_up((size_t)T * K, 1024);
+  w.sumxf = off;    off += round_up(tok_tiles * ng * 16 * 4, 256);
   w.total = off;
   return w;
 }
 
 // ------------------------------------------------------------------ plans
 struct DecodePlan {
-  int S, split_k, slices_per_cta, row_tiles, tok_tiles;
+  int row_tiles, tok_tiles, ctas, steps_per_cta;   // steps_per_cta == 0: one block-row per CTA
 };
-DecodePlan plan_decode(int T, int K, int N, int sm_count, bool allow_split) {
+DecodePlan plan_decode(int T, int K, int N, long long steps_total, int sm_count) {
   using namespace w4a4;
   DecodePlan p;
-  const int ng = K / BCOL;
   p.row_tiles = (N + dec::ROWS - 1) / dec::ROWS;
   p.tok_tiles = (T + dec::TOK - 1) / dec::TOK;
-  const long long base = (long long)p.row_tiles * p.tok_tiles;
-  const long long target = 2LL * sm_count;
-  p.S = ng < dec::S_MAX ? ng : dec::S_MAX;
-  p.split_k = 1;
-  if (allow_split && base < target && ng > 1) {
-    int want = (int)((target + base - 1) / base);
-    int S = (ng + want - 1) / want;
-    if (S < 1) S = 1;
-    if (S > dec::S_MAX) S = dec::S_MAX;
-    int slices = (ng + S - 1) / S;
-    if (slices > 1 && base * slices <= 1024) {
-      p.S = S;
-      p.split_k = slices;
-    }
+  const long long resident = 2LL * sm_count;
+  // enough independent (block-row, token tile) pairs: no shared rows needed
+  if ((long long)p.row_tiles * p.tok_tiles >= 2 * resident) {
+    p.ctas = p.row_tiles;
+    p.steps_per_cta = 0;
+    return p;
   }
-  const int n_slices = (ng + p.S - 1) / p.S;
-  p.slices_per_cta = p.split_k > 1 ? 1 : n_slices;
+  long long want = (resident + p.tok_tiles - 1) / p.tok_tiles;
+  long long L = (steps_total + want - 1) / want;
+  if (L < 2) L = 2;
+  long long ctas = (steps_total + L - 1) / L;
+  if ((ctas + p.row_tiles) * p.tok_tiles > (long long)WS_PARTIAL_TILES ||
+      (long long)p.row_tiles * p.tok_tiles * 4 > W4A4_WORKSPACE_COUNTER_BYTES) {
+    p.ctas = p.row_tiles;
+    p.steps_per_cta = 0;
+    return p;
+  }
+  p.ctas = (int)ctas;
+  p.steps_per_cta = (int)L;
   return p;
 }
 
@@ -143,8 +147,9 @@ struct GemmArgs {
   const void* W_high;
   const int32_t* hp_row_offsets;
   const int32_t* hp_col_indices;
-  const void* X_s4;
-  const void* X_s8;        // expanded activations when already available, else NULL
+  const void* X_s4;        // packed activation codes, or NULL when XE is given
+  const void* XE;          // expanded activation codes (T, K), or NULL
+  const float* sumxf;      // transposed float group sums that go with XE
   const void* scale_u4;
   const void* zero_u4;
   const int32_t* sum_X;
@@ -161,17 +166,63 @@ struct GemmArgs {
   cudaStream_t stream;
 };
 
+cudaError_t launch_pdl(cudaLaunchConfig_t& cfg, bool pdl, cudaLaunchAttribute* attr) {
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  return cudaSuccess;
+}
+
+int launch_expand(const GemmArgs& a, void* XE, float* sumxf, DeviceInfo* dev) {
+  using namespace w4a4;
+  ExpandParams e;
+  e.X_s4 = static_cast<const int8_t*>(a.X_s4);
+  e.sum_X = a.sum_X;
+  e.XE = static_cast<int8_t*>(XE);
+  e.sumxf = sumxf;
+  e.T = a.T;
+  e.K = a.K;
+  const long long words = (long long)a.T * (a.K / 8);
+  long long blocks = (words + 255) / 256;
+  if (blocks > 4LL * dev->sm_count) blocks = 4LL * dev->sm_count;
+  expand_activations_kernel<<<(int)blocks, 256, 0, a.stream>>>(e);
+  cudaError_t err = cudaGetLastError();
+  if (err != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "expand kernel launch: %s", cudaGetErrorString(err));
+  return W4A4_OK;
+}
+
 int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   using namespace w4a4;
   const bool dump = a.acc_dump || a.acc_hi_dump;
-  DecodePlan plan = plan_decode(a.T, a.K, a.N, dev->sm_count, !dump);
-  const WsLayout wl = ws_layout(a.T, a.K);
-  if (plan.split_k > 1 && (a.ws == nullptr || a.ws_bytes < wl.x_s4))
-    return fail(W4A4_ERR_WORKSPACE, "split-K needs a workspace of at least %zu bytes", wl.x_s4);
-
-  CUtensorMap tm_low, tm_high;
   const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
   if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
+  const int ng = a.K / BCOL;
+  const int row_tiles = (a.N + dec::ROWS - 1) / dec::ROWS;
+  if (row_tiles > dec::MAX_ROW_TILES_SMEM)
+    return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d exceeds %d rows", a.N, dec::MAX_ROW_TILES_SMEM * dec::ROWS);
+  const long long steps_total = (long long)row_tiles * (a.do_dense ? ng : 0) + (has_sparse ? a.nnz : 0);
+  DecodePlan plan = plan_decode(a.T, a.K, a.N, steps_total, dev->sm_count);
+  const WsLayout wl = ws_layout(a.T, a.K);
+  if (a.ws == nullptr || a.ws_bytes < wl.total)
+    return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, a.ws_bytes);
+  char* ws = static_cast<char*>(a.ws);
+
+  // expanded activations: given by the caller, or built here from the packed codes
+  const void* XE = a.XE;
+  const float* sumxf = a.sumxf;
+  bool pdl = a.pdl;
+  if (XE == nullptr) {
+    int rc = launch_expand(a, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf), dev);
+    if (rc) return rc;
+    XE = ws + wl.xe;
+    sumxf = a.sum_X ? reinterpret_cast<float*>(ws + wl.sumxf) : nullptr;
+    pdl = true;
+  }
+  if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
+
+  const bool nt2 = a.T > 8;
+  CUtensorMap tm_low, tm_high, tm_x;
   // the operand that is switched off borrows the other one's map and is never read
   int rc = make_map(&tm_low, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
                     a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, dec::ROWS,
@@ -180,14 +231,15 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   rc = make_map(&tm_high, has_sparse ? a.W_high : a.W_low, has_sparse ? 64 : (uint64_t)a.K / 2,
                 has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, dec::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
+  rc = make_map(&tm_x, XE, (uint64_t)a.K, (uint64_t)a.T, BCOL, nt2 ? 16 : 8, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (rc) return rc;
 
   dec::Params p;
   p.hp_row_offsets = a.hp_row_offsets;
   p.hp_col_indices = a.hp_col_indices;
-  p.X_s4 = static_cast<const int8_t*>(a.X_s4);
   p.scale_u4 = static_cast<const __half*>(a.scale_u4);
   p.zero_u4 = static_cast<const __half*>(a.zero_u4);
-  p.sum_X = a.sum_X;
+  p.sumxf = a.do_dense ? sumxf : nullptr;
   p.scale_x = static_cast<const __half*>(a.scale_x);
   p.Y = static_cast<__half*>(a.Y);
   if (a.flags & W4A4_FLAG_OUT_TOKEN_MAJOR) {
@@ -197,20 +249,20 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
     p.y_stride_n = a.T;
     p.y_stride_t = 1;
   }
-  p.partial = a.ws ? reinterpret_cast<float*>(static_cast<char*>(a.ws) + wl.partial) : nullptr;
-  p.counters = a.ws ? reinterpret_cast<int*>(static_cast<char*>(a.ws) + wl.counters) : nullptr;
+  p.partial = reinterpret_cast<float*>(ws + wl.partial);
+  p.counters = reinterpret_cast<int*>(ws + wl.counters);
   p.acc_dump = a.acc_dump;
   p.acc_hi_dump = a.acc_hi_dump;
-  p.T = a.T; p.K = a.K; p.N = a.N; p.ng = a.K / BCOL; p.nnz = has_sparse ? a.nnz : 0;
-  p.S = plan.S;
-  p.split_k = plan.split_k;
-  p.slices_per_cta = plan.slices_per_cta;
-  p.do_dense = a.do_dense ? 1 : 0;
+  p.T = a.T; p.K = a.K; p.N = a.N; p.ng = ng; p.nnz = has_sparse ? a.nnz : 0;
+  p.row_tiles = row_tiles;
+  p.nd = a.do_dense ? ng : 0;
+  p.sparse_on = has_sparse ? 1 : 0;
+  p.steps_total = (int)steps_total;
+  p.steps_per_cta = plan.steps_per_cta;
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
 
-  const size_t smem = dec::smem_bytes(plan.S);
-  const bool nt2 = a.T > 8;
-  void (*kern)(const CUtensorMap, const CUtensorMap, const dec::Params) =
+  const size_t smem = dec::smem_bytes();
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const dec::Params) =
       dump ? (nt2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
            : (nt2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -218,22 +270,19 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
 
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
-  cfg.gridDim = dim3(plan.row_tiles, plan.split_k, plan.tok_tiles);
+  cfg.gridDim = dim3(plan.ctas, plan.tok_tiles, 1);
   cfg.blockDim = dim3(dec::THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = a.pdl ? 1 : 0;
-  e = cudaLaunchKernelEx(&cfg, kern, tm_low, tm_high, p);
+  launch_pdl(cfg, pdl, attr);
+  e = cudaLaunchKernelEx(&cfg, kern, tm_low, tm_high, tm_x, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }
 
 int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x, int32_t* sum_X,
-                 void* X_s8, int T, int K, cudaStream_t stream) {
+                 void* XE, float* sumxf, int T, int K, cudaStream_t stream) {
   using namespace w4a4;
   QuantParams q;
   q.X = static_cast<const __half*>(X);
@@ -242,7 +291,8 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   q.X_s4 = static_cast<int8_t*>(X_s4);
   q.scale_x = static_cast<__half*>(scale_x);
   q.sum_X = sum_X;
-  q.X_s8 = static_cast<int8_t*>(X_s8);
+  q.XE = static_cast<int8_t*>(XE);
+  q.sumxf = sumxf;
   q.T = T;
   q.K = K;
   q.vec_ok = (aligned(X, 16) && (ldx % 8 == 0)) ? 1 : 0;
@@ -270,13 +320,14 @@ int check_common(int T, int K, int N, int nnz) {
 int run_gemm(GemmArgs& a) {
   int rc = check_common(a.T, a.K, a.N, a.nnz);
   if (rc) return rc;
-  CHECK_ARG(a.X_s4 != nullptr, "X_s4 is NULL");
+  CHECK_ARG(a.X_s4 != nullptr || a.XE != nullptr, "X_s4 is NULL");
   CHECK_ARG(a.scale_u4 != nullptr || (a.acc_dump || a.acc_hi_dump), "scale_u4 is NULL");
   CHECK_ARG(!a.do_dense || a.W_low != nullptr, "W_low is NULL");
   CHECK_ARG(a.nnz == 0 || (a.W_high && a.hp_row_offsets && a.hp_col_indices), "residual arrays are NULL with nnz=%d", a.nnz);
   if (!aligned(a.W_low, 16) || !aligned(a.W_high, 16))
     return fail(W4A4_ERR_ALIGNMENT, "weight pointers must be 16-byte aligned");
   if (!aligned(a.X_s4, 4)) return fail(W4A4_ERR_ALIGNMENT, "X_s4 must be 4-byte aligned");
+  if ((long long)a.T > 16LL * 65535) return fail(W4A4_ERR_UNSUPPORTED, "T=%d exceeds the grid limit", a.T);
   DeviceInfo* dev = nullptr;
   rc = current_device(&dev);
   if (rc) return rc;
@@ -334,7 +385,7 @@ int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, voi
   CHECK_ARG(ldx >= K, "ldx (%lld) must be >= K (%d)", ldx, K);
   if (!aligned(X, 2) || !aligned(X_s4, 4) || !aligned(sum_X, 4) || !aligned(scale_x, 2))
     return fail(W4A4_ERR_ALIGNMENT, "activation_quant pointer alignment");
-  return launch_quant(X, ldx, perm, X_s4, scale_x, sum_X, nullptr, T, K, static_cast<cudaStream_t>(stream));
+  return launch_quant(X, ldx, perm, X_s4, scale_x, sum_X, nullptr, nullptr, T, K, static_cast<cudaStream_t>(stream));
 }
 
 size_t w4a4_workspace_bytes(int T, int K, int N, int nnz) {
@@ -367,6 +418,41 @@ int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t
   return run_gemm(a);
 }
 
+size_t w4a4_expanded_codes_bytes(int T, int K) { return (T < 1 || K < 128) ? 0 : (size_t)T * K; }
+size_t w4a4_expanded_sums_bytes(int T, int K) {
+  return (T < 1 || K < 128) ? 0 : (size_t)((T + 15) / 16) * (K / 128) * 16 * 4;
+}
+
+int w4a4_expand_activations(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
+                            void* stream) {
+  int rc = check_common(T, K, 1, 0);
+  if (rc) return rc;
+  CHECK_ARG(X_s4 && XE && (sum_X == nullptr || sumxf != nullptr), "NULL tensor pointer");
+  if (!aligned(X_s4, 4) || !aligned(XE, 16) || !aligned(sumxf, 16))
+    return fail(W4A4_ERR_ALIGNMENT, "expand_activations pointer alignment");
+  DeviceInfo* dev = nullptr;
+  rc = current_device(&dev);
+  if (rc) return rc;
+  GemmArgs a{};
+  a.X_s4 = X_s4; a.sum_X = sum_X; a.T = T; a.K = K; a.stream = static_cast<cudaStream_t>(stream);
+  return launch_expand(a, XE, sumxf, dev);
+}
+
+int w4a4_fused_dense_sparse_expanded(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                                     const int32_t* hp_col_indices, const void* XE, const float* sumxf,
+                                     const void* scale_u4, const void* zero_u4, const void* scale_x, void* Y, int T,
+                                     int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes,
+                                     void* stream) {
+  CHECK_ARG(Y && zero_u4 && XE && sumxf && scale_x, "NULL tensor pointer");
+  GemmArgs a{};
+  a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
+  a.XE = XE; a.sumxf = sumxf; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.scale_x = scale_x; a.Y = Y;
+  a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
+  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = false;
+  a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
+  return run_gemm(a);
+}
+
 int w4a4_dense_gemm(const void* W_low, const void* X_s4, const void* scale_u4, const void* zero_u4,
                     const int32_t* sum_X, const void* scale_x, void* Y_low, int T, int K, int N, int flags,
                     void* workspace, size_t workspace_bytes, void* stream) {
@@ -384,12 +470,14 @@ int w4a4_sparse_gemm(const void* W_high, const int32_t* hp_row_offsets, const in
                      const void* X_s4, const void* scale_u4, const void* scale_x, void* Y_high, int T, int K, int N,
                      int nnz, int flags, void* workspace, size_t workspace_bytes, void* stream) {
   CHECK_ARG(Y_high && scale_x, "NULL tensor pointer");
-  if (nnz == 0) {   // empty block-CSR: the product is zero (reference: cuda_kernel/ops.py:367-369)
+  {
+    // block-rows without blocks are never visited by the kernel: they are zero
+    // (an empty block-CSR gives an all-zero product, cuda_kernel/ops.py:367-369)
     int rc0 = check_common(T, K, N, nnz);
     if (rc0) return rc0;
     cudaError_t e = cudaMemsetAsync(Y_high, 0, (size_t)N * T * 2, static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
-    return W4A4_OK;
+    if (nnz == 0) return W4A4_OK;
   }
   GemmArgs a{};
   a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
@@ -413,13 +501,13 @@ int w4a4_fused_quant_dense_sparse(const void* X, long long ldx, const int32_t* p
     return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, workspace_bytes);
   char* ws = static_cast<char*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  rc = launch_quant(X, ldx, perm, ws + wl.x_s4, ws + wl.scale_x, reinterpret_cast<int32_t*>(ws + wl.sum_x), nullptr,
+  rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
                     T, K, s);
   if (rc) return rc;
   GemmArgs a{};
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
-  a.X_s4 = ws + wl.x_s4; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4;
-  a.sum_X = reinterpret_cast<int32_t*>(ws + wl.sum_x); a.scale_x = ws + wl.scale_x; a.Y = Y;
+  a.XE = ws + wl.xe; a.sumxf = reinterpret_cast<float*>(ws + wl.sumxf); a.scale_u4 = scale_u4; a.zero_u4 = zero_u4;
+  a.scale_x = ws + wl.scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
   a.do_dense = true; a.sparse_weight = 16.f; a.pdl = true;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = s;

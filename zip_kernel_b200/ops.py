@@ -231,6 +231,53 @@ def fused_dense_sparse_cuda_int4(
     return Y
 
 
+def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor):
+    """Quantised activations in the layout the GEMM kernels read: returns
+    ``(XE (T, K) int8, sumxf (ceil(T/16), K/128, 16) fp32)``.  Build once and reuse
+    across the linears that share an input (no counterpart in the reference)."""
+    assert X_s4.is_cuda and X_s4.dtype == torch.int8 and sum_X.dtype == torch.int32
+    T, K = int(X_s4.shape[0]), int(X_s4.shape[1]) * 2
+    X = X_s4.contiguous()
+    sm = sum_X.contiguous()
+    XE = torch.empty((T, K), dtype=torch.int8, device=X.device)
+    sumxf = torch.zeros(((T + 15) // 16, K // BCOL, 16), dtype=torch.float32, device=X.device)
+    with torch.cuda.device(X.device):
+        _lib.check(_L.w4a4_expand_activations(X.data_ptr(), sm.data_ptr(), XE.data_ptr(), sumxf.data_ptr(),
+                                              T, K, _lib.stream_ptr(X.device)), "expand_activations")
+    return XE, sumxf
+
+
+def fused_dense_sparse_expanded_cuda(
+    W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
+    XE, sumxf, scale_u4, zero_u4, scale_x, d_out, d_in,
+    *, token_major: bool = False, force: Optional[str] = None,
+) -> torch.Tensor:
+    """:func:`fused_dense_sparse_cuda_int4` on activations already expanded by
+    :func:`expand_activations_cuda`; a single kernel launch."""
+    d_out, d_in = int(d_out), int(d_in)
+    T = int(XE.shape[0])
+    assert XE.is_cuda and XE.dtype == torch.int8 and XE.shape == (T, d_in) and XE.is_contiguous()
+    assert sumxf.dtype == torch.float32 and sumxf.is_contiguous()
+    W = W_low_packed.contiguous()
+    nnz = int(W_high_blocks_packed.shape[0]) if W_high_blocks_packed.numel() else 0
+    Wh = W_high_blocks_packed.contiguous()
+    ro = hp_row_offsets.contiguous().to(torch.int32)
+    ci = hp_col_indices.contiguous().to(torch.int32)
+    _check_bsr(ro, ci, d_out, d_in, nnz)
+    s = scale_u4.contiguous().to(torch.float16)
+    z = zero_u4.contiguous().to(torch.float16)
+    sx = scale_x.contiguous().to(torch.float16)
+    Y = _out(d_out, T, W.device, token_major)
+    with torch.cuda.device(W.device):
+        ws = _lib.workspace(W.device, T, d_in, d_out, nnz)
+        _lib.check(_L.w4a4_fused_dense_sparse_expanded(
+            W.data_ptr(), Wh.data_ptr() if nnz else None, ro.data_ptr(), ci.data_ptr() if nnz else None,
+            XE.data_ptr(), sumxf.data_ptr(), s.data_ptr(), z.data_ptr(), sx.data_ptr(), Y.data_ptr(),
+            T, d_in, d_out, nnz, _flags(token_major, force), ws.data_ptr(), ws.numel(),
+            _lib.stream_ptr(W.device)), "fused_dense_sparse_expanded")
+    return Y
+
+
 fused_gemv_cuda_decode = fused_dense_sparse_cuda_int4
 fused_gemv_cuda_smallT = fused_dense_sparse_cuda_int4
 fused_dense_sparse_cuda = fused_dense_sparse_cuda_int4
@@ -354,4 +401,6 @@ __all__ = [
     "fused_dense_sparse_e2e_cuda",
     "dump_accumulators",
     "reserve_workspace",
+    "expand_activations_cuda",
+    "fused_dense_sparse_expanded_cuda",
 ]

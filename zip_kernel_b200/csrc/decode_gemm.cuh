@@ -7,11 +7,12 @@
 //   Y[n,t] = fp16( sx[t] * ( sum_g s[n,g] * (acc[g,n,t] - z[n,g] * sumX[t,g])
 //                            + w * sum_{blk in block-row} s[n,bc] * acc_hi[blk,n,t] ) )
 //
-// Work decomposition.  One "step" is a 128-row x 128-column tile of packed
-// nibbles (8 KB): a group of the dense weights of one block-row, or one residual
-// block.  All steps of the layer form one line, block-row after block-row, dense
-// groups first and the row's residual blocks behind them:
-//   first_step(r) = r * ng + hp_row_offsets[r].
+// Work decomposition.  One "step" is a tile of packed nibbles of one block-row
+// (128 rows): two adjacent groups of the dense weights (128 x 128 bytes = 16 KB,
+// so every TMA row is a full 128-byte line), or one residual block (8 KB,
+// contiguous).  All steps of the layer form one line, block-row after
+// block-row, dense pairs first and the row's residual blocks behind them:
+//   first_step(r) = r * ceil(ng / 2) + hp_row_offsets[r].
 // The line is cut into equal contiguous ranges, one per CTA, so every CTA
 // streams the same number of bytes however N, K and the residual mask fall
 // relative to the SM count.  A CTA that owns a whole block-row writes it out
@@ -20,16 +21,19 @@
 // applies scale_x and writes fp16.  Nothing ever waits for another CTA.
 //
 // Data flow per CTA.  A producer warp walks the range and, per step, issues
-// three non-multicast asynchronous copies into one slot of an 8-deep
-// shared-memory ring guarded by mbarriers: the weight tile (TMA, 8 KB), the
-// matching 128-byte slice of the expanded activation codes of up to 16 tokens
-// (TMA, 128-byte swizzle so fragment reads are conflict-free) and the 16 group
-// sums (bulk copy).  Eight consumer warps (16 rows each) read their fragments
-// with 128-bit loads, expand nibbles to s8 lanes scaled by 16 with three logic
-// ops per word, run mma.sync m16n8k32 s8 (element order inside a group is
-// permuted identically on both operands), and fold each group's int32
-// accumulator in fp32 with the group's scale and zero, which every thread
-// fetches with plain loads issued ahead of the slot wait.
+// non-multicast asynchronous copies into one slot of a 4-deep shared-memory
+// ring guarded by mbarriers: the weight tile (TMA, or a plain bulk copy for a
+// residual block), the matching 128-byte slices of the expanded activation codes
+// of up to 16 tokens (TMA, 128-byte swizzle so fragment reads are conflict-free)
+// and the group sums (bulk copy).  Eight consumer warps (16 rows each) read
+// their fragments with 128-bit loads, expand nibbles to s8 lanes scaled by 16
+// with three logic ops per word, run mma.sync m16n8k32 s8 on the two groups as
+// independent chains (element order inside a group is permuted identically on
+// both operands), and fold each group's int32 accumulator in fp32 with the
+// group's scale and zero using packed f32x2 FMAs.  Scales and zeros of the
+// CTA's 128 rows are staged in shared memory 16 groups at a time with 128-bit
+// loads that are issued one span ahead and parked in registers, so the loop
+// never waits on a scattered 2-byte load.
 #pragma once
 
 #include <cuda.h>
@@ -43,19 +47,23 @@ constexpr int ROWS = 128;
 constexpr int CONSUMER_WARPS = 8;
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
-constexpr int STAGES = 8;
+constexpr int STAGES = 4;
 constexpr int TOK = 16;                           // tokens per CTA pass
-constexpr int W_TILE_BYTES = ROWS * GROUP_BYTES;  // 8192
-constexpr int X_TILE_BYTES = TOK * BCOL;          // 2048 (16 tokens x 128 codes)
-constexpr int SUMX_BYTES = TOK * 4;               // 64
-constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES + 1024;
-constexpr int MAX_ROW_TILES_SMEM = 2048;          // block-row offsets cached in shared memory
+constexpr int W_TILE_BYTES = ROWS * 2 * GROUP_BYTES;   // 16384: 128 rows x two groups
+constexpr int BLK_BYTES = BROW * GROUP_BYTES;     // 8192: one residual block
+constexpr int X_TILE_BYTES = TOK * BCOL;          // 2048 (16 tokens x 128 codes) per group
+constexpr int SUMX_BYTES = TOK * 4;               // 64 per group
+constexpr int STAGE_BYTES = W_TILE_BYTES + 2 * X_TILE_BYTES;   // group sums live in a ring of their own
+constexpr int MAX_ROW_TILES_SMEM = 1024;          // block-row offsets cached in shared memory
+constexpr int SZ_CHUNK = 16;                      // groups of scale/zero staged per span
+constexpr int SZ_BYTES = SZ_CHUNK * ROWS * 8;     // float2 (scale/16, scale*zero) per (group, row)
 
 enum : int { SITE_DEC_FULL = 1, SITE_DEC_EMPTY = 2, SITE_DEC_DRAIN = 3, SITE_DEC_DUMP = 4 };
 
 struct Params {
   const int* hp_row_offsets;
   const int* hp_col_indices;
+  const int8_t* W_high;     // (nnz, 128, 64) residual blocks
   const __half* scale_u4;   // (N, ng)
   const __half* zero_u4;    // (N, ng) or nullptr
   const float* sumxf;       // [tok tiles][ng][16] or nullptr
@@ -68,23 +76,80 @@ struct Params {
   int* acc_hi_dump;         // optional (nnz, 128, T) int32
   int T, K, N, ng, nnz;
   int row_tiles;
-  int nd;                   // dense steps per block-row (ng, or 0 when the dense part is off)
+  int nd;                   // dense steps per block-row (ceil(ng/2), or 0 when the dense part is off)
   int sparse_on;
+  int sz_vec;               // scale/zero rows may be read with 128-bit loads
   int steps_total;
   int steps_per_cta;        // 0: one whole block-row per CTA (no shared rows, no workspace)
   float sparse_weight;      // 16 (fused) or 1 (sparse-only op)
 };
 
-inline size_t smem_bytes() { return 1024 + (size_t)STAGES * STAGE_BYTES + (MAX_ROW_TILES_SMEM + 1) * 4 + 256; }
+inline size_t smem_bytes() {
+  return 1024 + (size_t)STAGES * STAGE_BYTES + STAGES * 2 * SUMX_BYTES + SZ_BYTES + (MAX_ROW_TILES_SMEM + 2) * 4 + 256;
+}
+
+// d = a * b + c on two packed fp32 lanes
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
+
+// D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col) with a zero accumulator input
+__device__ __forceinline__ void mma_m16n8k32_s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                                      uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+
+// One group of one warp: 16 rows x 128 codes against NT*8 tokens.
+template <int NT>
+__device__ __forceinline__ void group_mma(int (&acc)[NT][4], const uint4& wa, const uint4& wb, const uint4 (&q0)[NT],
+                                          const uint4 (&q1)[NT]) {
+  const uint32_t wa_[4] = {wa.x, wa.y, wa.z, wa.w};
+  const uint32_t wb_[4] = {wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+  for (int jj = 0; jj < 4; ++jj) {
+    const uint32_t a0 = nib_lo_x16(wa_[jj]), a1 = nib_lo_x16(wb_[jj]);
+    const uint32_t a2 = nib_hi_x16(wa_[jj]), a3 = nib_hi_x16(wb_[jj]);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const uint32_t b0_[4] = {q0[nt].x, q0[nt].z, q1[nt].x, q1[nt].z};
+      const uint32_t b1_[4] = {q0[nt].y, q0[nt].w, q1[nt].y, q1[nt].w};
+      if (jj == 0) mma_m16n8k32_s8_first(acc[nt], a0, a1, a2, a3, b0_[jj], b1_[jj]);
+      else         mma_m16n8k32_s8(acc[nt], a0, a1, a2, a3, b0_[jj], b1_[jj]);
+    }
+  }
+}
+
+// y += acc * f - c * sumx   for the thread's two rows (a: acc[0..1], b: acc[2..3])
+template <int NT>
+__device__ __forceinline__ void group_fold(float2 (&y)[NT][2], const int (&acc)[NT][4], float fa, float fb, float ca,
+                                           float cb, const float2 (&sx)[NT]) {
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) {
+    const float2 ta = fma2(make_float2(-ca, -ca), sx[nt], y[nt][0]);
+    const float2 tb = fma2(make_float2(-cb, -cb), sx[nt], y[nt][1]);
+    y[nt][0] = fma2(make_float2(__int2float_rn(acc[nt][0]), __int2float_rn(acc[nt][1])), make_float2(fa, fa), ta);
+    y[nt][1] = fma2(make_float2(__int2float_rn(acc[nt][2]), __int2float_rn(acc[nt][3])), make_float2(fb, fb), tb);
+  }
+}
 
 template <int NT, bool DUMP>
 __global__ void __launch_bounds__(THREADS, 2)
-decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_constant__ CUtensorMap tm_high,
-                   const __grid_constant__ CUtensorMap tm_x, const Params p) {
+decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_constant__ CUtensorMap tm_x2,
+                   const __grid_constant__ CUtensorMap tm_x1, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* stage_buf = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  int* row_off = reinterpret_cast<int*>(stage_buf + STAGES * STAGE_BYTES);      // first_step(r), r = 0..row_tiles
+  unsigned char* sumx_ring = stage_buf + STAGES * STAGE_BYTES;
+  float2* szs = reinterpret_cast<float2*>(sumx_ring + STAGES * 2 * SUMX_BYTES);   // [16 groups][128 rows] (s/16, s*z)
+  int* row_off = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(szs) + SZ_BYTES);   // first_step(r)
   uint64_t* full = reinterpret_cast<uint64_t*>(row_off + MAX_ROW_TILES_SMEM + 2);
   uint64_t* empty = full + STAGES;
   int* misc = reinterpret_cast<int*>(empty + STAGES);     // [0] = last-arriver flag, [1] = a wait gave up
@@ -96,6 +161,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
   const int tt = blockIdx.y;
   const int tok0 = tt * TOK;
   const int L = p.steps_per_cta;
+  constexpr int XG_BYTES = NT * 8 * BCOL;     // activation bytes actually copied per group
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -106,8 +172,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
     misc[0] = 0;
     misc[1] = 0;
     tma_prefetch_desc(&tm_low);
-    tma_prefetch_desc(&tm_high);
-    tma_prefetch_desc(&tm_x);
+    tma_prefetch_desc(&tm_x2);
+    tma_prefetch_desc(&tm_x1);
   }
   // first_step(r) for every block-row (weights only: valid before the dependency wait)
   for (int r = tid; r <= p.row_tiles; r += THREADS)
@@ -131,59 +197,65 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
     // ------------------------------------------------------------ producer
     if (lane == 0 && lo < hi) {
       const bool with_sums = p.sumxf != nullptr;
+      const float* sums_base = with_sums ? p.sumxf + (size_t)tt * p.ng * TOK : nullptr;
       bool ok = true;
-      int issued = 0;
-      // Step `pos` of block-row r -> the slot's three copies.  The weight tile does
-      // not depend on the preceding kernel in the stream, the other two do.
-      auto issue = [&](int pos, int r, int n, bool weights, bool acts) {
-        const int st = n % STAGES;
+      // Per step: the weight tile does not depend on the preceding kernel in the
+      // stream, the activation copies do.  Dense step j of block-row r covers
+      // groups 2j and 2j+1; a residual step covers one block.
+      auto issue_w = [&](int j, int r, int st) {
         unsigned char* slot = stage_buf + st * STAGE_BYTES;
-        const int j = pos - row_off[r];
-        const bool dense = j < p.nd;
-        int blk = 0, g = j;
-        if (!dense) {
-          blk = ld_plain(p.hp_row_offsets + r) + j - p.nd;
-          g = ld_plain(p.hp_col_indices + blk);
+        if (j < p.nd) {
+          const int n_sum = with_sums ? ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES : 0;
+          mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + 2 * XG_BYTES + n_sum);
+          tma_load_2d(slot, &tm_low, 2 * j * GROUP_BYTES, r * ROWS, &full[st]);
+        } else {
+          const int blk = ld_plain(p.hp_row_offsets + r) + j - p.nd;
+          mbar_arrive_expect_tx(&full[st], BLK_BYTES + XG_BYTES);
+          bulk_load_1d(slot, p.W_high + (size_t)blk * BLK_BYTES, BLK_BYTES, &full[st]);
         }
-        if (weights) {
-          const uint32_t bytes = W_TILE_BYTES + NT * 8 * BCOL + ((dense && with_sums) ? SUMX_BYTES : 0);
-          mbar_arrive_expect_tx(&full[st], bytes);
-          if (dense) tma_load_2d(slot, &tm_low, g * GROUP_BYTES, r * ROWS, &full[st]);
-          else       tma_load_2d(slot, &tm_high, 0, blk * BROW, &full[st]);
-        }
-        if (acts) {
-          tma_load_2d(slot + W_TILE_BYTES, &tm_x, g * BCOL, tok0, &full[st]);
-          if (dense && with_sums)
-            bulk_load_1d(slot + W_TILE_BYTES + X_TILE_BYTES, p.sumxf + ((size_t)tt * p.ng + g) * TOK, SUMX_BYTES,
-                         &full[st]);
+      };
+      auto issue_x = [&](int j, int r, int st) {
+        unsigned char* slot = stage_buf + st * STAGE_BYTES + W_TILE_BYTES;
+        if (j < p.nd) {
+          tma_load_3d(slot, &tm_x2, 0, 2 * j, tok0, &full[st]);
+          if (with_sums)
+            bulk_load_1d(sumx_ring + st * 2 * SUMX_BYTES, sums_base + 2 * j * TOK,
+                         ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES, &full[st]);
+        } else {
+          const int blk = ld_plain(p.hp_row_offsets + r) + j - p.nd;
+          tma_load_3d(slot, &tm_x1, 0, ld_plain(p.hp_col_indices + blk), tok0, &full[st]);
         }
       };
       // ring fill: weight tiles first, then wait for the activations' producer kernel
       const int n_pre = min(STAGES, hi - lo);
       {
-        int r = r_first;
+        int r = r_first, row_hi = row_off[r + 1];
         for (int n = 0; n < n_pre; ++n) {
           const int pos = lo + n;
-          while (pos >= row_off[r + 1]) ++r;
-          issue(pos, r, n, true, false);
+          while (pos >= row_hi) row_hi = row_off[++r + 1];
+          issue_w(pos - row_off[r], r, n);
         }
       }
       grid_dependency_wait();
-      int r = r_first;
-      for (int pos = lo; pos < hi; ++pos, ++issued) {
-        while (pos >= row_off[r + 1]) ++r;
-        if (issued < n_pre) {
-          issue(pos, r, issued, false, true);
-        } else {
-          ok = mbar_wait(&empty[issued % STAGES], ((issued / STAGES) & 1) ^ 1, SITE_DEC_EMPTY);
+      int r = r_first, row_lo = row_off[r], row_hi = row_off[r + 1];
+      int st = 0;
+      uint32_t ph = 1;                     // parity the empty barrier is waited on
+      int n = 0;
+      for (int pos = lo; pos < hi; ++pos, ++n) {
+        while (pos >= row_hi) { ++r; row_lo = row_hi; row_hi = row_off[r + 1]; }
+        const int j = pos - row_lo;
+        if (n >= n_pre) {
+          ok = mbar_wait(&empty[st], ph, SITE_DEC_EMPTY);
           if (!ok) break;
-          issue(pos, r, issued, true, true);
+          issue_w(j, r, st);
         }
+        issue_x(j, r, st);
+        if (++st == STAGES) { st = 0; ph ^= 1; }
       }
       if (!ok) {
         misc[1] = 1;
         // let copies already in flight land before the CTA may retire
-        for (int i = max(0, issued - STAGES); i < issued; ++i)
+        for (int i = max(0, n - STAGES); i < n; ++i)
           mbar_wait(&full[i % STAGES], (i / STAGES) & 1, SITE_DEC_DRAIN);
       }
     }
@@ -195,113 +267,235 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
     const int r_b = r_a + 8;
     grid_dependency_wait();               // scale_x, and the workspace of earlier launches
 
-    float y[NT][4];
+    // Per-thread constant offsets inside a slot.  The activation tile is a stack
+    // of 128-byte lines under the 128-byte swizzle (16-byte chunk index XOR line
+    // index mod 8): a dense step holds line 2*token + h for group h, a residual
+    // step line = token.
+    int xd0[2][NT], xd1[2][NT], xs0[NT], xs1[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int xr = nt * 8 + gid;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int line = 2 * xr + h;
+        xd0[h][nt] = W_TILE_BYTES + line * BCOL + (((2 * tig) ^ (line & 7)) << 4);
+        xd1[h][nt] = W_TILE_BYTES + line * BCOL + (((2 * tig + 1) ^ (line & 7)) << 4);
+      }
+      xs0[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig) ^ (xr & 7)) << 4);
+      xs1[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig + 1) ^ (xr & 7)) << 4);
+    }
+
+    float2 y[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = make_float2(0.f, 0.f);
     bool ok = true;
     int consumed = 0;
-    int pos = lo;
+
+    // The CTA's range is walked in spans: a run of dense steps of one block-row
+    // that lies inside one aligned window of 32 groups, or the residual blocks of
+    // a block-row.  `walk` yields the next span and advances (r, pos).
+    struct Span { int r, j0, j1, dense; };
+    auto walk = [&](int& r, int& pos, Span& sp) -> bool {
+      while (pos < hi) {
+        const int row_lo = row_off[r], row_hi = row_off[r + 1];
+        if (pos >= row_hi) { ++r; continue; }
+        const int j = pos - row_lo;
+        const int seg_end = min(hi, row_hi) - row_lo;
+        if (j < p.nd) {
+          sp.j1 = min(min(seg_end, p.nd), (j / (SZ_CHUNK / 2) + 1) * (SZ_CHUNK / 2));
+          sp.dense = 1;
+        } else {
+          sp.j1 = seg_end;
+          sp.dense = 0;
+        }
+        sp.r = r;
+        sp.j0 = j;
+        pos = row_lo + sp.j1;
+        return true;
+      }
+      return false;
+    };
+    // Scale/zero window of a dense span: thread t fetches 8 groups of row t/2
+    // (one 128-bit load from each array when rows are 16-byte aligned) and parks
+    // them as (scale/16, scale*zero): the accumulators carry a factor 16 from the
+    // weight expansion.
+    const int lrow = tid >> 1, lhalf = tid & 1;
+    uint4 ps, pz;
+    auto fetch_sz = [&](const Span& sp) {
+      ps = pz = make_uint4(0, 0, 0, 0);
+      if (!sp.dense || p.scale_u4 == nullptr) return;
+      const int row = sp.r * ROWS + lrow;
+      if (row >= p.N) return;
+      const int g = (2 * sp.j0 / SZ_CHUNK) * SZ_CHUNK + lhalf * 8;
+      if (g >= p.ng) return;
+      const __half* srow = p.scale_u4 + (size_t)row * p.ng;
+      const __half* zrow = p.zero_u4 ? p.zero_u4 + (size_t)row * p.ng : nullptr;
+      if (p.sz_vec) {
+        ps = *reinterpret_cast<const uint4*>(srow + g);
+        if (zrow) pz = *reinterpret_cast<const uint4*>(zrow + g);
+      } else {
+        __half hs[8], hz[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          hs[i] = (g + i < p.ng) ? srow[g + i] : __float2half(0.f);
+          hz[i] = (g + i < p.ng && zrow) ? zrow[g + i] : __float2half(0.f);
+        }
+        ps = *reinterpret_cast<uint4*>(&hs[0]);
+        pz = *reinterpret_cast<uint4*>(&hz[0]);
+      }
+    };
+    auto park_sz = [&]() {
+      const __half2* hs = reinterpret_cast<const __half2*>(&ps);
+      const __half2* hz = reinterpret_cast<const __half2*>(&pz);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
+        szs[(lhalf * 8 + 2 * i) * ROWS + lrow] = make_float2(s2.x * 0.0625f, s2.x * z2.x);
+        szs[(lhalf * 8 + 2 * i + 1) * ROWS + lrow] = make_float2(s2.y * 0.0625f, s2.y * z2.y);
+      }
+    };
+
+    int r_w = r_first, pos_w = lo;
+    Span cur, nxt;
+    bool have = walk(r_w, pos_w, cur);
+    if (have) fetch_sz(cur);
+    int prev_r = -1;
     // A wait that gives up clears `ok` for the whole warp; the loops still run to
     // their end (skipping the work) so that every named barrier below is reached.
-    for (int r = r_first; pos < hi; ++r) {
+    while (have) {
+      const bool have_next = walk(r_w, pos_w, nxt);
+      asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");   // previous span's window is free
+      if (cur.dense) park_sz();
+      if (have_next) fetch_sz(nxt);
+      asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
+
+      const int r = cur.r;
       const int row_lo = row_off[r], row_hi = row_off[r + 1];
-      const int seg_hi = min(hi, row_hi);
-      if (seg_hi <= pos) continue;        // block-row without steps
       const int row0 = r * ROWS;
-      const int blk0 = p.sparse_on ? ld_plain(p.hp_row_offsets + r) : 0;
-      const size_t sz_a = (size_t)(row0 + r_a) * p.ng, sz_b = (size_t)(row0 + r_b) * p.ng;
-      const bool live_a = row0 + r_a < p.N && p.scale_u4 != nullptr;
-      const bool live_b = row0 + r_b < p.N && p.scale_u4 != nullptr;
+      if (r != prev_r) {      // first span of a block-row in this CTA
+        prev_r = r;
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) y[nt][i] = 0.f;
+        for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = make_float2(0.f, 0.f);
+      }
 
-      for (; pos < seg_hi; ++pos, ++consumed) {
-        const int j = pos - row_lo;
-        const bool is_dense = j < p.nd;
-        const int blk = blk0 + j - p.nd;
-        const int g = is_dense ? j : ld_plain(p.hp_col_indices + blk);
-        // group scale / zero of this thread's two rows, requested ahead of the slot wait
-        float s_a = 0.f, s_b = 0.f, z_a = 0.f, z_b = 0.f;
-        if (live_a) {
-          s_a = __half2float(ld_plain(p.scale_u4 + sz_a + g));
-          if (is_dense && p.zero_u4) z_a = __half2float(ld_plain(p.zero_u4 + sz_a + g));
-        }
-        if (live_b) {
-          s_b = __half2float(ld_plain(p.scale_u4 + sz_b + g));
-          if (is_dense && p.zero_u4) z_b = __half2float(ld_plain(p.zero_u4 + sz_b + g));
-        }
-        const int st = consumed % STAGES;
-        if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (consumed / STAGES) & 1, SITE_DEC_FULL));
-        if (!ok) continue;
-        const unsigned char* slot = stage_buf + st * STAGE_BYTES;
-        const uint4 wa = *reinterpret_cast<const uint4*>(slot + r_a * GROUP_BYTES + tig * 16);
-        const uint4 wb = *reinterpret_cast<const uint4*>(slot + r_b * GROUP_BYTES + tig * 16);
-        uint4 q0[NT], q1[NT];
-        float2 sx[NT];
+      if (cur.dense) {
+        for (int j = cur.j0; j < cur.j1; ++j, ++consumed) {
+          const int g = 2 * j;
+          const bool two = g + 1 < p.ng;
+          const int st = consumed % STAGES;
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (consumed / STAGES) & 1, SITE_DEC_FULL));
+          if (!ok) continue;
+          const unsigned char* slot = stage_buf + st * STAGE_BYTES;
+          const unsigned char* wrow_a = slot + r_a * (2 * GROUP_BYTES) + tig * 16;
+          const unsigned char* wrow_b = slot + r_b * (2 * GROUP_BYTES) + tig * 16;
+          const float* sums = reinterpret_cast<const float*>(sumx_ring + st * 2 * SUMX_BYTES);
+          uint4 wa[2], wb[2];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const int xr = nt * 8 + gid;     // token row of the activation tile (128-byte swizzle)
-          const unsigned char* xrow = slot + W_TILE_BYTES + xr * BCOL;
-          q0[nt] = *reinterpret_cast<const uint4*>(xrow + (((2 * tig) ^ (xr & 7)) << 4));
-          q1[nt] = *reinterpret_cast<const uint4*>(xrow + (((2 * tig + 1) ^ (xr & 7)) << 4));
-          sx[nt] = (is_dense && p.sumxf)
-                       ? *reinterpret_cast<const float2*>(slot + W_TILE_BYTES + X_TILE_BYTES + (nt * 8 + tig * 2) * 4)
-                       : make_float2(0.f, 0.f);
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[st]);
-
-        int acc[NT][4];
+          for (int h = 0; h < 2; ++h) {
+            wa[h] = *reinterpret_cast<const uint4*>(wrow_a + h * GROUP_BYTES);
+            wb[h] = *reinterpret_cast<const uint4*>(wrow_b + h * GROUP_BYTES);
+          }
+          const float2 sza0 = szs[(g & (SZ_CHUNK - 1)) * ROWS + r_a];
+          const float2 szb0 = szs[(g & (SZ_CHUNK - 1)) * ROWS + r_b];
+          const float2 sza1 = szs[((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_a];
+          const float2 szb1 = szs[((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_b];
+          int acc0[NT][4], acc1[NT][4];
+          {
+            uint4 q0[NT], q1[NT];
+            float2 sx[NT];
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+            for (int nt = 0; nt < NT; ++nt) {
+              q0[nt] = *reinterpret_cast<const uint4*>(slot + xd0[0][nt]);
+              q1[nt] = *reinterpret_cast<const uint4*>(slot + xd1[0][nt]);
+              sx[nt] = p.sumxf ? *reinterpret_cast<const float2*>(sums + nt * 8 + tig * 2) : make_float2(0.f, 0.f);
+            }
+            group_mma<NT>(acc0, wa[0], wb[0], q0, q1);
+            group_fold<NT>(y, acc0, sza0.x, szb0.x, sza0.y, szb0.y, sx);
+          }
+          {
+            uint4 q0[NT], q1[NT];
+            float2 sx[NT];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) acc[nt][i] = 0;
-        const uint32_t wa_[4] = {wa.x, wa.y, wa.z, wa.w};
-        const uint32_t wb_[4] = {wb.x, wb.y, wb.z, wb.w};
+            for (int nt = 0; nt < NT; ++nt) {
+              q0[nt] = *reinterpret_cast<const uint4*>(slot + xd0[1][nt]);
+              q1[nt] = *reinterpret_cast<const uint4*>(slot + xd1[1][nt]);
+              sx[nt] = (p.sumxf && two) ? *reinterpret_cast<const float2*>(sums + TOK + nt * 8 + tig * 2)
+                                        : make_float2(0.f, 0.f);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[st]);      // every shared-memory read of this slot is done
+            group_mma<NT>(acc1, wa[1], wb[1], q0, q1);
+            group_fold<NT>(y, acc1, sza1.x, szb1.x, sza1.y, szb1.y, sx);
+          }
+          if (DUMP && p.acc_dump) {
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const uint32_t b0_[4] = {q0[nt].x, q0[nt].z, q1[nt].x, q1[nt].z};
-          const uint32_t b1_[4] = {q0[nt].y, q0[nt].w, q1[nt].y, q1[nt].w};
+            for (int h = 0; h < 2; ++h)
 #pragma unroll
-          for (int jj = 0; jj < 4; ++jj)
-            mma_m16n8k32_s8(acc[nt], nib_lo_x16(wa_[jj]), nib_lo_x16(wb_[jj]), nib_hi_x16(wa_[jj]),
-                            nib_hi_x16(wb_[jj]), b0_[jj], b1_[jj]);
-        }
-
-        // fold: accumulators carry a factor 16 from the weight expansion
-        const float w = is_dense ? 0.0625f : 0.0625f * p.sparse_weight;
-        const float fa = s_a * w, fb = s_b * w;
-        const float ca = s_a * z_a, cb = s_b * z_b;
+              for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          y[nt][0] = fmaf((float)acc[nt][0], fa, fmaf(-ca, sx[nt].x, y[nt][0]));
-          y[nt][1] = fmaf((float)acc[nt][1], fa, fmaf(-ca, sx[nt].y, y[nt][1]));
-          y[nt][2] = fmaf((float)acc[nt][2], fb, fmaf(-cb, sx[nt].x, y[nt][2]));
-          y[nt][3] = fmaf((float)acc[nt][3], fb, fmaf(-cb, sx[nt].y, y[nt][3]));
-        }
-        if (DUMP) {
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int rl = (i & 2) ? r_b : r_a;
-              const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
-              if (tok >= p.T) continue;
-              // parity aid, not a hot path: every store is range-checked
-              if (is_dense) {
-                const size_t idx = ((size_t)g * p.N + row0 + rl) * p.T + tok;
-                if (p.acc_dump && row0 + rl < p.N) {
-                  if (g >= 0 && g < p.ng && idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = acc[nt][i] >> 4;
+                for (int i = 0; i < 4; ++i) {
+                  const int rl = (i & 2) ? r_b : r_a;
+                  const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
+                  if (tok >= p.T || g + h >= p.ng || row0 + rl >= p.N) continue;
+                  // parity aid, not a hot path: every store is range-checked
+                  const size_t idx = ((size_t)(g + h) * p.N + row0 + rl) * p.T + tok;
+                  if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = (h ? acc1[nt][i] : acc0[nt][i]) >> 4;
                   else record_error(SITE_DEC_DUMP, 1);
                 }
-              } else if (p.acc_hi_dump) {
+          }
+        }
+      } else {
+        const int blk0 = ld_plain(p.hp_row_offsets + r);
+        for (int j = cur.j0; j < cur.j1; ++j, ++consumed) {
+          const int blk = blk0 + j - p.nd;
+          const int g = ld_plain(p.hp_col_indices + blk);
+          // a residual block's column is anywhere in the row: fetch the two scales directly
+          float s_a = 0.f, s_b = 0.f;
+          if (p.scale_u4) {
+            if (row0 + r_a < p.N) s_a = __half2float(ld_plain(p.scale_u4 + (size_t)(row0 + r_a) * p.ng + g));
+            if (row0 + r_b < p.N) s_b = __half2float(ld_plain(p.scale_u4 + (size_t)(row0 + r_b) * p.ng + g));
+          }
+          const int st = consumed % STAGES;
+          if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (consumed / STAGES) & 1, SITE_DEC_FULL));
+          if (!ok) continue;
+          const unsigned char* slot = stage_buf + st * STAGE_BYTES;
+          const uint4 wa = *reinterpret_cast<const uint4*>(slot + r_a * GROUP_BYTES + tig * 16);
+          const uint4 wb = *reinterpret_cast<const uint4*>(slot + r_b * GROUP_BYTES + tig * 16);
+          uint4 q0[NT], q1[NT];
+          float2 sx[NT];
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            q0[nt] = *reinterpret_cast<const uint4*>(slot + xs0[nt]);
+            q1[nt] = *reinterpret_cast<const uint4*>(slot + xs1[nt]);
+            sx[nt] = make_float2(0.f, 0.f);
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&empty[st]);
+          int acc[NT][4];
+          group_mma<NT>(acc, wa, wb, q0, q1);
+          const float w = 0.0625f * p.sparse_weight;
+          group_fold<NT>(y, acc, s_a * w, s_b * w, 0.f, 0.f, sx);
+          if (DUMP && p.acc_hi_dump) {
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int rl = (i & 2) ? r_b : r_a;
+                const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
+                if (tok >= p.T) continue;
                 const size_t idx = ((size_t)blk * BROW + rl) * p.T + tok;
                 if (blk >= 0 && blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = acc[nt][i] >> 4;
                 else record_error(SITE_DEC_DUMP, 2);
               }
-            }
+          }
         }
       }
+
+      // this block-row continues in the next span: keep accumulating
+      const bool row_done = !have_next || nxt.r != r;
+      cur = nxt;
+      have = have_next;
+      if (!row_done) continue;
 
       // ---------------------------------------------------------- block-row done
       if (p.Y == nullptr) continue;
@@ -315,8 +509,9 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
               const int row = row0 + ((i & 2) ? r_b : r_a);
               const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
               if (row < p.N && tok < p.T) {
+                const float v = (i & 1) ? y[nt][i >> 1].y : y[nt][i >> 1].x;
                 const float sxs = __half2float(ld_plain(p.scale_x + tok));
-                p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(y[nt][i] * sxs);
+                p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v * sxs);
               }
             }
         }
@@ -329,8 +524,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
         float* dst = base + (size_t)(cta + r) * tile;
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-          *reinterpret_cast<float2*>(dst + r_a * TOK + nt * 8 + tig * 2) = make_float2(y[nt][0], y[nt][1]);
-          *reinterpret_cast<float2*>(dst + r_b * TOK + nt * 8 + tig * 2) = make_float2(y[nt][2], y[nt][3]);
+          *reinterpret_cast<float2*>(dst + r_a * TOK + nt * 8 + tig * 2) = y[nt][0];
+          *reinterpret_cast<float2*>(dst + r_b * TOK + nt * 8 + tig * 2) = y[nt][1];
         }
         __threadfence();
         asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");

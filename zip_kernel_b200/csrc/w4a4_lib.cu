@@ -90,6 +90,21 @@ int make_map(CUtensorMap* m, const void* ptr, uint64_t row_bytes, uint64_t rows,
   return W4A4_OK;
 }
 
+// Expanded activations (T, K) bytes seen as [token][group][128 bytes]; the box takes
+// `groups` adjacent groups of `tokens` tokens, 128-byte swizzle.  Tokens and groups
+// past the end read as zero.
+int make_map_x(CUtensorMap* m, const void* XE, int T, int K, uint32_t groups, uint32_t tokens) {
+  cuuint64_t dims[3] = {128, (cuuint64_t)(K / 128), (cuuint64_t)T};
+  cuuint64_t strides[2] = {128, (cuuint64_t)K};
+  cuuint32_t box[3] = {128, groups, tokens};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(XE), dims, strides, box, estr,
+                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(W4A4_ERR_LAUNCH, "cuTensorMapEncodeTiled(activations) failed (%d)", (int)r);
+  return W4A4_OK;
+}
+
 // ------------------------------------------------------------------ workspace layout
 constexpr size_t WS_PARTIAL_TILES = 1024;                                   // shared block-row pieces
 constexpr size_t WS_PARTIAL_BYTES = WS_PARTIAL_TILES * 128 * 16 * 4;       // 8 MiB
@@ -201,7 +216,8 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   const int row_tiles = (a.N + dec::ROWS - 1) / dec::ROWS;
   if (row_tiles > dec::MAX_ROW_TILES_SMEM)
     return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d exceeds %d rows", a.N, dec::MAX_ROW_TILES_SMEM * dec::ROWS);
-  const long long steps_total = (long long)row_tiles * (a.do_dense ? ng : 0) + (has_sparse ? a.nnz : 0);
+  const int dense_steps = a.do_dense ? (ng + 1) / 2 : 0;      // two groups per dense step
+  const long long steps_total = (long long)row_tiles * dense_steps + (has_sparse ? a.nnz : 0);
   DecodePlan plan = plan_decode(a.T, a.K, a.N, steps_total, dev->sm_count);
   const WsLayout wl = ws_layout(a.T, a.K);
   if (a.ws == nullptr || a.ws_bytes < wl.total)
@@ -222,21 +238,21 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
 
   const bool nt2 = a.T > 8;
-  CUtensorMap tm_low, tm_high, tm_x;
-  // the operand that is switched off borrows the other one's map and is never read
+  CUtensorMap tm_low, tm_x2, tm_x1;
+  // dense weights: 128 rows x two groups (128 bytes) per copy; unused (but valid) when the dense part is off
   int rc = make_map(&tm_low, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
-                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, dec::ROWS,
-                    CU_TENSOR_MAP_SWIZZLE_NONE);
+                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, a.do_dense ? 2 * GROUP_BYTES : GROUP_BYTES,
+                    dec::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
-  rc = make_map(&tm_high, has_sparse ? a.W_high : a.W_low, has_sparse ? 64 : (uint64_t)a.K / 2,
-                has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, dec::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  rc = make_map_x(&tm_x2, XE, a.T, a.K, 2, nt2 ? 16 : 8);     // dense steps: two groups
   if (rc) return rc;
-  rc = make_map(&tm_x, XE, (uint64_t)a.K, (uint64_t)a.T, BCOL, nt2 ? 16 : 8, CU_TENSOR_MAP_SWIZZLE_128B);
+  rc = make_map_x(&tm_x1, XE, a.T, a.K, 1, nt2 ? 16 : 8);     // residual steps: one group
   if (rc) return rc;
 
   dec::Params p;
   p.hp_row_offsets = a.hp_row_offsets;
   p.hp_col_indices = a.hp_col_indices;
+  p.W_high = static_cast<const int8_t*>(a.W_high);
   p.scale_u4 = static_cast<const __half*>(a.scale_u4);
   p.zero_u4 = static_cast<const __half*>(a.zero_u4);
   p.sumxf = a.do_dense ? sumxf : nullptr;
@@ -255,8 +271,9 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   p.acc_hi_dump = a.acc_hi_dump;
   p.T = a.T; p.K = a.K; p.N = a.N; p.ng = ng; p.nnz = has_sparse ? a.nnz : 0;
   p.row_tiles = row_tiles;
-  p.nd = a.do_dense ? ng : 0;
+  p.nd = dense_steps;
   p.sparse_on = has_sparse ? 1 : 0;
+  p.sz_vec = (ng % 8 == 0 && aligned(a.scale_u4, 16) && aligned(a.zero_u4, 16)) ? 1 : 0;
   p.steps_total = (int)steps_total;
   p.steps_per_cta = plan.steps_per_cta;
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
@@ -276,7 +293,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   cfg.stream = a.stream;
   cudaLaunchAttribute attr[1];
   launch_pdl(cfg, pdl, attr);
-  e = cudaLaunchKernelEx(&cfg, kern, tm_low, tm_high, tm_x, p);
+  e = cudaLaunchKernelEx(&cfg, kern, tm_low, tm_x2, tm_x1, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }

@@ -61,12 +61,13 @@ def load() -> ctypes.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    if not os.path.exists(LIB_PATH):
+    path = os.environ.get("W4A4_B200_LIB", LIB_PATH)
+    if not os.path.exists(path):
         raise RuntimeError(
-            f"{LIB_PATH} is missing: build it with `python -m zip_kernel_b200.build` "
+            f"{path} is missing: build it with `python -m zip_kernel_b200.build` "
             "(needs nvcc; there is no CPU fallback)"
         )
-    lib = ctypes.CDLL(LIB_PATH)
+    lib = ctypes.CDLL(path)
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)
         fn.restype = res

@@ -1,4 +1,4 @@
-// Kernel 3: weight-streaming stream-K fused GEMM for small token counts (16
+// Kernel 3: weight-streaming split-K fused GEMM for small token counts (16
 // tokens per CTA pass).  Replaces the reference's dp4a GEMV family
 // (cuda_kernel/csrc/fused_dense_sparse/fused_gemv_decode.cu:54-191,
 // fused_gemv_smallT.cu:47-221) and the split-K branch of its MMA kernel
@@ -10,15 +10,16 @@
 // Work decomposition.  One "step" is a tile of packed nibbles of one block-row
 // (128 rows): two adjacent groups of the dense weights (128 x 128 bytes = 16 KB,
 // so every TMA row is a full 128-byte line), or one residual block (8 KB,
-// contiguous).  All steps of the layer form one line, block-row after
-// block-row, dense pairs first and the row's residual blocks behind them:
-//   first_step(r) = r * ceil(ng / 2) + hp_row_offsets[r].
-// The line is cut into equal contiguous ranges, one per CTA, so every CTA
-// streams the same number of bytes however N, K and the residual mask fall
-// relative to the SM count.  A CTA that owns a whole block-row writes it out
-// directly; a block-row shared by several CTAs meets in an fp32 workspace, and
-// the CTA that arrives last at the row's counter adds the pieces in K order,
-// applies scale_x and writes fp16.  Nothing ever waits for another CTA.
+// contiguous).  A block-row is owned by a thread-block cluster of S CTAs
+// (S = 1..8, chosen so that the grid fills the SMs about twice): CTA k of the
+// cluster takes the k-th share of the row's dense steps - known without reading
+// memory, so its first weight copies leave at once - and the k-th share of the
+// row's residual blocks.  When the row is finished the S partial tiles meet in
+// distributed shared memory: every CTA parks its 128 x 16 fp32 tile in its own
+// shared memory, the cluster synchronises, and CTA k adds rows
+// [k*128/S, (k+1)*128/S) of all S tiles in rank order, applies scale_x and
+// writes fp16.  No global-memory round trip, counter or workspace is involved,
+// and nothing waits on a CTA outside its own cluster.
 //
 // Data flow per CTA.  A producer warp walks the range and, per step, issues
 // non-multicast asynchronous copies into one slot of a 4-deep shared-memory
@@ -54,7 +55,7 @@ constexpr int BLK_BYTES = BROW * GROUP_BYTES;     // 8192: one residual block
 constexpr int X_TILE_BYTES = TOK * BCOL;          // 2048 (16 tokens x 128 codes) per group
 constexpr int SUMX_BYTES = TOK * 4;               // 64 per group
 constexpr int STAGE_BYTES = W_TILE_BYTES + 2 * X_TILE_BYTES;   // group sums live in a ring of their own
-constexpr int MAX_ROW_TILES_SMEM = 1024;          // block-row offsets cached in shared memory
+constexpr int MAX_CLUSTER = 8;                    // portable cluster size limit
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero staged per span
 constexpr int SZ_BYTES = SZ_CHUNK * ROWS * 8;     // float2 (scale/16, scale*zero) per (group, row)
 
@@ -70,8 +71,6 @@ struct Params {
   const __half* scale_x;    // (T)
   __half* Y;
   long long y_stride_n, y_stride_t;
-  float* partial;           // [tok tiles][ctas + row tiles][128][16] fp32
-  int* counters;            // [tok tiles][row tiles], zero between launches
   int* acc_dump;            // optional (ng, N, T) int32
   int* acc_hi_dump;         // optional (nnz, 128, T) int32
   int T, K, N, ng, nnz;
@@ -79,13 +78,28 @@ struct Params {
   int nd;                   // dense steps per block-row (ceil(ng/2), or 0 when the dense part is off)
   int sparse_on;
   int sz_vec;               // scale/zero rows may be read with 128-bit loads
-  int steps_total;
-  int steps_per_cta;        // 0: one whole block-row per CTA (no shared rows, no workspace)
+  int split;                // CTAs per block-row (= cluster size along x)
   float sparse_weight;      // 16 (fused) or 1 (sparse-only op)
 };
 
-inline size_t smem_bytes() {
-  return 1024 + (size_t)STAGES * STAGE_BYTES + STAGES * 2 * SUMX_BYTES + SZ_BYTES + (MAX_ROW_TILES_SMEM + 2) * 4 + 256;
+inline size_t smem_bytes() { return 1024 + (size_t)STAGES * STAGE_BYTES + STAGES * 2 * SUMX_BYTES + SZ_BYTES + 256; }
+
+// ---- thread-block cluster helpers (no multicast; plain distributed-shared-memory loads)
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// All threads of all CTAs of the cluster arrive; hardware barrier, not a spin loop.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_dsmem_f32(const void* own_smem_ptr, uint32_t peer_rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(own_smem_ptr)), "r"(peer_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }
 
 // d = a * b + c on two packed fp32 lanes
@@ -149,19 +163,22 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sumx_ring = stage_buf + STAGES * STAGE_BYTES;
   float2* szs = reinterpret_cast<float2*>(sumx_ring + STAGES * 2 * SUMX_BYTES);   // [16 groups][128 rows] (s/16, s*z)
-  int* row_off = reinterpret_cast<int*>(reinterpret_cast<unsigned char*>(szs) + SZ_BYTES);   // first_step(r)
-  uint64_t* full = reinterpret_cast<uint64_t*>(row_off + MAX_ROW_TILES_SMEM + 2);
+  uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(szs) + SZ_BYTES);
   uint64_t* empty = full + STAGES;
-  int* misc = reinterpret_cast<int*>(empty + STAGES);     // [0] = last-arriver flag, [1] = a wait gave up
+  int* misc = reinterpret_cast<int*>(empty + STAGES);     // [1] = a wait gave up
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int cta = blockIdx.x;
+  const int S = p.split;
+  const int rank = S > 1 ? (int)cluster_ctarank() : 0;   // == blockIdx.x % S
+  const int r = blockIdx.x / S;                            // block-row of this cluster
   const int tt = blockIdx.y;
   const int tok0 = tt * TOK;
-  const int L = p.steps_per_cta;
+  const int row0 = r * ROWS;
   constexpr int XG_BYTES = NT * 8 * BCOL;     // activation bytes actually copied per group
+  // this CTA's share of the dense steps of the block-row: needs no memory access
+  const int d_lo = (int)((long long)rank * p.nd / S), d_hi = (int)((long long)(rank + 1) * p.nd / S);
 
   if (tid == 0) {
     for (int i = 0; i < STAGES; ++i) {
@@ -169,87 +186,62 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
       mbar_init(&empty[i], CONSUMER_WARPS);
     }
     mbar_fence_init();
-    misc[0] = 0;
     misc[1] = 0;
     tma_prefetch_desc(&tm_low);
     tma_prefetch_desc(&tm_x2);
     tma_prefetch_desc(&tm_x1);
   }
-  // first_step(r) for every block-row (weights only: valid before the dependency wait)
-  for (int r = tid; r <= p.row_tiles; r += THREADS)
-    row_off[r] = r * p.nd + (p.sparse_on ? ld_plain(p.hp_row_offsets + r) : 0);
   __syncthreads();
-
-  const int lo = L ? cta * L : row_off[cta];
-  const int hi = L ? min(p.steps_total, lo + L) : row_off[cta + 1];
-  // block-row that contains step `lo`: largest r with first_step(r) <= lo
-  int r_first = cta;
-  if (L) {
-    int a = 0, b = p.row_tiles;            // invariant: row_off[a] <= lo < row_off[b] (lo < steps_total)
-    while (b - a > 1) {
-      const int m = (a + b) >> 1;
-      if (row_off[m] <= lo) a = m; else b = m;
-    }
-    r_first = a;
-  }
 
   if (warp == CONSUMER_WARPS) {
     // ------------------------------------------------------------ producer
-    if (lane == 0 && lo < hi) {
+    if (lane == 0) {
       const bool with_sums = p.sumxf != nullptr;
       const float* sums_base = with_sums ? p.sumxf + (size_t)tt * p.ng * TOK : nullptr;
       bool ok = true;
-      // Per step: the weight tile does not depend on the preceding kernel in the
-      // stream, the activation copies do.  Dense step j of block-row r covers
-      // groups 2j and 2j+1; a residual step covers one block.
-      auto issue_w = [&](int j, int r, int st) {
-        unsigned char* slot = stage_buf + st * STAGE_BYTES;
-        if (j < p.nd) {
-          const int n_sum = with_sums ? ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES : 0;
-          mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + 2 * XG_BYTES + n_sum);
-          tma_load_2d(slot, &tm_low, 2 * j * GROUP_BYTES, r * ROWS, &full[st]);
-        } else {
-          const int blk = ld_plain(p.hp_row_offsets + r) + j - p.nd;
-          mbar_arrive_expect_tx(&full[st], BLK_BYTES + XG_BYTES);
-          bulk_load_1d(slot, p.W_high + (size_t)blk * BLK_BYTES, BLK_BYTES, &full[st]);
-        }
+      // The weight copy of a step does not depend on the preceding kernel in the
+      // stream, the activation copies do.  Dense step j covers groups 2j, 2j+1.
+      auto dense_w = [&](int j, int st) {
+        const int n_sum = with_sums ? ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES : 0;
+        mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + 2 * XG_BYTES + n_sum);
+        tma_load_2d(stage_buf + st * STAGE_BYTES, &tm_low, 2 * j * GROUP_BYTES, row0, &full[st]);
       };
-      auto issue_x = [&](int j, int r, int st) {
-        unsigned char* slot = stage_buf + st * STAGE_BYTES + W_TILE_BYTES;
-        if (j < p.nd) {
-          tma_load_3d(slot, &tm_x2, 0, 2 * j, tok0, &full[st]);
-          if (with_sums)
-            bulk_load_1d(sumx_ring + st * 2 * SUMX_BYTES, sums_base + 2 * j * TOK,
-                         ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES, &full[st]);
-        } else {
-          const int blk = ld_plain(p.hp_row_offsets + r) + j - p.nd;
-          tma_load_3d(slot, &tm_x1, 0, ld_plain(p.hp_col_indices + blk), tok0, &full[st]);
-        }
+      auto dense_x = [&](int j, int st) {
+        tma_load_3d(stage_buf + st * STAGE_BYTES + W_TILE_BYTES, &tm_x2, 0, 2 * j, tok0, &full[st]);
+        if (with_sums)
+          bulk_load_1d(sumx_ring + st * 2 * SUMX_BYTES, sums_base + 2 * j * TOK,
+                       ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES, &full[st]);
       };
       // ring fill: weight tiles first, then wait for the activations' producer kernel
-      const int n_pre = min(STAGES, hi - lo);
-      {
-        int r = r_first, row_hi = row_off[r + 1];
-        for (int n = 0; n < n_pre; ++n) {
-          const int pos = lo + n;
-          while (pos >= row_hi) row_hi = row_off[++r + 1];
-          issue_w(pos - row_off[r], r, n);
-        }
+      const int n_dense = d_hi - d_lo;
+      const int n_pre = min(STAGES, n_dense);
+      for (int n = 0; n < n_pre; ++n) dense_w(d_lo + n, n);
+      // this CTA's share of the residual blocks of the block-row
+      int b_lo = 0, b_hi = 0;
+      if (p.sparse_on) {
+        const int o0 = ld_plain(p.hp_row_offsets + r), o1 = ld_plain(p.hp_row_offsets + r + 1);
+        b_lo = o0 + (int)((long long)rank * (o1 - o0) / S);
+        b_hi = o0 + (int)((long long)(rank + 1) * (o1 - o0) / S);
       }
       grid_dependency_wait();
-      int r = r_first, row_lo = row_off[r], row_hi = row_off[r + 1];
-      int st = 0;
+      int st = 0, n = 0;
       uint32_t ph = 1;                     // parity the empty barrier is waited on
-      int n = 0;
-      for (int pos = lo; pos < hi; ++pos, ++n) {
-        while (pos >= row_hi) { ++r; row_lo = row_hi; row_hi = row_off[r + 1]; }
-        const int j = pos - row_lo;
+      for (int j = d_lo; j < d_hi && ok; ++j, ++n) {
         if (n >= n_pre) {
           ok = mbar_wait(&empty[st], ph, SITE_DEC_EMPTY);
           if (!ok) break;
-          issue_w(j, r, st);
+          dense_w(j, st);
         }
-        issue_x(j, r, st);
+        dense_x(j, st);
+        if (++st == STAGES) { st = 0; ph ^= 1; }
+      }
+      for (int blk = b_lo; blk < b_hi && ok; ++blk, ++n) {
+        ok = mbar_wait(&empty[st], ph, SITE_DEC_EMPTY);
+        if (!ok) break;
+        unsigned char* slot = stage_buf + st * STAGE_BYTES;
+        mbar_arrive_expect_tx(&full[st], BLK_BYTES + XG_BYTES);
+        bulk_load_1d(slot, p.W_high + (size_t)blk * BLK_BYTES, BLK_BYTES, &full[st]);
+        tma_load_3d(slot + W_TILE_BYTES, &tm_x1, 0, ld_plain(p.hp_col_indices + blk), tok0, &full[st]);
         if (++st == STAGES) { st = 0; ph ^= 1; }
       }
       if (!ok) {
@@ -259,7 +251,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
           mbar_wait(&full[i % STAGES], (i / STAGES) & 1, SITE_DEC_DRAIN);
       }
     }
-  } else if (lo < hi) {
+  } else {
     // ------------------------------------------------------------ consumers
     const int gid = lane >> 2;
     const int tig = lane & 3;
@@ -290,27 +282,29 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
     for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = make_float2(0.f, 0.f);
     bool ok = true;
     int consumed = 0;
+    int b_lo = 0, b_hi = 0;
+    if (p.sparse_on) {
+      const int o0 = ld_plain(p.hp_row_offsets + r), o1 = ld_plain(p.hp_row_offsets + r + 1);
+      b_lo = o0 + (int)((long long)rank * (o1 - o0) / S);
+      b_hi = o0 + (int)((long long)(rank + 1) * (o1 - o0) / S);
+    }
 
-    // The CTA's range is walked in spans: a run of dense steps of one block-row
-    // that lies inside one aligned window of 32 groups, or the residual blocks of
-    // a block-row.  `walk` yields the next span and advances (r, pos).
-    struct Span { int r, j0, j1, dense; };
-    auto walk = [&](int& r, int& pos, Span& sp) -> bool {
-      while (pos < hi) {
-        const int row_lo = row_off[r], row_hi = row_off[r + 1];
-        if (pos >= row_hi) { ++r; continue; }
-        const int j = pos - row_lo;
-        const int seg_end = min(hi, row_hi) - row_lo;
-        if (j < p.nd) {
-          sp.j1 = min(min(seg_end, p.nd), (j / (SZ_CHUNK / 2) + 1) * (SZ_CHUNK / 2));
-          sp.dense = 1;
-        } else {
-          sp.j1 = seg_end;
-          sp.dense = 0;
-        }
-        sp.r = r;
+    // The dense share is walked in spans that lie inside one aligned window of 16
+    // groups (8 steps); the residual blocks form a last span.
+    struct Span { int j0, j1, dense; };
+    auto walk = [&](int& j, int& did_sparse, Span& sp) -> bool {
+      if (j < d_hi) {
         sp.j0 = j;
-        pos = row_lo + sp.j1;
+        sp.j1 = min(d_hi, (j / (SZ_CHUNK / 2) + 1) * (SZ_CHUNK / 2));
+        sp.dense = 1;
+        j = sp.j1;
+        return true;
+      }
+      if (!did_sparse && b_lo < b_hi) {
+        did_sparse = 1;
+        sp.j0 = b_lo;
+        sp.j1 = b_hi;
+        sp.dense = 0;
         return true;
       }
       return false;
@@ -324,7 +318,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
     auto fetch_sz = [&](const Span& sp) {
       ps = pz = make_uint4(0, 0, 0, 0);
       if (!sp.dense || p.scale_u4 == nullptr) return;
-      const int row = sp.r * ROWS + lrow;
+      const int row = row0 + lrow;
       if (row >= p.N) return;
       const int g = (2 * sp.j0 / SZ_CHUNK) * SZ_CHUNK + lhalf * 8;
       if (g >= p.ng) return;
@@ -355,28 +349,18 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
       }
     };
 
-    int r_w = r_first, pos_w = lo;
+    int j_w = d_lo, did_sparse = 0;
     Span cur, nxt;
-    bool have = walk(r_w, pos_w, cur);
+    bool have = walk(j_w, did_sparse, cur);
     if (have) fetch_sz(cur);
-    int prev_r = -1;
     // A wait that gives up clears `ok` for the whole warp; the loops still run to
-    // their end (skipping the work) so that every named barrier below is reached.
+    // their end (skipping the work) so that every barrier below is reached.
     while (have) {
-      const bool have_next = walk(r_w, pos_w, nxt);
+      const bool have_next = walk(j_w, did_sparse, nxt);
       asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");   // previous span's window is free
       if (cur.dense) park_sz();
       if (have_next) fetch_sz(nxt);
       asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
-
-      const int r = cur.r;
-      const int row_lo = row_off[r], row_hi = row_off[r + 1];
-      const int row0 = r * ROWS;
-      if (r != prev_r) {      // first span of a block-row in this CTA
-        prev_r = r;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = make_float2(0.f, 0.f);
-      }
 
       if (cur.dense) {
         for (int j = cur.j0; j < cur.j1; ++j, ++consumed) {
@@ -445,9 +429,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
           }
         }
       } else {
-        const int blk0 = ld_plain(p.hp_row_offsets + r);
-        for (int j = cur.j0; j < cur.j1; ++j, ++consumed) {
-          const int blk = blk0 + j - p.nd;
+        for (int blk = cur.j0; blk < cur.j1; ++blk, ++consumed) {
           const int g = ld_plain(p.hp_col_indices + blk);
           // a residual block's column is anywhere in the row: fetch the two scales directly
           float s_a = 0.f, s_b = 0.f;
@@ -491,69 +473,58 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
         }
       }
 
-      // this block-row continues in the next span: keep accumulating
-      const bool row_done = !have_next || nxt.r != r;
       cur = nxt;
       have = have_next;
-      if (!row_done) continue;
-
-      // ---------------------------------------------------------- block-row done
-      if (p.Y == nullptr) continue;
-      const bool whole = (L == 0) || ((lo <= row_lo) && (row_hi <= hi));
-      if (whole) {
-        if (ok) {
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int row = row0 + ((i & 2) ? r_b : r_a);
-              const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
-              if (row < p.N && tok < p.T) {
-                const float v = (i & 1) ? y[nt][i >> 1].y : y[nt][i >> 1].x;
-                const float sxs = __half2float(ld_plain(p.scale_x + tok));
-                p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v * sxs);
-              }
-            }
-        }
-      } else {
-        // shared block-row: park this CTA's piece, the last arriver adds them up
-        const int first_cta = row_lo / L;
-        const int n_pieces = (row_hi - 1) / L - first_cta + 1;
-        const size_t tile = (size_t)ROWS * TOK;
-        float* base = p.partial + (size_t)tt * (gridDim.x + p.row_tiles) * tile;
-        float* dst = base + (size_t)(cta + r) * tile;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          *reinterpret_cast<float2*>(dst + r_a * TOK + nt * 8 + tig * 2) = y[nt][0];
-          *reinterpret_cast<float2*>(dst + r_b * TOK + nt * 8 + tig * 2) = y[nt][1];
-        }
-        __threadfence();
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
-        if (tid == 0) {
-          int* ctr = p.counters + tt * p.row_tiles + r;
-          const int prev = atomicAdd(ctr, 1);
-          const int last = (prev == n_pieces - 1);
-          if (last) *ctr = 0;
-          misc[0] = last;
-        }
-        asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");
-        if (misc[0] && ok) {
-          __threadfence();
-          constexpr int NCOL = NT * 8;
-          const float* src = base + (size_t)(first_cta + r) * tile;
-          for (int i = tid; i < ROWS * NCOL; i += CONSUMER_THREADS) {
-            const int rl = i / NCOL, col = i - rl * NCOL;
-            const int row = row0 + rl, tok = tok0 + col;
-            if (row >= p.N || tok >= p.T) continue;
-            float v = 0.f;
-            for (int c = 0; c < n_pieces; ++c) v += __ldcg(src + (size_t)c * tile + rl * TOK + col);
-            v *= __half2float(ld_plain(p.scale_x + tok));
-            p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v);
-          }
-        }
-      }
     }
     if (!ok) misc[1] = 1;
+
+    // ---------------------------------------------------------- block-row share done
+    if (p.Y != nullptr && S == 1) {
+      if (ok) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int row = row0 + ((i & 2) ? r_b : r_a);
+            const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
+            if (row < p.N && tok < p.T) {
+              const float v = (i & 1) ? y[nt][i >> 1].y : y[nt][i >> 1].x;
+              const float sxs = __half2float(ld_plain(p.scale_x + tok));
+              p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v * sxs);
+            }
+          }
+      }
+    } else if (p.Y != nullptr) {
+      // park this CTA's 128 x 16 partial tile in its own shared memory (the ring is
+      // drained: every copy that was issued has been consumed)
+      float* red = reinterpret_cast<float*>(stage_buf);
+      asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");   // nobody still reads the last slot
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        *reinterpret_cast<float2*>(red + r_a * TOK + nt * 8 + tig * 2) = y[nt][0];
+        *reinterpret_cast<float2*>(red + r_b * TOK + nt * 8 + tig * 2) = y[nt][1];
+      }
+    }
+  }
+
+  if (p.Y != nullptr && S > 1) {
+    // Every thread of every CTA of the cluster reaches both barriers: no path
+    // above returns early.  CTA k then owns rows [k*128/S, (k+1)*128/S) of the tile.
+    __syncwarp();
+    cluster_sync_all();
+    const float* red = reinterpret_cast<const float*>(stage_buf);
+    constexpr int NCOL = NT * 8;
+    const int rl_lo = rank * ROWS / S, rl_hi = (rank + 1) * ROWS / S;
+    for (int i = tid; i < (rl_hi - rl_lo) * NCOL; i += THREADS) {
+      const int rl = rl_lo + i / NCOL, col = i % NCOL;
+      const int row = row0 + rl, tok = tok0 + col;
+      if (row >= p.N || tok >= p.T) continue;
+      float v = 0.f;
+      for (int c = 0; c < S; ++c) v += ld_dsmem_f32(red + rl * TOK + col, (uint32_t)c);
+      v *= __half2float(ld_plain(p.scale_x + tok));
+      p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v);
+    }
+    cluster_sync_all();     // peers may not retire while their tiles are still being read
   }
 }
 

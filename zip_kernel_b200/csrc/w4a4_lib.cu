@@ -6,6 +6,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 #include <string>
@@ -128,32 +129,23 @@ WsLayout ws_layout(int T, int K) {
 
 // ------------------------------------------------------------------ plans
 struct DecodePlan {
-  int row_tiles, tok_tiles, ctas, steps_per_cta;   // steps_per_cta == 0: one block-row per CTA
+  int row_tiles, tok_tiles, split;   // split = CTAs (cluster size) per block-row
 };
-DecodePlan plan_decode(int T, int K, int N, long long steps_total, int sm_count) {
+DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count) {
   using namespace w4a4;
   DecodePlan p;
   p.row_tiles = (N + dec::ROWS - 1) / dec::ROWS;
   p.tok_tiles = (T + dec::TOK - 1) / dec::TOK;
-  const long long resident = 2LL * sm_count;
-  // enough independent (block-row, token tile) pairs: no shared rows needed
-  if ((long long)p.row_tiles * p.tok_tiles >= 2 * resident) {
-    p.ctas = p.row_tiles;
-    p.steps_per_cta = 0;
-    return p;
-  }
-  long long want = (resident + p.tok_tiles - 1) / p.tok_tiles;
-  long long L = (steps_total + want - 1) / want;
-  if (L < 2) L = 2;
-  long long ctas = (steps_total + L - 1) / L;
-  if ((ctas + p.row_tiles) * p.tok_tiles > (long long)WS_PARTIAL_TILES ||
-      (long long)p.row_tiles * p.tok_tiles * 4 > W4A4_WORKSPACE_COUNTER_BYTES) {
-    p.ctas = p.row_tiles;
-    p.steps_per_cta = 0;
-    return p;
-  }
-  p.ctas = (int)ctas;
-  p.steps_per_cta = (int)L;
+  // aim at about two resident CTAs per SM; a block-row is never cut finer than its steps
+  const long long base = (long long)p.row_tiles * p.tok_tiles;
+  long long s = (2LL * sm_count + base / 2) / base;
+  // tuning override for A/B experiments
+  static const int env_split = getenv("W4A4_DECODE_SPLIT") ? atoi(getenv("W4A4_DECODE_SPLIT")) : 0;
+  if (env_split > 0) s = env_split;
+  if (s > dec::MAX_CLUSTER) s = dec::MAX_CLUSTER;
+  if (s > dense_steps) s = dense_steps;
+  if (s < 1) s = 1;
+  p.split = (int)s;
   return p;
 }
 
@@ -181,14 +173,6 @@ struct GemmArgs {
   cudaStream_t stream;
 };
 
-cudaError_t launch_pdl(cudaLaunchConfig_t& cfg, bool pdl, cudaLaunchAttribute* attr) {
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  return cudaSuccess;
-}
-
 int launch_expand(const GemmArgs& a, void* XE, float* sumxf, DeviceInfo* dev) {
   using namespace w4a4;
   ExpandParams e;
@@ -214,11 +198,10 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
   const int ng = a.K / BCOL;
   const int row_tiles = (a.N + dec::ROWS - 1) / dec::ROWS;
-  if (row_tiles > dec::MAX_ROW_TILES_SMEM)
-    return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d exceeds %d rows", a.N, dec::MAX_ROW_TILES_SMEM * dec::ROWS);
   const int dense_steps = a.do_dense ? (ng + 1) / 2 : 0;      // two groups per dense step
-  const long long steps_total = (long long)row_tiles * dense_steps + (has_sparse ? a.nnz : 0);
-  DecodePlan plan = plan_decode(a.T, a.K, a.N, steps_total, dev->sm_count);
+  DecodePlan plan = plan_decode(a.T, a.N, dense_steps > 0 ? dense_steps : 1, dev->sm_count);
+  if ((long long)plan.row_tiles * plan.split > 2147483647LL)
+    return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d is too large", a.N);
   const WsLayout wl = ws_layout(a.T, a.K);
   if (a.ws == nullptr || a.ws_bytes < wl.total)
     return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, a.ws_bytes);
@@ -265,8 +248,6 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
     p.y_stride_n = a.T;
     p.y_stride_t = 1;
   }
-  p.partial = reinterpret_cast<float*>(ws + wl.partial);
-  p.counters = reinterpret_cast<int*>(ws + wl.counters);
   p.acc_dump = a.acc_dump;
   p.acc_hi_dump = a.acc_hi_dump;
   p.T = a.T; p.K = a.K; p.N = a.N; p.ng = ng; p.nnz = has_sparse ? a.nnz : 0;
@@ -274,8 +255,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   p.nd = dense_steps;
   p.sparse_on = has_sparse ? 1 : 0;
   p.sz_vec = (ng % 8 == 0 && aligned(a.scale_u4, 16) && aligned(a.zero_u4, 16)) ? 1 : 0;
-  p.steps_total = (int)steps_total;
-  p.steps_per_cta = plan.steps_per_cta;
+  p.split = plan.split;
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
 
   const size_t smem = dec::smem_bytes();
@@ -287,12 +267,26 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
 
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof cfg);
-  cfg.gridDim = dim3(plan.ctas, plan.tok_tiles, 1);
+  cfg.gridDim = dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1);
   cfg.blockDim = dim3(dec::THREADS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = a.stream;
-  cudaLaunchAttribute attr[1];
-  launch_pdl(cfg, pdl, attr);
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  if (plan.split > 1) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = plan.split;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n_attr;
   e = cudaLaunchKernelEx(&cfg, kern, tm_low, tm_x2, tm_x1, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;

@@ -68,12 +68,11 @@ int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, voi
                           void* scale_x, int32_t* sum_X, int T, int K, void* stream);
 
 /* Scratch bytes the GEMM entry points below need for (T, K, N, nnz); the same
- * size serves all of them.  The first W4A4_WORKSPACE_COUNTER_BYTES bytes hold
- * arrival counters that must be zero before the first use (w4a4_workspace_init
- * or a memset); the kernels leave them zero again. */
-#define W4A4_WORKSPACE_COUNTER_BYTES 65536
+ * size serves all of them.  The scratch holds the activations in the layout the
+ * kernels read (expanded codes, transposed group sums, and the per-token scales
+ * when the library quantises); its contents need no initialisation and calls
+ * that share one scratch buffer must be ordered on one stream. */
 size_t w4a4_workspace_bytes(int T, int K, int N, int nnz);
-int w4a4_workspace_init(void* workspace, size_t workspace_bytes, void* stream);
 
 /* Replaces fused_dense_sparse_mma_int4_launch, fused_gemv_decode_launch and
  * fused_gemv_smallT_launch (bindings.cc:187-235; kernels

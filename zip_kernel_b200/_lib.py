@@ -29,7 +29,6 @@ SIGNATURES = {
     "w4a4_device_error": (_INT, [_c.POINTER(_INT), _PTR]),
     "w4a4_activation_quant": (_INT, [_PTR, _LL, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _PTR]),
     "w4a4_workspace_bytes": (_SZ, [_INT, _INT, _INT, _INT]),
-    "w4a4_workspace_init": (_INT, [_PTR, _SZ, _PTR]),
     "w4a4_fused_dense_sparse": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_expanded_codes_bytes": (_SZ, [_INT, _INT]),
     "w4a4_expanded_sums_bytes": (_SZ, [_INT, _INT]),
@@ -100,7 +99,7 @@ def stream_ptr(device) -> int:
 
 
 # ---------------------------------------------------------------------------
-# workspace cache: one zero-initialised buffer per (device, stream), grown on
+# workspace cache: one scratch buffer per (device, stream), grown on
 # demand.  Calls issued on one stream are ordered, so they can share scratch.
 # ---------------------------------------------------------------------------
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
@@ -119,7 +118,7 @@ def workspace(device: torch.device, T: int, K: int, N: int, nnz: int) -> torch.T
                 "run the shape once eagerly (or call zip_kernel_b200.ops.reserve_workspace)"
             )
         grow = max(need, int(buf.numel() * 1.5) if buf is not None else 0)
-        buf = torch.zeros(grow, dtype=torch.uint8, device=device)
+        buf = torch.empty(grow, dtype=torch.uint8, device=device)
         _workspaces[key] = buf
     return buf
 

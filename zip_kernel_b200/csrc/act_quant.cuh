@@ -11,9 +11,13 @@
 // with an approximate division (activation_quant.cu:76-92); its naive kernel and
 // its oracle do not (csrc_naive/activation_quant_naive.cu:132-133).
 //
-// One CTA per token.  The row is read from HBM exactly once with 128-bit loads
-// (or gathered through perm), parked in shared memory as fp16 while the CTA
-// reduces max|x| with warp shuffles, then quantised from shared memory; a thread
+// A token is handled by a thread-block cluster of C CTAs (C = 1 for long
+// prompts, up to 8 when only a few tokens are in flight and one CTA per token
+// would leave the GPU idle).  Each CTA reads its K/C slice of the row from HBM
+// exactly once with 128-bit loads (or gathered through perm), parks it in shared
+// memory as fp16 while it reduces max|x| with warp shuffles, pushes its maximum
+// into the shared memory of every CTA of the cluster and meets them at one
+// cluster barrier; then it quantises its slice from shared memory.  A thread
 // owns 8 consecutive codes = one 32-bit packed word, and 16 neighbouring lanes
 // own one group, so sum_X is a 4-step shuffle reduction.
 #pragma once
@@ -35,6 +39,7 @@ struct QuantParams {
   float* sumxf;           // optional [ceil(T/16)][K/128][16] float group sums, or nullptr
   int T, K;
   int vec_ok;             // 1 when every row start is 16-byte aligned
+  int C;                  // CTAs (cluster size) per token; divides K/128
 };
 
 __device__ __forceinline__ uint2 expand_word(uint32_t w) { return make_uint2(nib_lo_s8(w), nib_hi_s8(w)); }
@@ -52,36 +57,43 @@ __device__ __forceinline__ float half_abs_max8(const uint4& v, float m) {
 __global__ void __launch_bounds__(QUANT_THREADS)
 act_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(16) unsigned char quant_smem[];
-  uint4* row = reinterpret_cast<uint4*>(quant_smem);          // K/8 chunks of 8 halfs
+  uint4* row = reinterpret_cast<uint4*>(quant_smem);          // this CTA's chunks of 8 halfs
   __shared__ float warp_max[QUANT_THREADS / 32];
+  __shared__ float peer_max[8];
 
-  // Let a dependent GEMM kernel start its weight prefetch while this one runs.
+  // Let the next kernel in the stream be scheduled early; then wait until the
+  // producer of X (and every earlier user of the output buffers) has finished.
   grid_launch_dependents();
+  grid_dependency_wait();
 
-  const int t = blockIdx.x;
+  const int C = p.C;
+  const int t = blockIdx.x / C;
+  const int rank = blockIdx.x - t * C;
   const int tid = threadIdx.x;
-  const int nchunk = p.K >> 3;
+  const int nchunk_row = p.K >> 3;
+  const int c_lo = rank * (nchunk_row / C), c_hi = c_lo + nchunk_row / C;   // slice, a multiple of 16 chunks
   const __half* xrow = p.X + (long long)t * p.ldx;
 
   float m = 0.f;
   if (p.perm == nullptr && p.vec_ok) {
     const uint4* src = reinterpret_cast<const uint4*>(xrow);
-    for (int c = tid; c < nchunk; c += QUANT_THREADS) {
+    for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
       uint4 v = ld_plain(src + c);
-      row[c] = v;
+      row[c - c_lo] = v;
       m = half_abs_max8(v, m);
     }
   } else {
-    for (int c = tid; c < nchunk; c += QUANT_THREADS) {
+    for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
       __align__(16) __half h[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
-        int k = c * 8 + j;
-        int src = p.perm ? ld_plain(p.perm + k) : k;
+        const int k = c * 8 + j;
+        int src = k;
+        if (p.perm) src = p.perm[k];
         h[j] = xrow[src];
       }
       uint4 v = *reinterpret_cast<uint4*>(h);
-      row[c] = v;
+      row[c - c_lo] = v;
       m = half_abs_max8(v, m);
     }
   }
@@ -92,27 +104,39 @@ act_quant_kernel(const QuantParams p) {
   m = warp_max[0];
 #pragma unroll
   for (int w = 1; w < QUANT_THREADS / 32; ++w) m = fmaxf(m, warp_max[w]);
+  if (C > 1) {
+    // push this CTA's maximum into slot `rank` of every CTA of the cluster
+    if (tid < C) {
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(smem_u32(&peer_max[rank])), "r"(tid));
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote), "f"(m) : "memory");
+    }
+    __syncwarp();
+    // every thread of every CTA of the cluster arrives here: hardware barrier, no spin
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    for (int c = 0; c < C; ++c) m = fmaxf(m, peer_max[c]);
+  }
 
   const __half scale16 = __float2half_rn(__fdiv_rn(m, 7.0f));
   const float s = __half2float(scale16);
   const bool zero_row = !(s > 0.f);
   const float s_safe = zero_row ? 1.0f : s;
-  if (tid == 0) p.scale_x[t] = scale16;
+  if (tid == 0 && rank == 0) p.scale_x[t] = scale16;
 
   uint32_t* out = p.X_s4 ? reinterpret_cast<uint32_t*>(p.X_s4 + (long long)t * (p.K >> 1)) : nullptr;
   int* sums = p.sum_X ? p.sum_X + (long long)t * (p.K >> 7) : nullptr;
   const int ng = p.K >> 7;
   float* sumsf = p.sumxf ? p.sumxf + ((long long)(t >> 4) * ng) * 16 + (t & 15) : nullptr;
-  // All lanes of a warp run the same number of iterations (nchunk is a multiple
-  // of 16 and lanes are consecutive), so the shuffles below are convergent for
-  // every 16-lane half that holds a live group.
-  for (int c0 = 0; c0 < nchunk; c0 += QUANT_THREADS) {
+  // All lanes of a warp run the same number of iterations (the slice is a multiple
+  // of 16 chunks and lanes are consecutive), so the shuffles below are convergent
+  // for every 16-lane half that holds a live group.
+  for (int c0 = c_lo; c0 < c_hi; c0 += QUANT_THREADS) {
     const int c = c0 + tid;
-    const bool live = c < nchunk;
+    const bool live = c < c_hi;
     uint32_t word = 0;
     int sum = 0;
     if (live) {
-      uint4 v = row[c];
+      uint4 v = row[c - c_lo];
       const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -154,6 +178,7 @@ struct ExpandParams {
 
 __global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandParams p) {
   grid_launch_dependents();
+  grid_dependency_wait();
   const long long words = (long long)p.T * (p.K >> 3);
   const long long stride = (long long)gridDim.x * blockDim.x;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(p.X_s4);

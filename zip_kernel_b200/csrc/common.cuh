@@ -13,7 +13,9 @@ constexpr int BCOL = 128;   // quantisation group / residual block columns (arch
 constexpr int GROUP_BYTES = BCOL / 2;   // packed bytes of one group of one row
 
 // Every device-side wait polls at most this many times, then records an error
-// and gives up, so a logic error can never leave the GPU spinning.
+// and gives up, so a logic error can never leave the GPU spinning.  (A long
+// hardware suspend hint on try_wait was measured slower than plain polling:
+// the wake-up adds latency to every pipeline step.)
 constexpr uint32_t WAIT_POLL_LIMIT = 1u << 22;
 
 // Device error word: 0 = ok.  Non-zero = (site id << 8) | detail of the first
@@ -65,7 +67,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int site) {
   for (uint32_t i = 0; i < WAIT_POLL_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (i > 1024) __nanosleep(64);
+    if (i > 4096) __nanosleep(64);
   }
   record_error(site, parity);
   return false;
@@ -133,7 +135,7 @@ __device__ __forceinline__ uint32_t nib_hi_s8(uint32_t w) { return sext4_bytes((
 // D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_m16n8k32_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                                 uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};"
       : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])

@@ -115,7 +115,7 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
 // D(16x8,s32) = A(16x32,s8,row) * B(32x8,s8,col) with a zero accumulator input
 __device__ __forceinline__ void mma_m16n8k32_s8_first(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                                       uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
       : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
@@ -167,6 +167,9 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
   uint64_t* empty = full + STAGES;
   int* misc = reinterpret_cast<int*>(empty + STAGES);     // [1] = a wait gave up
 
+  // the next kernel in the stream may be scheduled as soon as every CTA got here;
+  // it waits for this grid's completion before it touches anything we use
+  grid_launch_dependents();
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;

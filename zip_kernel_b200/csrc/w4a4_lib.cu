@@ -107,20 +107,16 @@ int make_map_x(CUtensorMap* m, const void* XE, int T, int K, uint32_t groups, ui
 }
 
 // ------------------------------------------------------------------ workspace layout
-constexpr size_t WS_PARTIAL_TILES = 1024;                                   // shared block-row pieces
-constexpr size_t WS_PARTIAL_BYTES = WS_PARTIAL_TILES * 128 * 16 * 4;       // 8 MiB
+// Scratch for activations in the layout the GEMM kernels read: per-token scales
+// (only when the library quantises), expanded codes and transposed group sums.
 struct WsLayout {
-  size_t counters, partial, x_s4, scale_x, sum_x, xe, sumxf, total;
+  size_t scale_x, xe, sumxf, total;
 };
 WsLayout ws_layout(int T, int K) {
   WsLayout w;
   const size_t ng = K / 128, tok_tiles = (T + 15) / 16;
   size_t off = 0;
-  w.counters = off; off += W4A4_WORKSPACE_COUNTER_BYTES;
-  w.partial = off;  off += WS_PARTIAL_BYTES;
-  w.x_s4 = off;     off += round_up((size_t)T * (K / 2), 256);
   w.scale_x = off;  off += round_up((size_t)T * 2, 256);
-  w.sum_x = off;    off += round_up((size_t)T * ng * 4, 256);
   w.xe = off;       off += round_up((size_t)T * K, 1024);
   w.sumxf = off;    off += round_up(tok_tiles * ng * 16 * 4, 256);
   w.total = off;
@@ -136,15 +132,17 @@ DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count) {
   DecodePlan p;
   p.row_tiles = (N + dec::ROWS - 1) / dec::ROWS;
   p.tok_tiles = (T + dec::TOK - 1) / dec::TOK;
-  // aim at about two resident CTAs per SM; a block-row is never cut finer than its steps
+  // The SMs are limited by instruction issue before they are limited by shared-memory
+  // capacity, so one CTA per SM (or a little more) is the sweet spot: take the largest
+  // power-of-two cluster that keeps the grid within ~1.4 CTAs per SM.
   const long long base = (long long)p.row_tiles * p.tok_tiles;
-  long long s = (2LL * sm_count + base / 2) / base;
+  long long s = 1;
+  while (s * 2 <= dec::MAX_CLUSTER && base * s * 2 * 10 <= 14LL * sm_count) s *= 2;
   // tuning override for A/B experiments
   static const int env_split = getenv("W4A4_DECODE_SPLIT") ? atoi(getenv("W4A4_DECODE_SPLIT")) : 0;
   if (env_split > 0) s = env_split;
   if (s > dec::MAX_CLUSTER) s = dec::MAX_CLUSTER;
-  if (s > dense_steps) s = dense_steps;
-  if (s < 1) s = 1;
+  while (s > dense_steps && s > 1) s /= 2;
   p.split = (int)s;
   return p;
 }
@@ -173,6 +171,35 @@ struct GemmArgs {
   cudaStream_t stream;
 };
 
+// Launch with the programmatic-dependent-launch attribute (the kernels call
+// griddepcontrol.wait before they touch memory another kernel may still use) and,
+// for cluster > 1, a 1-D thread-block cluster.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, int cluster,
+                      Args... args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof cfg);
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[n].val.programmaticStreamSerializationAllowed = 1;
+  ++n;
+  if (cluster > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, args...);
+}
+
 int launch_expand(const GemmArgs& a, void* XE, float* sumxf, DeviceInfo* dev) {
   using namespace w4a4;
   ExpandParams e;
@@ -185,8 +212,7 @@ int launch_expand(const GemmArgs& a, void* XE, float* sumxf, DeviceInfo* dev) {
   const long long words = (long long)a.T * (a.K / 8);
   long long blocks = (words + 255) / 256;
   if (blocks > 4LL * dev->sm_count) blocks = 4LL * dev->sm_count;
-  expand_activations_kernel<<<(int)blocks, 256, 0, a.stream>>>(e);
-  cudaError_t err = cudaGetLastError();
+  cudaError_t err = launch_ex(expand_activations_kernel, dim3((unsigned)blocks), dim3(256), 0, a.stream, 1, e);
   if (err != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "expand kernel launch: %s", cudaGetErrorString(err));
   return W4A4_OK;
 }
@@ -202,16 +228,15 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   DecodePlan plan = plan_decode(a.T, a.N, dense_steps > 0 ? dense_steps : 1, dev->sm_count);
   if ((long long)plan.row_tiles * plan.split > 2147483647LL)
     return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d is too large", a.N);
-  const WsLayout wl = ws_layout(a.T, a.K);
-  if (a.ws == nullptr || a.ws_bytes < wl.total)
-    return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, a.ws_bytes);
-  char* ws = static_cast<char*>(a.ws);
-
   // expanded activations: given by the caller, or built here from the packed codes
   const void* XE = a.XE;
   const float* sumxf = a.sumxf;
   bool pdl = a.pdl;
   if (XE == nullptr) {
+    const WsLayout wl = ws_layout(a.T, a.K);
+    if (a.ws == nullptr || a.ws_bytes < wl.total)
+      return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, a.ws_bytes);
+    char* ws = static_cast<char*>(a.ws);
     int rc = launch_expand(a, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf), dev);
     if (rc) return rc;
     XE = ws + wl.xe;
@@ -265,35 +290,15 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(decode): %s", cudaGetErrorString(e));
 
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof cfg);
-  cfg.gridDim = dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1);
-  cfg.blockDim = dim3(dec::THREADS);
-  cfg.dynamicSmemBytes = smem;
-  cfg.stream = a.stream;
-  cudaLaunchAttribute attr[2];
-  int n_attr = 0;
-  if (pdl) {
-    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
-    ++n_attr;
-  }
-  if (plan.split > 1) {
-    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
-    attr[n_attr].val.clusterDim.x = plan.split;
-    attr[n_attr].val.clusterDim.y = 1;
-    attr[n_attr].val.clusterDim.z = 1;
-    ++n_attr;
-  }
-  cfg.attrs = attr;
-  cfg.numAttrs = n_attr;
-  e = cudaLaunchKernelEx(&cfg, kern, tm_low, tm_x2, tm_x1, p);
+  (void)pdl;
+  e = launch_ex(kern, dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
+                plan.split, tm_low, tm_x2, tm_x1, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }
 
 int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x, int32_t* sum_X,
-                 void* XE, float* sumxf, int T, int K, cudaStream_t stream) {
+                 void* XE, float* sumxf, int T, int K, cudaStream_t stream, int sm_count) {
   using namespace w4a4;
   QuantParams q;
   q.X = static_cast<const __half*>(X);
@@ -307,14 +312,19 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   q.T = T;
   q.K = K;
   q.vec_ok = (aligned(X, 16) && (ldx % 8 == 0)) ? 1 : 0;
-  const size_t smem = (size_t)K * 2;
+  // few tokens: spread each token over a cluster so the row is read by many SMs at once
+  int C = 1;
+  const int ng = K / 128;
+  for (int c = 8; c > 1; c >>= 1)
+    if (ng % c == 0 && (long long)T * c <= 2LL * sm_count) { C = c; break; }
+  q.C = C;
+  const size_t smem = (size_t)K * 2 / C;
   if (smem > 200 * 1024) return fail(W4A4_ERR_UNSUPPORTED, "K=%d exceeds the quantisation kernel's row buffer", K);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(quant): %s", cudaGetErrorString(e));
   }
-  act_quant_kernel<<<T, QUANT_THREADS, smem, stream>>>(q);
-  cudaError_t e = cudaGetLastError();
+  cudaError_t e = launch_ex(act_quant_kernel, dim3((unsigned)((long long)T * C)), dim3(QUANT_THREADS), smem, stream, C, q);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "quant kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }
@@ -396,7 +406,11 @@ int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, voi
   CHECK_ARG(ldx >= K, "ldx (%lld) must be >= K (%d)", ldx, K);
   if (!aligned(X, 2) || !aligned(X_s4, 4) || !aligned(sum_X, 4) || !aligned(scale_x, 2))
     return fail(W4A4_ERR_ALIGNMENT, "activation_quant pointer alignment");
-  return launch_quant(X, ldx, perm, X_s4, scale_x, sum_X, nullptr, nullptr, T, K, static_cast<cudaStream_t>(stream));
+  DeviceInfo* dev = nullptr;
+  rc = current_device(&dev);
+  if (rc) return rc;
+  return launch_quant(X, ldx, perm, X_s4, scale_x, sum_X, nullptr, nullptr, T, K, static_cast<cudaStream_t>(stream),
+                      dev->sm_count);
 }
 
 size_t w4a4_workspace_bytes(int T, int K, int N, int nnz) {
@@ -404,15 +418,6 @@ size_t w4a4_workspace_bytes(int T, int K, int N, int nnz) {
   (void)nnz;
   if (T < 1 || K < 128) return 0;
   return ws_layout(T, K).total;
-}
-
-int w4a4_workspace_init(void* workspace, size_t workspace_bytes, void* stream) {
-  CHECK_ARG(workspace != nullptr, "workspace is NULL");
-  if (workspace_bytes < W4A4_WORKSPACE_COUNTER_BYTES)
-    return fail(W4A4_ERR_WORKSPACE, "workspace smaller than the counter block");
-  cudaError_t e = cudaMemsetAsync(workspace, 0, W4A4_WORKSPACE_COUNTER_BYTES, static_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaMemsetAsync: %s", cudaGetErrorString(e));
-  return W4A4_OK;
 }
 
 int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
@@ -512,8 +517,11 @@ int w4a4_fused_quant_dense_sparse(const void* X, long long ldx, const int32_t* p
     return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, workspace_bytes);
   char* ws = static_cast<char*>(workspace);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  DeviceInfo* dev = nullptr;
+  rc = current_device(&dev);
+  if (rc) return rc;
   rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
-                    T, K, s);
+                    T, K, s, dev->sm_count);
   if (rc) return rc;
   GemmArgs a{};
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;

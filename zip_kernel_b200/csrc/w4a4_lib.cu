@@ -132,12 +132,12 @@ DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count) {
   DecodePlan p;
   p.row_tiles = (N + dec::ROWS - 1) / dec::ROWS;
   p.tok_tiles = (T + dec::TOK - 1) / dec::TOK;
-  // The SMs are limited by instruction issue before they are limited by shared-memory
-  // capacity, so one CTA per SM (or a little more) is the sweet spot: take the largest
-  // power-of-two cluster that keeps the grid within ~1.4 CTAs per SM.
+  // Largest power-of-two cluster that keeps the grid within the two CTAs per SM that
+  // fit at once (a grid that needs a second wave costs far more than it gains;
+  // measured on the Llama-3-8B decode shapes with dependent launches enabled).
   const long long base = (long long)p.row_tiles * p.tok_tiles;
   long long s = 1;
-  while (s * 2 <= dec::MAX_CLUSTER && base * s * 2 * 10 <= 14LL * sm_count) s *= 2;
+  while (s * 2 <= dec::MAX_CLUSTER && base * s * 2 * 10 <= 18LL * sm_count) s *= 2;
   // tuning override for A/B experiments
   static const int env_split = getenv("W4A4_DECODE_SPLIT") ? atoi(getenv("W4A4_DECODE_SPLIT")) : 0;
   if (env_split > 0) s = env_split;
@@ -185,9 +185,13 @@ cudaError_t launch_ex(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem
   cfg.stream = stream;
   cudaLaunchAttribute attr[2];
   int n = 0;
-  attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[n].val.programmaticStreamSerializationAllowed = 1;
-  ++n;
+  // W4A4_NO_PDL=1 switches programmatic dependent launch off (A/B experiments)
+  static const bool no_pdl = getenv("W4A4_NO_PDL") && atoi(getenv("W4A4_NO_PDL")) != 0;
+  if (!no_pdl) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
   if (cluster > 1) {
     attr[n].id = cudaLaunchAttributeClusterDimension;
     attr[n].val.clusterDim.x = cluster;

@@ -138,6 +138,34 @@ int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t*
                            int32_t* acc_hi, int T, int K, int N, int nnz, int flags, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* No counterpart in the reference (its launchers allocate split-K partials with
+ * torch::empty, fused_dense_sparse_mma_int4.cu:1873-1879).
+ *
+ * Same computation and arguments as w4a4_fused_dense_sparse, for callers that
+ * cannot allocate device memory and therefore have no workspace to pass: code
+ * that runs inside someone else's CUDA-graph capture or allocator-free serving
+ * loop, a plugin whose host owns every allocation, a process whose memory pool is
+ * already carved up.  The scratch the call needs (the activations in the layout
+ * the GEMM reads) lives in an array that is part of the library image instead,
+ * so the size is capped: T <= W4A4_NOALLOC_MAX_T tokens and
+ * K <= W4A4_NOALLOC_MAX_K features (about 528 KiB, held by every GPU that loads
+ * the library until the process exits).  Larger shapes return
+ * W4A4_ERR_UNSUPPORTED with a message naming the limits.  The call itself never
+ * calls cudaMalloc / cudaFree or any allocating routine.
+ *
+ * The first call on a device looks up the device address of that array (one
+ * cudaGetSymbolAddress with that device current); make that first call outside
+ * any stream capture.  All calls on a device share the one array and it keeps
+ * the previous call's contents (the part that must start clean is cleared on
+ * every call): two calls whose GPU work overlaps - different streams without an
+ * ordering between them - race on it.  Order them on one stream. */
+#define W4A4_NOALLOC_MAX_T 16
+#define W4A4_NOALLOC_MAX_K 32768
+int w4a4_fused_dense_sparse_noalloc(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                                    const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
+                                    const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y,
+                                    int T, int K, int N, int nnz, int flags, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -37,6 +37,7 @@ SIGNATURES = {
     "w4a4_dense_gemm": (_INT, [_PTR] * 7 + [_INT] * 4 + [_PTR, _SZ, _PTR]),
     "w4a4_sparse_gemm": (_INT, [_PTR] * 7 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_fused_quant_dense_sparse": (_INT, [_PTR, _LL] + [_PTR] * 8 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_fused_dense_sparse_noalloc": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR]),
     "w4a4_dump_accumulators": (_INT, [_PTR] * 7 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
 }
 

@@ -369,6 +369,39 @@ int run_gemm(GemmArgs& a) {
   return launch_decode(a, dev);
 }
 
+// ------------------------------------------------------------------ built-in scratch
+// Scratch for w4a4_fused_dense_sparse_noalloc: expanded activation codes of up to
+// NOALLOC_MAX_T tokens of up to NOALLOC_MAX_K features, followed by their
+// transposed group sums.  It lives in the library image, so every GPU that loads
+// the library holds these ~528 KiB until the process exits.
+constexpr int NOALLOC_MAX_T = W4A4_NOALLOC_MAX_T;
+constexpr int NOALLOC_MAX_K = W4A4_NOALLOC_MAX_K;
+constexpr size_t NOALLOC_XE_BYTES = (size_t)NOALLOC_MAX_T * NOALLOC_MAX_K;
+constexpr size_t NOALLOC_SUMS_BYTES = (size_t)(NOALLOC_MAX_K / 128) * 16 * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_XE_BYTES + NOALLOC_SUMS_BYTES];
+
+// In host code `g_noalloc_scratch` is only a handle for the symbol, not an address
+// a kernel can use.  The device address is looked up once per device, with that
+// device current, and remembered.
+void* g_noalloc_addr[64] = {};
+
+int noalloc_scratch_address(void** out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(W4A4_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_noalloc_addr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(W4A4_ERR_LAUNCH, "cudaGetSymbolAddress(built-in scratch): %s", cudaGetErrorString(e));
+    g_noalloc_addr[dev] = p;
+  }
+  *out = g_noalloc_addr[dev];
+  return W4A4_OK;
+}
+
 }  // namespace
 
 // ===================================================================== C ABI
@@ -547,6 +580,46 @@ int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t*
   a.T = T; a.K = K; a.N = N; a.nnz = acc_hi ? nnz : 0; a.flags = flags;
   a.do_dense = acc != nullptr; a.sparse_weight = 16.f; a.pdl = false;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
+  return run_gemm(a);
+}
+
+int w4a4_fused_dense_sparse_noalloc(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
+                                    const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
+                                    const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y, int T,
+                                    int K, int N, int nnz, int flags, void* stream) {
+  int rc = check_common(T, K, N, nnz);
+  if (rc) return rc;
+  CHECK_ARG(Y && X_s4 && zero_u4 && sum_X && scale_x, "NULL tensor pointer");
+  if (T > NOALLOC_MAX_T || K > NOALLOC_MAX_K)
+    return fail(W4A4_ERR_UNSUPPORTED,
+                "T=%d, K=%d exceed the built-in scratch of w4a4_fused_dense_sparse_noalloc (T <= %d, K <= %d); "
+                "use w4a4_fused_dense_sparse with a caller-provided workspace",
+                T, K, NOALLOC_MAX_T, NOALLOC_MAX_K);
+  if (!aligned(X_s4, 4)) return fail(W4A4_ERR_ALIGNMENT, "X_s4 must be 4-byte aligned");
+  void* scratch = nullptr;
+  rc = noalloc_scratch_address(&scratch);      // first call on a device resolves the address
+  if (rc) return rc;
+  DeviceInfo* dev = nullptr;
+  rc = current_device(&dev);
+  if (rc) return rc;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* xe = static_cast<char*>(scratch);
+  float* sums = reinterpret_cast<float*>(xe + NOALLOC_XE_BYTES);
+  // The array keeps whatever the previous call left.  The codes of the T live
+  // tokens are overwritten below and rows past T are never read; the group sums of
+  // the token tile are cleared so that no stale lane of an earlier call is read.
+  cudaError_t e = cudaMemsetAsync(sums, 0, (size_t)(K / 128) * 16 * sizeof(float), s);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaMemsetAsync(built-in scratch): %s", cudaGetErrorString(e));
+  GemmArgs x{};
+  x.X_s4 = X_s4; x.sum_X = sum_X; x.T = T; x.K = K; x.stream = s;
+  rc = launch_expand(x, xe, sums, dev);
+  if (rc) return rc;
+  GemmArgs a{};
+  a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
+  a.XE = xe; a.sumxf = sums; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.scale_x = scale_x; a.Y = Y;
+  a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags | W4A4_FLAG_FORCE_STREAM;
+  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = true;
+  a.ws = nullptr; a.ws_bytes = 0; a.stream = s;
   return run_gemm(a);
 }
 

@@ -1,8 +1,437 @@
-// Kernel 2 (tensor-core path) - placeholder until the tcgen05 kernel lands.
+// Kernel 2: tensor-core fused GEMM for many tokens (prefill), tcgen05 / TMEM.
+// Replaces the reference's mma.sync m16n8k64 s4 kernels
+// (cuda_kernel/csrc/fused_dense_sparse/fused_dense_sparse_mma_int4.cu:184-1190,
+// dense_gemm/dense_gemm_mma_int4.cu:39-431, sparse_gemm/sparse_gemm_mma_int4.cu:25-253).
+//
+//   Y[n,t] = fp16( sx[t] * ( sum_g s[n,g] * (acc[g,n,t] - z[n,g] * sumX[t,g])
+//                            + w * sum_{blk in block-row} s[n,bc] * acc_hi[blk,n,t] ) )
+//
+// sm_100a tensor cores have no 4-bit integer MMA, so nibbles are widened to s8 on
+// the way: a CTA owns 128 weight rows (one block-row = MMA M) x TN tokens (MMA N).
+// Per K-group of 128 (and per residual block of the block-row, which is just one
+// more K-step):
+//   * the producer warp issues two non-multicast TMA copies: the packed weight
+//     tile (128 x 64 bytes) and the tokens' expanded codes (TN x 128 bytes,
+//     128-byte swizzle = the K-major operand layout tcgen05 reads directly);
+//   * four unpack warps widen the weight tile into a second shared-memory ring
+//     in the same swizzled K-major layout (s8 lanes scaled by 16, three logic ops
+//     per 8 codes, same element permutation as the activations);
+//   * one thread issues four tcgen05.mma kind::i8 (K = 32 each) into a fresh
+//     int32 accumulator in TMEM (two accumulator buffers alternate) and commits
+//     to mbarriers that release the operand slots and publish the accumulator;
+//   * eight fold warps read the accumulator with tcgen05.ld and fold it in fp32:
+//     y += acc * (s/16) - (s*z) * sumX  (per-(row, group) scales make this drain
+//     per group inherent to the contract), keeping y (128 x TN fp32) in registers.
+// Epilogue: y * scale_x -> fp16 -> Y.  Every mbarrier wait is bounded; a wait
+// that gives up records an error, all roles fall through to the common exit and
+// the TMEM allocation is released.
 #pragma once
+
+#include <cuda.h>
+
 #include "common.cuh"
+
 namespace w4a4 {
 namespace pre {
-inline bool supported(int, int, int) { return false; }
+
+constexpr int ROWS = 128;                 // MMA M
+constexpr int TN = 128;                   // tokens per CTA = MMA N
+constexpr int W_STAGES = 4;               // packed weight tiles (8 KB each)
+constexpr int AB_STAGES = 3;              // widened weight tiles / activation tiles (16 KB each)
+constexpr int WP_BYTES = ROWS * GROUP_BYTES;      // 8192
+constexpr int A_BYTES = ROWS * BCOL;              // 16384
+constexpr int X_BYTES = TN * BCOL;                // 16384
+constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
+constexpr int TMEM_COLS = 2 * TN;                 // two int32 accumulator buffers
+
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_UNPACK0 = 2, N_UNPACK_WARPS = 4, WARP_FOLD0 = 6, N_FOLD_WARPS = 8;
+constexpr int THREADS = (WARP_FOLD0 + N_FOLD_WARPS) * 32;   // 448
+constexpr int FOLD_THREADS = N_FOLD_WARPS * 32;
+constexpr int COLS_PER_FOLD = TN / 2;             // a fold thread owns one row and half of the tokens
+
+enum : int {
+  SITE_PRE_WEMPTY = 16, SITE_PRE_WFULL, SITE_PRE_AEMPTY, SITE_PRE_AFULL, SITE_PRE_XEMPTY, SITE_PRE_XFULL,
+  SITE_PRE_ACCEMPTY, SITE_PRE_ACCFULL, SITE_PRE_DUMP
+};
+
+struct Params {
+  const int* hp_row_offsets;
+  const int* hp_col_indices;
+  const __half* scale_u4;   // (N, ng)
+  const __half* zero_u4;    // (N, ng) or nullptr
+  const float* sumxf;       // [ceil(T/16)][ng][16] or nullptr
+  const __half* scale_x;    // (T)
+  __half* Y;
+  long long y_stride_n, y_stride_t;
+  int* acc_dump;            // optional (ng, N, T) int32
+  int* acc_hi_dump;         // optional (nnz, 128, T) int32
+  int T, K, N, ng, nnz;
+  int nd;                   // dense K-steps (ng, or 0 when the dense part is off)
+  int sparse_on;
+  int sz_vec;
+  float sparse_weight;
+};
+
+inline bool supported(int T, int K, int N) { return T >= 1 && K >= 128 && N >= 1; }
+
+struct SmemLayout {
+  static constexpr size_t wp = 0;
+  static constexpr size_t a = wp + (size_t)W_STAGES * WP_BYTES;
+  static constexpr size_t x = a + (size_t)AB_STAGES * A_BYTES;
+  static constexpr size_t sz = x + (size_t)AB_STAGES * X_BYTES;                 // float2 [SZ_CHUNK][128]
+  static constexpr size_t sums = sz + (size_t)SZ_CHUNK * ROWS * 8;              // float  [SZ_CHUNK][TN]
+  static constexpr size_t sxs = sums + (size_t)SZ_CHUNK * TN * 4;               // float  [TN]
+  static constexpr size_t bars = sxs + (size_t)TN * 4;
+  static constexpr size_t total = bars + 256;
+};
+inline size_t smem_bytes() { return 1024 + SmemLayout::total; }
+
+// ---------------------------------------------------------------- tcgen05 wrappers
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(ncols)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// K-major operand tile of 128-byte rows under the 128-byte swizzle: 8-row groups are 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);        // start address, 16-byte units
+  d |= (uint64_t)1 << 16;                                  // leading byte offset (unused with swizzle)
+  d |= (uint64_t)(1024 >> 4) << 32;                        // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;                                  // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                                  // SWIZZLE_128B
+  return d;
+}
+// kind::i8, s8 x s8 -> s32, both operands K-major, M = 128, N = TN
+constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+__device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+      : "memory");
+}
+// arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+template <bool DUMP>
+__global__ void __launch_bounds__(THREADS, 1)
+prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wh,
+                    const __grid_constant__ CUtensorMap tm_x, const Params p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  unsigned char* wp_ring = sm + SmemLayout::wp;
+  unsigned char* a_ring = sm + SmemLayout::a;
+  unsigned char* x_ring = sm + SmemLayout::x;
+  float2* szs = reinterpret_cast<float2*>(sm + SmemLayout::sz);
+  float* sums = reinterpret_cast<float*>(sm + SmemLayout::sums);
+  float* sxs = reinterpret_cast<float*>(sm + SmemLayout::sxs);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SmemLayout::bars);
+  uint64_t* w_full = bars;                      // [W_STAGES]
+  uint64_t* w_empty = w_full + W_STAGES;        // [W_STAGES]
+  uint64_t* a_full = w_empty + W_STAGES;        // [AB_STAGES]
+  uint64_t* a_empty = a_full + AB_STAGES;       // [AB_STAGES]
+  uint64_t* x_full = a_empty + AB_STAGES;       // [AB_STAGES]
+  uint64_t* x_empty = x_full + AB_STAGES;       // [AB_STAGES]
+  uint64_t* acc_full = x_empty + AB_STAGES;     // [2]
+  uint64_t* acc_empty = acc_full + 2;           // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  grid_launch_dependents();
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int r = blockIdx.x;                     // block-row
+  const int row0 = r * ROWS;
+  const int tok0 = blockIdx.y * TN;
+
+  if (tid == 0) {
+    for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
+    for (int i = 0; i < AB_STAGES; ++i) {
+      mbar_init(&a_full[i], N_UNPACK_WARPS); mbar_init(&a_empty[i], 1);
+      mbar_init(&x_full[i], 1);              mbar_init(&x_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], N_FOLD_WARPS); }
+    mbar_fence_init();
+    tma_prefetch_desc(&tm_w);
+    tma_prefetch_desc(&tm_wh);
+    tma_prefetch_desc(&tm_x);
+  }
+  if (warp == WARP_MMA) tmem_alloc(tmem_slot, TMEM_COLS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  // K-steps of this CTA: the dense groups, then the residual blocks of the block-row
+  int b_lo = 0, b_hi = 0;
+  if (p.sparse_on) {
+    b_lo = ld_plain(p.hp_row_offsets + r);
+    b_hi = ld_plain(p.hp_row_offsets + r + 1);
+  }
+  const int n_steps = p.nd + (b_hi - b_lo);
+
+  if (warp == WARP_TMA) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      bool ok = true;
+      // weights do not depend on the preceding kernel: fill the packed ring first
+      const int n_pre = min(W_STAGES, n_steps);
+      auto issue_w = [&](int n, int st) {
+        mbar_arrive_expect_tx(&w_full[st], WP_BYTES);
+        if (n < p.nd) tma_load_2d(wp_ring + st * WP_BYTES, &tm_w, n * GROUP_BYTES, row0, &w_full[st]);
+        else          tma_load_2d(wp_ring + st * WP_BYTES, &tm_wh, 0, (b_lo + n - p.nd) * BROW, &w_full[st]);
+      };
+      for (int n = 0; n < n_pre; ++n) issue_w(n, n);
+      grid_dependency_wait();
+      int ws = 0, xs = 0;
+      uint32_t wph = 1, xph = 1;
+      for (int n = 0; n < n_steps && ok; ++n) {
+        if (n >= n_pre) {
+          ok = mbar_wait(&w_empty[ws], wph, SITE_PRE_WEMPTY);
+          if (!ok) break;
+          issue_w(n, ws);
+        }
+        if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
+        ok = mbar_wait(&x_empty[xs], xph, SITE_PRE_XEMPTY);
+        if (!ok) break;
+        const int g = n < p.nd ? n : ld_plain(p.hp_col_indices + b_lo + n - p.nd);
+        mbar_arrive_expect_tx(&x_full[xs], X_BYTES);
+        tma_load_3d(x_ring + xs * X_BYTES, &tm_x, 0, g, tok0, &x_full[xs]);
+        if (++xs == AB_STAGES) { xs = 0; xph ^= 1; }
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      bool ok = true;
+      int st = 0;
+      uint32_t ph = 0;
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const int buf = n & 1;
+        ok = mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, SITE_PRE_ACCEMPTY);
+        if (ok) ok = mbar_wait(&a_full[st], ph, SITE_PRE_AFULL);
+        if (ok) ok = mbar_wait(&x_full[st], ph, SITE_PRE_XFULL);
+        if (!ok) break;
+        tc_fence_after();
+        const uint64_t adesc = smem_desc_sw128(a_ring + st * A_BYTES);
+        const uint64_t bdesc = smem_desc_sw128(x_ring + st * X_BYTES);
+        const uint32_t d = tmem_base + buf * TN;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) umma_i8(d, adesc + j * 2, bdesc + j * 2, j > 0);   // +32 bytes per K = 32
+        umma_commit(&a_empty[st]);
+        umma_commit(&x_empty[st]);
+        umma_commit(&acc_full[buf]);
+        if (++st == AB_STAGES) { st = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp < WARP_FOLD0) {
+    // ------------------------------------------------------------ unpack warps
+    const int ut = tid - WARP_UNPACK0 * 32;      // 0..127
+    bool ok = true;
+    int ws = 0, as = 0;
+    uint32_t wph = 0, aph = 1;
+    for (int n = 0; n < n_steps; ++n) {
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&w_full[ws], wph, SITE_PRE_WFULL));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], aph, SITE_PRE_AEMPTY));
+      if (ok) {
+        tc_fence_after();      // the slot was last read by tcgen05.mma
+        const unsigned char* src = wp_ring + ws * WP_BYTES;
+        unsigned char* dst = a_ring + as * A_BYTES;
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+          const int item = pass * 128 + ut;      // 16 packed bytes = 32 codes
+          const int row = item >> 2, pc = item & 3;
+          const uint4 w = *reinterpret_cast<const uint4*>(src + item * 16);
+          const uint4 o0 = make_uint4(nib_lo_x16(w.x), nib_hi_x16(w.x), nib_lo_x16(w.y), nib_hi_x16(w.y));
+          const uint4 o1 = make_uint4(nib_lo_x16(w.z), nib_hi_x16(w.z), nib_lo_x16(w.w), nib_hi_x16(w.w));
+          unsigned char* drow = dst + row * BCOL;
+          *reinterpret_cast<uint4*>(drow + (((2 * pc) ^ (row & 7)) << 4)) = o0;
+          *reinterpret_cast<uint4*>(drow + (((2 * pc + 1) ^ (row & 7)) << 4)) = o1;
+        }
+        fence_proxy_async_smem();                // generic-proxy writes -> visible to the tensor core
+      }
+      __syncwarp();
+      if (ok && lane == 0) {
+        mbar_arrive(&w_empty[ws]);
+        mbar_arrive(&a_full[as]);
+      }
+      if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
+      if (++as == AB_STAGES) { as = 0; aph ^= 1; }
+    }
+  } else {
+    // ------------------------------------------------------------ fold warps
+    const int ft = tid - WARP_FOLD0 * 32;        // 0..255
+    const int quarter = warp & 3;                // TMEM lanes this warp may read: 32*quarter .. +31
+    const int chalf = (warp - WARP_FOLD0) >> 2;  // which half of the tokens
+    const int rl = quarter * 32 + lane;          // local row
+    const int row = row0 + rl;
+    const int c0 = chalf * COLS_PER_FOLD;
+    grid_dependency_wait();
+    for (int i = ft; i < TN; i += FOLD_THREADS)
+      sxs[i] = (tok0 + i < p.T && p.scale_x) ? __half2float(ld_plain(p.scale_x + tok0 + i)) : 0.f;
+    asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");
+
+    float y[COLS_PER_FOLD];
+#pragma unroll
+    for (int i = 0; i < COLS_PER_FOLD; ++i) y[i] = 0.f;
+
+    // scale/zero window: thread ft fetches 8 groups of row ft/2; sums window: 16 groups x TN tokens
+    const int lrow = ft >> 1, lhalf = ft & 1;
+    uint4 ps, pz;
+    auto fetch_sz = [&](int gwin) {
+      ps = pz = make_uint4(0, 0, 0, 0);
+      const int grow = row0 + lrow;
+      const int g = gwin + lhalf * 8;
+      if (p.scale_u4 == nullptr || grow >= p.N || g >= p.ng) return;
+      const __half* srow = p.scale_u4 + (size_t)grow * p.ng;
+      const __half* zrow = p.zero_u4 ? p.zero_u4 + (size_t)grow * p.ng : nullptr;
+      if (p.sz_vec) {
+        ps = *reinterpret_cast<const uint4*>(srow + g);
+        if (zrow) pz = *reinterpret_cast<const uint4*>(zrow + g);
+      } else {
+        __half hs[8], hz[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          hs[i] = (g + i < p.ng) ? srow[g + i] : __float2half(0.f);
+          hz[i] = (g + i < p.ng && zrow) ? zrow[g + i] : __float2half(0.f);
+        }
+        ps = *reinterpret_cast<uint4*>(&hs[0]);
+        pz = *reinterpret_cast<uint4*>(&hz[0]);
+      }
+    };
+    auto park_window = [&](int gwin) {
+      const __half2* hs = reinterpret_cast<const __half2*>(&ps);
+      const __half2* hz = reinterpret_cast<const __half2*>(&pz);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
+        szs[(lhalf * 8 + 2 * i) * ROWS + lrow] = make_float2(s2.x * 0.0625f, s2.x * z2.x);
+        szs[(lhalf * 8 + 2 * i + 1) * ROWS + lrow] = make_float2(s2.y * 0.0625f, s2.y * z2.y);
+      }
+      // group sums of the CTA's tokens for the window's groups
+      for (int i = ft; i < SZ_CHUNK * TN; i += FOLD_THREADS) {
+        const int gl = i / TN, t = i - gl * TN;
+        const int g = gwin + gl, tok = tok0 + t;
+        float v = 0.f;
+        if (p.sumxf && g < p.ng && tok < p.T) v = ld_plain(p.sumxf + ((size_t)(tok >> 4) * p.ng + g) * 16 + (tok & 15));
+        sums[i] = v;
+      }
+    };
+
+    bool ok = true;
+    if (p.nd > 0) fetch_sz(0);
+    for (int n = 0; n < n_steps; ++n) {
+      const bool is_dense = n < p.nd;
+      if (is_dense && (n % SZ_CHUNK) == 0) {
+        asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");   // previous window no longer read
+        park_window(n);
+        if (n + SZ_CHUNK < p.nd) fetch_sz(n + SZ_CHUNK);
+        asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");
+      }
+      float f = 0.f, c = 0.f;
+      int blk = 0;
+      if (is_dense) {
+        const float2 v = szs[(n % SZ_CHUNK) * ROWS + rl];
+        f = v.x;
+        c = v.y;
+      } else {
+        blk = b_lo + n - p.nd;
+        if (p.scale_u4 && row < p.N)
+          f = __half2float(ld_plain(p.scale_u4 + (size_t)row * p.ng + ld_plain(p.hp_col_indices + blk))) * 0.0625f *
+              p.sparse_weight;
+      }
+      const int buf = n & 1;
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (n >> 1) & 1, SITE_PRE_ACCFULL));
+      if (!ok) continue;
+      tc_fence_after();
+      const float* srow = sums + (n % SZ_CHUNK) * TN + c0;
+#pragma unroll
+      for (int cc = 0; cc < COLS_PER_FOLD; cc += 32) {
+        uint32_t a[32];
+        tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TN + c0 + cc, a);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float sx = is_dense ? srow[cc + i] : 0.f;
+          y[cc + i] = fmaf(__int2float_rn((int)a[i]), f, fmaf(-c, sx, y[cc + i]));
+        }
+        if (DUMP) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int tok = tok0 + c0 + cc + i;
+            if (tok >= p.T) continue;
+            // parity aid, not a hot path: every store is range-checked
+            if (is_dense) {
+              const size_t idx = ((size_t)n * p.N + row) * p.T + tok;
+              if (p.acc_dump && row < p.N) {
+                if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = ((int)a[i]) >> 4;
+                else record_error(SITE_PRE_DUMP, 1);
+              }
+            } else if (p.acc_hi_dump) {
+              const size_t idx = ((size_t)blk * BROW + rl) * p.T + tok;
+              if (blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = ((int)a[i]) >> 4;
+              else record_error(SITE_PRE_DUMP, 2);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    }
+
+    // ---------------------------------------------------------- epilogue
+    if (ok && p.Y != nullptr && row < p.N) {
+      const bool vec = (p.y_stride_t == 1) && ((p.y_stride_n & 7) == 0) && ((tok0 + c0) % 8 == 0) &&
+                       ((reinterpret_cast<uintptr_t>(p.Y) & 15) == 0) && (tok0 + c0 + COLS_PER_FOLD <= p.T);
+      if (vec) {
+        __half* dst = p.Y + (size_t)row * p.y_stride_n + tok0 + c0;
+#pragma unroll
+        for (int i = 0; i < COLS_PER_FOLD; i += 8) {
+          __align__(16) __half2 h[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            h[k] = __floats2half2_rn(y[i + 2 * k] * sxs[c0 + i + 2 * k], y[i + 2 * k + 1] * sxs[c0 + i + 2 * k + 1]);
+          *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<uint4*>(h);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < COLS_PER_FOLD; ++i) {
+          const int tok = tok0 + c0 + i;
+          if (tok < p.T)
+            p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(y[i] * sxs[c0 + i]);
+        }
+      }
+    }
+  }
+
+  // common exit: every role falls through to here, then the allocating warp frees TMEM
+  tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 }  // namespace pre
 }  // namespace w4a4

@@ -301,6 +301,74 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   return W4A4_OK;
 }
 
+int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
+  using namespace w4a4;
+  const bool dump = a.acc_dump || a.acc_hi_dump;
+  const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
+  if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
+  const int ng = a.K / BCOL;
+  const int row_tiles = (a.N + pre::ROWS - 1) / pre::ROWS;
+  const int tok_tiles = (a.T + pre::TN - 1) / pre::TN;
+  if (tok_tiles > 65535) return fail(W4A4_ERR_UNSUPPORTED, "T=%d exceeds the grid limit of the tensor-core path", a.T);
+  // expanded activations: given by the caller, or built here from the packed codes
+  const void* XE = a.XE;
+  const float* sumxf = a.sumxf;
+  if (XE == nullptr) {
+    const WsLayout wl = ws_layout(a.T, a.K);
+    if (a.ws == nullptr || a.ws_bytes < wl.total)
+      return fail(W4A4_ERR_WORKSPACE, "workspace of %zu bytes required, got %zu", wl.total, a.ws_bytes);
+    char* ws = static_cast<char*>(a.ws);
+    int rc = launch_expand(a, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf), dev);
+    if (rc) return rc;
+    XE = ws + wl.xe;
+    sumxf = a.sum_X ? reinterpret_cast<float*>(ws + wl.sumxf) : nullptr;
+  }
+  if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
+
+  CUtensorMap tm_w, tm_wh, tm_x;
+  // the operand that is switched off borrows the other one's map and is never read
+  int rc = make_map(&tm_w, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
+                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  rc = make_map(&tm_wh, has_sparse ? a.W_high : a.W_low, has_sparse ? 64 : (uint64_t)a.K / 2,
+                has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  rc = make_map_x(&tm_x, XE, a.T, a.K, 1, pre::TN);
+  if (rc) return rc;
+
+  pre::Params p;
+  p.hp_row_offsets = a.hp_row_offsets;
+  p.hp_col_indices = a.hp_col_indices;
+  p.scale_u4 = static_cast<const __half*>(a.scale_u4);
+  p.zero_u4 = static_cast<const __half*>(a.zero_u4);
+  p.sumxf = a.do_dense ? sumxf : nullptr;
+  p.scale_x = static_cast<const __half*>(a.scale_x);
+  p.Y = static_cast<__half*>(a.Y);
+  if (a.flags & W4A4_FLAG_OUT_TOKEN_MAJOR) {
+    p.y_stride_n = 1;
+    p.y_stride_t = a.N;
+  } else {
+    p.y_stride_n = a.T;
+    p.y_stride_t = 1;
+  }
+  p.acc_dump = a.acc_dump;
+  p.acc_hi_dump = a.acc_hi_dump;
+  p.T = a.T; p.K = a.K; p.N = a.N; p.ng = ng; p.nnz = has_sparse ? a.nnz : 0;
+  p.nd = a.do_dense ? ng : 0;
+  p.sparse_on = has_sparse ? 1 : 0;
+  p.sz_vec = (ng % 8 == 0 && aligned(a.scale_u4, 16) && aligned(a.zero_u4, 16)) ? 1 : 0;
+  p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
+
+  const size_t smem = pre::smem_bytes();
+  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const pre::Params) =
+      dump ? pre::prefill_gemm_kernel<true> : pre::prefill_gemm_kernel<false>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(prefill): %s", cudaGetErrorString(e));
+  e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, tm_x, p);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "prefill kernel launch: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
 int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x, int32_t* sum_X,
                  void* XE, float* sumxf, int T, int K, cudaStream_t stream, int sm_count) {
   using namespace w4a4;
@@ -357,7 +425,10 @@ int run_gemm(GemmArgs& a) {
   rc = current_device(&dev);
   if (rc) return rc;
   const bool dump = a.acc_dump || a.acc_hi_dump;
-  bool tensor_path = w4a4::pre::supported(a.T, a.K, a.N) && a.T > 16;
+  // few tokens: weights are streamed once and the MMA shape hardly matters; many
+  // tokens: the tcgen05 kernel.  W4A4_TENSOR_MIN_T moves the switch-over (A/B runs).
+  static const int min_t = getenv("W4A4_TENSOR_MIN_T") ? atoi(getenv("W4A4_TENSOR_MIN_T")) : 1 << 30;
+  bool tensor_path = w4a4::pre::supported(a.T, a.K, a.N) && a.T >= min_t;
   if (a.flags & W4A4_FLAG_FORCE_STREAM) tensor_path = false;
   if (a.flags & W4A4_FLAG_FORCE_TENSOR) {
     if (!w4a4::pre::supported(a.T, a.K, a.N))
@@ -365,7 +436,7 @@ int run_gemm(GemmArgs& a) {
     tensor_path = true;
   }
   (void)dump;
-  if (tensor_path) return fail(W4A4_ERR_UNSUPPORTED, "tensor-core path not built");
+  if (tensor_path) return launch_prefill(a, dev);
   return launch_decode(a, dev);
 }
 

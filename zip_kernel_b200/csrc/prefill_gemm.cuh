@@ -36,8 +36,9 @@ namespace pre {
 
 constexpr int ROWS = 128;                 // MMA M
 constexpr int TN = 128;                   // tokens per CTA = MMA N
-constexpr int W_STAGES = 4;               // packed weight tiles (8 KB each)
-constexpr int AB_STAGES = 3;              // widened weight tiles / activation tiles (16 KB each)
+constexpr int W_STAGES = 6;               // packed weight tiles in flight (8 KB each)
+constexpr int A_STAGES = 2;               // widened weight tiles (16 KB each, produced locally)
+constexpr int X_STAGES = 6;               // activation tiles in flight (16 KB each)
 constexpr int WP_BYTES = ROWS * GROUP_BYTES;      // 8192
 constexpr int A_BYTES = ROWS * BCOL;              // 16384
 constexpr int X_BYTES = TN * BCOL;                // 16384
@@ -77,8 +78,8 @@ inline bool supported(int T, int K, int N) { return T >= 1 && K >= 128 && N >= 1
 struct SmemLayout {
   static constexpr size_t wp = 0;
   static constexpr size_t a = wp + (size_t)W_STAGES * WP_BYTES;
-  static constexpr size_t x = a + (size_t)AB_STAGES * A_BYTES;
-  static constexpr size_t sz = x + (size_t)AB_STAGES * X_BYTES;                 // float2 [SZ_CHUNK][128]
+  static constexpr size_t x = a + (size_t)A_STAGES * A_BYTES;
+  static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float2 [SZ_CHUNK][128]
   static constexpr size_t sums = sz + (size_t)SZ_CHUNK * ROWS * 8;              // float  [SZ_CHUNK][TN]
   static constexpr size_t sxs = sums + (size_t)SZ_CHUNK * TN * 4;               // float  [TN]
   static constexpr size_t bars = sxs + (size_t)TN * 4;
@@ -133,6 +134,16 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// d = a * b + c on two packed fp32 lanes
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;"
+      : "=l"(*reinterpret_cast<unsigned long long*>(&d))
+      : "l"(*reinterpret_cast<unsigned long long*>(&a)), "l"(*reinterpret_cast<unsigned long long*>(&b)),
+        "l"(*reinterpret_cast<unsigned long long*>(&c)));
+  return d;
+}
+
 template <bool DUMP>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wh,
@@ -148,11 +159,11 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SmemLayout::bars);
   uint64_t* w_full = bars;                      // [W_STAGES]
   uint64_t* w_empty = w_full + W_STAGES;        // [W_STAGES]
-  uint64_t* a_full = w_empty + W_STAGES;        // [AB_STAGES]
-  uint64_t* a_empty = a_full + AB_STAGES;       // [AB_STAGES]
-  uint64_t* x_full = a_empty + AB_STAGES;       // [AB_STAGES]
-  uint64_t* x_empty = x_full + AB_STAGES;       // [AB_STAGES]
-  uint64_t* acc_full = x_empty + AB_STAGES;     // [2]
+  uint64_t* a_full = w_empty + W_STAGES;        // [A_STAGES]
+  uint64_t* a_empty = a_full + A_STAGES;        // [A_STAGES]
+  uint64_t* x_full = a_empty + A_STAGES;        // [X_STAGES]
+  uint64_t* x_empty = x_full + X_STAGES;        // [X_STAGES]
+  uint64_t* acc_full = x_empty + X_STAGES;      // [2]
   uint64_t* acc_empty = acc_full + 2;           // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
@@ -166,10 +177,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   if (tid == 0) {
     for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
-    for (int i = 0; i < AB_STAGES; ++i) {
-      mbar_init(&a_full[i], N_UNPACK_WARPS); mbar_init(&a_empty[i], 1);
-      mbar_init(&x_full[i], 1);              mbar_init(&x_empty[i], 1);
-    }
+    for (int i = 0; i < A_STAGES; ++i) { mbar_init(&a_full[i], N_UNPACK_WARPS); mbar_init(&a_empty[i], 1); }
+    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], N_FOLD_WARPS); }
     mbar_fence_init();
     tma_prefetch_desc(&tm_w);
@@ -217,31 +226,32 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int g = n < p.nd ? n : ld_plain(p.hp_col_indices + b_lo + n - p.nd);
         mbar_arrive_expect_tx(&x_full[xs], X_BYTES);
         tma_load_3d(x_ring + xs * X_BYTES, &tm_x, 0, g, tok0, &x_full[xs]);
-        if (++xs == AB_STAGES) { xs = 0; xph ^= 1; }
+        if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
       }
     }
   } else if (warp == WARP_MMA) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
-      int st = 0;
-      uint32_t ph = 0;
+      int st = 0, xs = 0;
+      uint32_t ph = 0, xph = 0;
       for (int n = 0; n < n_steps && ok; ++n) {
         const int buf = n & 1;
         ok = mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, SITE_PRE_ACCEMPTY);
         if (ok) ok = mbar_wait(&a_full[st], ph, SITE_PRE_AFULL);
-        if (ok) ok = mbar_wait(&x_full[st], ph, SITE_PRE_XFULL);
+        if (ok) ok = mbar_wait(&x_full[xs], xph, SITE_PRE_XFULL);
         if (!ok) break;
         tc_fence_after();
         const uint64_t adesc = smem_desc_sw128(a_ring + st * A_BYTES);
-        const uint64_t bdesc = smem_desc_sw128(x_ring + st * X_BYTES);
+        const uint64_t bdesc = smem_desc_sw128(x_ring + xs * X_BYTES);
         const uint32_t d = tmem_base + buf * TN;
 #pragma unroll
         for (int j = 0; j < 4; ++j) umma_i8(d, adesc + j * 2, bdesc + j * 2, j > 0);   // +32 bytes per K = 32
         umma_commit(&a_empty[st]);
-        umma_commit(&x_empty[st]);
+        umma_commit(&x_empty[xs]);
         umma_commit(&acc_full[buf]);
-        if (++st == AB_STAGES) { st = 0; ph ^= 1; }
+        if (++st == A_STAGES) { st = 0; ph ^= 1; }
+        if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
       }
     }
   } else if (warp < WARP_FOLD0) {
@@ -276,7 +286,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         mbar_arrive(&a_full[as]);
       }
       if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
-      if (++as == AB_STAGES) { as = 0; aph ^= 1; }
+      if (++as == A_STAGES) { as = 0; aph ^= 1; }
     }
   } else {
     // ------------------------------------------------------------ fold warps
@@ -291,14 +301,25 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       sxs[i] = (tok0 + i < p.T && p.scale_x) ? __half2float(ld_plain(p.scale_x + tok0 + i)) : 0.f;
     asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");
 
-    float y[COLS_PER_FOLD];
+    float2 y2[COLS_PER_FOLD / 2];
 #pragma unroll
-    for (int i = 0; i < COLS_PER_FOLD; ++i) y[i] = 0.f;
+    for (int i = 0; i < COLS_PER_FOLD / 2; ++i) y2[i] = make_float2(0.f, 0.f);
 
     // scale/zero window: thread ft fetches 8 groups of row ft/2; sums window: 16 groups x TN tokens
     const int lrow = ft >> 1, lhalf = ft & 1;
+    constexpr int SUMS_PER_THREAD = SZ_CHUNK * TN / FOLD_THREADS;   // 8
     uint4 ps, pz;
+    float psum[SUMS_PER_THREAD];
     auto fetch_sz = [&](int gwin) {
+      // group sums of the CTA's tokens for the window's groups
+#pragma unroll
+      for (int k = 0; k < SUMS_PER_THREAD; ++k) {
+        const int i = ft + k * FOLD_THREADS;
+        const int gl = i / TN, t = i - gl * TN;
+        const int g = gwin + gl, tok = tok0 + t;
+        psum[k] = 0.f;
+        if (p.sumxf && g < p.ng && tok < p.T) psum[k] = ld_plain(p.sumxf + ((size_t)(tok >> 4) * p.ng + g) * 16 + (tok & 15));
+      }
       ps = pz = make_uint4(0, 0, 0, 0);
       const int grow = row0 + lrow;
       const int g = gwin + lhalf * 8;
@@ -328,14 +349,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         szs[(lhalf * 8 + 2 * i) * ROWS + lrow] = make_float2(s2.x * 0.0625f, s2.x * z2.x);
         szs[(lhalf * 8 + 2 * i + 1) * ROWS + lrow] = make_float2(s2.y * 0.0625f, s2.y * z2.y);
       }
-      // group sums of the CTA's tokens for the window's groups
-      for (int i = ft; i < SZ_CHUNK * TN; i += FOLD_THREADS) {
-        const int gl = i / TN, t = i - gl * TN;
-        const int g = gwin + gl, tok = tok0 + t;
-        float v = 0.f;
-        if (p.sumxf && g < p.ng && tok < p.T) v = ld_plain(p.sumxf + ((size_t)(tok >> 4) * p.ng + g) * 16 + (tok & 15));
-        sums[i] = v;
-      }
+#pragma unroll
+      for (int k = 0; k < SUMS_PER_THREAD; ++k) sums[ft + k * FOLD_THREADS] = psum[k];
     };
 
     bool ok = true;
@@ -370,9 +385,10 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         uint32_t a[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TN + c0 + cc, a);
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float sx = is_dense ? srow[cc + i] : 0.f;
-          y[cc + i] = fmaf(__int2float_rn((int)a[i]), f, fmaf(-c, sx, y[cc + i]));
+        for (int i = 0; i < 32; i += 2) {
+          const float2 sx = is_dense ? *reinterpret_cast<const float2*>(srow + cc + i) : make_float2(0.f, 0.f);
+          const float2 t = fma2(make_float2(-c, -c), sx, y2[(cc + i) >> 1]);
+          y2[(cc + i) >> 1] = fma2(make_float2(__int2float_rn((int)a[i]), __int2float_rn((int)a[i + 1])), make_float2(f, f), t);
         }
         if (DUMP) {
 #pragma unroll
@@ -410,7 +426,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           __align__(16) __half2 h[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            h[k] = __floats2half2_rn(y[i + 2 * k] * sxs[c0 + i + 2 * k], y[i + 2 * k + 1] * sxs[c0 + i + 2 * k + 1]);
+            h[k] = __floats2half2_rn(y2[(i >> 1) + k].x * sxs[c0 + i + 2 * k], y2[(i >> 1) + k].y * sxs[c0 + i + 2 * k + 1]);
           *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<uint4*>(h);
         }
       } else {
@@ -418,7 +434,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int i = 0; i < COLS_PER_FOLD; ++i) {
           const int tok = tok0 + c0 + i;
           if (tok < p.T)
-            p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(y[i] * sxs[c0 + i]);
+            p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] =
+                __float2half_rn(((i & 1) ? y2[i >> 1].y : y2[i >> 1].x) * sxs[c0 + i]);
         }
       }
     }

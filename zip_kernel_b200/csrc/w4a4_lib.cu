@@ -427,8 +427,16 @@ int run_gemm(GemmArgs& a) {
   const bool dump = a.acc_dump || a.acc_hi_dump;
   // few tokens: weights are streamed once and the MMA shape hardly matters; many
   // tokens: the tcgen05 kernel.  W4A4_TENSOR_MIN_T moves the switch-over (A/B runs).
-  static const int min_t = getenv("W4A4_TENSOR_MIN_T") ? atoi(getenv("W4A4_TENSOR_MIN_T")) : 1 << 30;
-  bool tensor_path = w4a4::pre::supported(a.T, a.K, a.N) && a.T >= min_t;
+  static const int min_t = getenv("W4A4_TENSOR_MIN_T") ? atoi(getenv("W4A4_TENSOR_MIN_T")) : 0;
+  bool tensor_path;
+  if (min_t > 0) {
+    tensor_path = a.T >= min_t;
+  } else {
+    // measured cross-over on B200: the tensor kernel needs a grid that fills the SMs
+    const long long tiles = (long long)((a.N + 127) / 128) * ((a.T + w4a4::pre::TN - 1) / w4a4::pre::TN);
+    tensor_path = a.T >= 256 || (a.T >= 64 && tiles >= dev->sm_count);
+  }
+  tensor_path = tensor_path && w4a4::pre::supported(a.T, a.K, a.N);
   if (a.flags & W4A4_FLAG_FORCE_STREAM) tensor_path = false;
   if (a.flags & W4A4_FLAG_FORCE_TENSOR) {
     if (!w4a4::pre::supported(a.T, a.K, a.N))

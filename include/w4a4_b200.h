@@ -84,9 +84,12 @@ int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t
                             int T, int K, int N, int nnz, int flags, void* workspace,
                             size_t workspace_bytes, void* stream);
 
-/* Activations in the layout the GEMM kernels consume ("expanded"): XE (T, K) int8,
- * one byte per code, every packed 32-bit word of X_s4 turned into its four
- * even-indexed codes followed by its four odd-indexed ones; sumxf
+/* Activations in the layout the GEMM kernels consume ("expanded"): XE, one int8
+ * per code, group-major [K/128][T rounded up to 16][128 bytes] (+ slack; ask
+ * w4a4_expanded_codes_bytes for the size): the 128 bytes of one (group, token)
+ * hold the group's packed words in order, each 32-bit word of X_s4 turned into
+ * its four even-indexed codes followed by its four odd-indexed ones, with the
+ * line's eight 16-byte chunks stored at chunk ^ (token & 7); sumxf
  * [ceil(T/16)][K/128][16] float = sum_X transposed per 16-token tile.
  * w4a4_fused_dense_sparse builds both internally on every call; a caller that
  * feeds several linears from one activation (q/k/v, gate/up) can build them once
@@ -148,7 +151,7 @@ int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t*
  * already carved up.  The scratch the call needs (the activations in the layout
  * the GEMM reads) lives in an array that is part of the library image instead,
  * so the size is capped: T <= W4A4_NOALLOC_MAX_T tokens and
- * K <= W4A4_NOALLOC_MAX_K features (about 528 KiB, held by every GPU that loads
+ * K <= W4A4_NOALLOC_MAX_K features (about 544 KiB, held by every GPU that loads
  * the library until the process exits).  Larger shapes return
  * W4A4_ERR_UNSUPPORTED with a message naming the limits.  The call itself never
  * calls cudaMalloc / cudaFree or any allocating routine.

@@ -35,14 +35,29 @@ struct QuantParams {
   int8_t* X_s4;           // (T, K/2) or nullptr
   __half* scale_x;        // (T)
   int* sum_X;             // (T, K/128) or nullptr
-  int8_t* XE;             // optional (T, K) expanded codes (see expand_word), or nullptr
+  int8_t* XE;             // optional expanded codes, group-major (see xe_offset), or nullptr
   float* sumxf;           // optional [ceil(T/16)][K/128][16] float group sums, or nullptr
   int T, K;
+  int t_pad;              // tokens rounded up to 16: row pitch of the expanded layout
   int vec_ok;             // 1 when every row start is 16-byte aligned
   int C;                  // CTAs (cluster size) per token; divides K/128
 };
 
 __device__ __forceinline__ uint2 expand_word(uint32_t w) { return make_uint2(nib_lo_s8(w), nib_hi_s8(w)); }
+
+// Expanded activation layout ("XE") read by both GEMM kernels: one byte per code,
+// group-major, [K/128][t_pad][128 bytes].  The 128 bytes of one (group, token)
+// hold the group's 16 packed words in order, each word turned into 8 bytes (its
+// four even-indexed codes, then its four odd-indexed ones, sign-extended), and
+// the eight 16-byte chunks of the line are stored at chunk ^ (token & 7).  A run
+// of consecutive tokens of one group is therefore contiguous in memory and is
+// already the 128-byte-swizzled K-major operand tile an int8 MMA reads, so the
+// GEMM kernels fetch it with one plain bulk copy.  `c` is the index of the packed
+// word in the token's row (c / 16 = group).
+__device__ __forceinline__ size_t xe_offset(int t, int c, int t_pad) {
+  const int g = c >> 4, w = c & 15;
+  return ((size_t)g * t_pad + t) * 128 + ((((w >> 1) ^ (t & 7)) << 4) | ((w & 1) << 3));
+}
 
 __device__ __forceinline__ float half_abs_max8(const uint4& v, float m) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
@@ -150,7 +165,7 @@ act_quant_kernel(const QuantParams p) {
         word |= (uint32_t)(i1 & 0xF) << (8 * i + 4);
       }
       if (out) out[c] = word;
-      if (p.XE) reinterpret_cast<uint2*>(p.XE + (long long)t * p.K)[c] = expand_word(word);
+      if (p.XE) *reinterpret_cast<uint2*>(p.XE + xe_offset(t, c, p.t_pad)) = expand_word(word);
     }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -161,19 +176,15 @@ act_quant_kernel(const QuantParams p) {
   }
 }
 
-// Expanded activation layout ("XE") consumed by both GEMM kernels: one byte per
-// code, and every packed 32-bit word (8 codes) becomes 8 bytes - its four
-// even-indexed codes, then its four odd-indexed ones, each sign-extended to s8.
-// The weights are permuted the same way when their nibbles are expanded, so the
-// dot products pair up.  This kernel builds XE and the transposed float group
-// sums from already-quantised activations (the operator-level entry points that
-// receive X_s4 / sum_X from the caller).
+// Builds the expanded layout and the transposed float group sums from already
+// quantised activations (the operator-level entry points that receive X_s4 /
+// sum_X from the caller).
 struct ExpandParams {
   const int8_t* X_s4;   // (T, K/2)
   const int* sum_X;     // (T, K/128) or nullptr
-  int8_t* XE;           // (T, K)
+  int8_t* XE;           // group-major expanded codes (see xe_offset)
   float* sumxf;         // [ceil(T/16)][K/128][16]
-  int T, K;
+  int T, K, t_pad;
 };
 
 __global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandParams p) {
@@ -182,9 +193,11 @@ __global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandPar
   const long long words = (long long)p.T * (p.K >> 3);
   const long long stride = (long long)gridDim.x * blockDim.x;
   const uint32_t* src = reinterpret_cast<const uint32_t*>(p.X_s4);
-  uint2* dst = reinterpret_cast<uint2*>(p.XE);
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride)
-    dst[i] = expand_word(ld_plain(src + i));
+  const int wpr = p.K >> 3;     // packed words per token
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride) {
+    const int t = (int)(i / wpr), c = (int)(i - (long long)t * wpr);
+    *reinterpret_cast<uint2*>(p.XE + xe_offset(t, c, p.t_pad)) = expand_word(ld_plain(src + i));
+  }
   if (p.sum_X) {
     const int ng = p.K >> 7;
     const long long n = (long long)p.T * ng;

@@ -24,9 +24,9 @@
 // Data flow per CTA.  A producer warp walks the range and, per step, issues
 // non-multicast asynchronous copies into one slot of a 4-deep shared-memory
 // ring guarded by mbarriers: the weight tile (TMA, or a plain bulk copy for a
-// residual block), the matching 128-byte slices of the expanded activation codes
-// of up to 16 tokens (TMA, 128-byte swizzle so fragment reads are conflict-free)
-// and the group sums (bulk copy).  Eight consumer warps (16 rows each) read
+// residual block), the expanded activation codes of up to 16 tokens for the same
+// groups (one contiguous bulk copy per group; the layout is pre-swizzled so
+// fragment reads are conflict-free) and the group sums (bulk copy).  Eight consumer warps (16 rows each) read
 // their fragments with 128-bit loads, expand nibbles to s8 lanes scaled by 16
 // with three logic ops per word, run mma.sync m16n8k32 s8 on the two groups as
 // independent chains (element order inside a group is permuted identically on
@@ -65,6 +65,8 @@ struct Params {
   const int* hp_row_offsets;
   const int* hp_col_indices;
   const int8_t* W_high;     // (nnz, 128, 64) residual blocks
+  const int8_t* XE;         // expanded activation codes, group-major [ng][t_pad][128]
+  int t_pad;
   const __half* scale_u4;   // (N, ng)
   const __half* zero_u4;    // (N, ng) or nullptr
   const float* sumxf;       // [tok tiles][ng][16] or nullptr
@@ -156,8 +158,7 @@ __device__ __forceinline__ void group_fold(float2 (&y)[NT][2], const int (&acc)[
 
 template <int NT, bool DUMP>
 __global__ void __launch_bounds__(THREADS, 2)
-decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_constant__ CUtensorMap tm_x2,
-                   const __grid_constant__ CUtensorMap tm_x1, const Params p) {
+decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* stage_buf = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -191,8 +192,6 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
     mbar_fence_init();
     misc[1] = 0;
     tma_prefetch_desc(&tm_low);
-    tma_prefetch_desc(&tm_x2);
-    tma_prefetch_desc(&tm_x1);
   }
   __syncthreads();
 
@@ -204,13 +203,17 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
       bool ok = true;
       // The weight copy of a step does not depend on the preceding kernel in the
       // stream, the activation copies do.  Dense step j covers groups 2j, 2j+1.
+      // the tokens' codes of one group are one contiguous run in the expanded layout
+      auto x_src = [&](int g) { return p.XE + ((size_t)g * p.t_pad + tok0) * BCOL; };
       auto dense_w = [&](int j, int st) {
-        const int n_sum = with_sums ? ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES : 0;
-        mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + 2 * XG_BYTES + n_sum);
+        const int n_grp = (2 * j + 1 < p.ng) ? 2 : 1;
+        mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + n_grp * XG_BYTES + (with_sums ? n_grp * SUMX_BYTES : 0));
         tma_load_2d(stage_buf + st * STAGE_BYTES, &tm_low, 2 * j * GROUP_BYTES, row0, &full[st]);
       };
       auto dense_x = [&](int j, int st) {
-        tma_load_3d(stage_buf + st * STAGE_BYTES + W_TILE_BYTES, &tm_x2, 0, 2 * j, tok0, &full[st]);
+        unsigned char* xt = stage_buf + st * STAGE_BYTES + W_TILE_BYTES;
+        bulk_load_1d(xt, x_src(2 * j), XG_BYTES, &full[st]);
+        if (2 * j + 1 < p.ng) bulk_load_1d(xt + X_TILE_BYTES, x_src(2 * j + 1), XG_BYTES, &full[st]);
         if (with_sums)
           bulk_load_1d(sumx_ring + st * 2 * SUMX_BYTES, sums_base + 2 * j * TOK,
                        ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES, &full[st]);
@@ -244,7 +247,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
         unsigned char* slot = stage_buf + st * STAGE_BYTES;
         mbar_arrive_expect_tx(&full[st], BLK_BYTES + XG_BYTES);
         bulk_load_1d(slot, p.W_high + (size_t)blk * BLK_BYTES, BLK_BYTES, &full[st]);
-        tma_load_3d(slot + W_TILE_BYTES, &tm_x1, 0, ld_plain(p.hp_col_indices + blk), tok0, &full[st]);
+        bulk_load_1d(slot + W_TILE_BYTES, x_src(ld_plain(p.hp_col_indices + blk)), XG_BYTES, &full[st]);
         if (++st == STAGES) { st = 0; ph ^= 1; }
       }
       if (!ok) {
@@ -262,20 +265,13 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
     const int r_b = r_a + 8;
     grid_dependency_wait();               // scale_x, and the workspace of earlier launches
 
-    // Per-thread constant offsets inside a slot.  The activation tile is a stack
-    // of 128-byte lines under the 128-byte swizzle (16-byte chunk index XOR line
-    // index mod 8): a dense step holds line 2*token + h for group h, a residual
-    // step line = token.
-    int xd0[2][NT], xd1[2][NT], xs0[NT], xs1[NT];
+    // Per-thread constant offsets inside a slot.  An activation tile is a stack of
+    // 128-byte lines (one per token) whose 16-byte chunks sit at chunk ^ (token & 7);
+    // a dense step holds one tile per group, X_TILE_BYTES apart.
+    int xs0[NT], xs1[NT];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const int xr = nt * 8 + gid;
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int line = 2 * xr + h;
-        xd0[h][nt] = W_TILE_BYTES + line * BCOL + (((2 * tig) ^ (line & 7)) << 4);
-        xd1[h][nt] = W_TILE_BYTES + line * BCOL + (((2 * tig + 1) ^ (line & 7)) << 4);
-      }
       xs0[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig) ^ (xr & 7)) << 4);
       xs1[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig + 1) ^ (xr & 7)) << 4);
     }
@@ -392,8 +388,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
             float2 sx[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              q0[nt] = *reinterpret_cast<const uint4*>(slot + xd0[0][nt]);
-              q1[nt] = *reinterpret_cast<const uint4*>(slot + xd1[0][nt]);
+              q0[nt] = *reinterpret_cast<const uint4*>(slot + xs0[nt]);
+              q1[nt] = *reinterpret_cast<const uint4*>(slot + xs1[nt]);
               sx[nt] = p.sumxf ? *reinterpret_cast<const float2*>(sums + nt * 8 + tig * 2) : make_float2(0.f, 0.f);
             }
             group_mma<NT>(acc0, wa[0], wb[0], q0, q1);
@@ -404,8 +400,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const __grid_cons
             float2 sx[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              q0[nt] = *reinterpret_cast<const uint4*>(slot + xd0[1][nt]);
-              q1[nt] = *reinterpret_cast<const uint4*>(slot + xd1[1][nt]);
+              q0[nt] = *reinterpret_cast<const uint4*>(slot + X_TILE_BYTES + xs0[nt]);
+              q1[nt] = *reinterpret_cast<const uint4*>(slot + X_TILE_BYTES + xs1[nt]);
               sx[nt] = (p.sumxf && two) ? *reinterpret_cast<const float2*>(sums + TOK + nt * 8 + tig * 2)
                                         : make_float2(0.f, 0.f);
             }

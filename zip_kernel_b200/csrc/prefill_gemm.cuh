@@ -10,9 +10,10 @@
 // the way: a CTA owns 128 weight rows (one block-row = MMA M) x TN tokens (MMA N).
 // Per K-group of 128 (and per residual block of the block-row, which is just one
 // more K-step):
-//   * the producer warp issues two non-multicast TMA copies: the packed weight
-//     tile (128 x 64 bytes) and the tokens' expanded codes (TN x 128 bytes,
-//     128-byte swizzle = the K-major operand layout tcgen05 reads directly);
+//   * the producer warp issues two non-multicast asynchronous copies: the packed
+//     weight tile (TMA, 128 x 64 bytes) and the tokens' expanded codes (one bulk
+//     copy of TN x 128 bytes: the expanded layout is group-major and pre-swizzled,
+//     i.e. already the K-major operand layout tcgen05 reads);
 //   * four unpack warps widen the weight tile into a second shared-memory ring
 //     in the same swizzled K-major layout (s8 lanes scaled by 16, three logic ops
 //     per 8 codes, same element permutation as the activations);
@@ -58,6 +59,8 @@ enum : int {
 struct Params {
   const int* hp_row_offsets;
   const int* hp_col_indices;
+  const int8_t* XE;         // expanded activation codes, group-major [ng][t_pad][128]
+  int t_pad;
   const __half* scale_u4;   // (N, ng)
   const __half* zero_u4;    // (N, ng) or nullptr
   const float* sumxf;       // [ceil(T/16)][ng][16] or nullptr
@@ -147,7 +150,7 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
 template <bool DUMP>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wh,
-                    const __grid_constant__ CUtensorMap tm_x, const Params p) {
+                    const Params p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* wp_ring = sm + SmemLayout::wp;
@@ -183,7 +186,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     mbar_fence_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_wh);
-    tma_prefetch_desc(&tm_x);
   }
   if (warp == WARP_MMA) tmem_alloc(tmem_slot, TMEM_COLS);
   tc_fence_before();
@@ -225,7 +227,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (!ok) break;
         const int g = n < p.nd ? n : ld_plain(p.hp_col_indices + b_lo + n - p.nd);
         mbar_arrive_expect_tx(&x_full[xs], X_BYTES);
-        tma_load_3d(x_ring + xs * X_BYTES, &tm_x, 0, g, tok0, &x_full[xs]);
+        // TN consecutive tokens of one group: contiguous and already in operand layout
+        bulk_load_1d(x_ring + xs * X_BYTES, p.XE + ((size_t)g * p.t_pad + tok0) * BCOL, X_BYTES, &x_full[xs]);
         if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
       }
     }

@@ -91,20 +91,10 @@ int make_map(CUtensorMap* m, const void* ptr, uint64_t row_bytes, uint64_t rows,
   return W4A4_OK;
 }
 
-// Expanded activations (T, K) bytes seen as [token][group][128 bytes]; the box takes
-// `groups` adjacent groups of `tokens` tokens, 128-byte swizzle.  Tokens and groups
-// past the end read as zero.
-int make_map_x(CUtensorMap* m, const void* XE, int T, int K, uint32_t groups, uint32_t tokens) {
-  cuuint64_t dims[3] = {128, (cuuint64_t)(K / 128), (cuuint64_t)T};
-  cuuint64_t strides[2] = {128, (cuuint64_t)K};
-  cuuint32_t box[3] = {128, groups, tokens};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = g_encode(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(XE), dims, strides, box, estr,
-                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(W4A4_ERR_LAUNCH, "cuTensorMapEncodeTiled(activations) failed (%d)", (int)r);
-  return W4A4_OK;
-}
+// Expanded activations: [K/128][t_pad][128] bytes with t_pad = T rounded up to 16,
+// plus slack so that a full 128-token tile copy of the last group stays inside.
+inline int xe_t_pad(int T) { return (T + 15) / 16 * 16; }
+inline size_t xe_bytes(int T, int K) { return (size_t)xe_t_pad(T) * K + 128 * 128; }
 
 // ------------------------------------------------------------------ workspace layout
 // Scratch for activations in the layout the GEMM kernels read: per-token scales
@@ -117,7 +107,7 @@ WsLayout ws_layout(int T, int K) {
   const size_t ng = K / 128, tok_tiles = (T + 15) / 16;
   size_t off = 0;
   w.scale_x = off;  off += round_up((size_t)T * 2, 256);
-  w.xe = off;       off += round_up((size_t)T * K, 1024);
+  w.xe = off;       off += round_up(xe_bytes(T, K), 1024);
   w.sumxf = off;    off += round_up(tok_tiles * ng * 16 * 4, 256);
   w.total = off;
   return w;
@@ -213,6 +203,7 @@ int launch_expand(const GemmArgs& a, void* XE, float* sumxf, DeviceInfo* dev) {
   e.sumxf = sumxf;
   e.T = a.T;
   e.K = a.K;
+  e.t_pad = xe_t_pad(a.T);
   const long long words = (long long)a.T * (a.K / 8);
   long long blocks = (words + 255) / 256;
   if (blocks > 4LL * dev->sm_count) blocks = 4LL * dev->sm_count;
@@ -250,21 +241,19 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
 
   const bool nt2 = a.T > 8;
-  CUtensorMap tm_low, tm_x2, tm_x1;
+  CUtensorMap tm_low;
   // dense weights: 128 rows x two groups (128 bytes) per copy; unused (but valid) when the dense part is off
   int rc = make_map(&tm_low, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
                     a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, a.do_dense ? 2 * GROUP_BYTES : GROUP_BYTES,
                     dec::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
-  if (rc) return rc;
-  rc = make_map_x(&tm_x2, XE, a.T, a.K, 2, nt2 ? 16 : 8);     // dense steps: two groups
-  if (rc) return rc;
-  rc = make_map_x(&tm_x1, XE, a.T, a.K, 1, nt2 ? 16 : 8);     // residual steps: one group
   if (rc) return rc;
 
   dec::Params p;
   p.hp_row_offsets = a.hp_row_offsets;
   p.hp_col_indices = a.hp_col_indices;
   p.W_high = static_cast<const int8_t*>(a.W_high);
+  p.XE = static_cast<const int8_t*>(XE);
+  p.t_pad = xe_t_pad(a.T);
   p.scale_u4 = static_cast<const __half*>(a.scale_u4);
   p.zero_u4 = static_cast<const __half*>(a.zero_u4);
   p.sumxf = a.do_dense ? sumxf : nullptr;
@@ -288,7 +277,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
 
   const size_t smem = dec::smem_bytes();
-  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const dec::Params) =
+  void (*kern)(const CUtensorMap, const dec::Params) =
       dump ? (nt2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
            : (nt2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -296,7 +285,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
 
   (void)pdl;
   e = launch_ex(kern, dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
-                plan.split, tm_low, tm_x2, tm_x1, p);
+                plan.split, tm_low, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }
@@ -325,7 +314,7 @@ int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
   }
   if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
 
-  CUtensorMap tm_w, tm_wh, tm_x;
+  CUtensorMap tm_w, tm_wh;
   // the operand that is switched off borrows the other one's map and is never read
   int rc = make_map(&tm_w, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
                     a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
@@ -333,12 +322,12 @@ int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
   rc = make_map(&tm_wh, has_sparse ? a.W_high : a.W_low, has_sparse ? 64 : (uint64_t)a.K / 2,
                 has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
-  rc = make_map_x(&tm_x, XE, a.T, a.K, 1, pre::TN);
-  if (rc) return rc;
 
   pre::Params p;
   p.hp_row_offsets = a.hp_row_offsets;
   p.hp_col_indices = a.hp_col_indices;
+  p.XE = static_cast<const int8_t*>(XE);
+  p.t_pad = xe_t_pad(a.T);
   p.scale_u4 = static_cast<const __half*>(a.scale_u4);
   p.zero_u4 = static_cast<const __half*>(a.zero_u4);
   p.sumxf = a.do_dense ? sumxf : nullptr;
@@ -360,11 +349,11 @@ int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
 
   const size_t smem = pre::smem_bytes();
-  void (*kern)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const pre::Params) =
+  void (*kern)(const CUtensorMap, const CUtensorMap, const pre::Params) =
       dump ? pre::prefill_gemm_kernel<true> : pre::prefill_gemm_kernel<false>;
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(prefill): %s", cudaGetErrorString(e));
-  e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, tm_x, p);
+  e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "prefill kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }
@@ -383,6 +372,7 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   q.sumxf = sumxf;
   q.T = T;
   q.K = K;
+  q.t_pad = xe_t_pad(T);
   q.vec_ok = (aligned(X, 16) && (ldx % 8 == 0)) ? 1 : 0;
   // few tokens: spread each token over a cluster so the row is read by many SMs at once
   int C = 1;
@@ -455,7 +445,7 @@ int run_gemm(GemmArgs& a) {
 // the library holds these ~528 KiB until the process exits.
 constexpr int NOALLOC_MAX_T = W4A4_NOALLOC_MAX_T;
 constexpr int NOALLOC_MAX_K = W4A4_NOALLOC_MAX_K;
-constexpr size_t NOALLOC_XE_BYTES = (size_t)NOALLOC_MAX_T * NOALLOC_MAX_K;
+constexpr size_t NOALLOC_XE_BYTES = (size_t)NOALLOC_MAX_T * NOALLOC_MAX_K + 128 * 128;
 constexpr size_t NOALLOC_SUMS_BYTES = (size_t)(NOALLOC_MAX_K / 128) * 16 * sizeof(float);
 static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_XE_BYTES + NOALLOC_SUMS_BYTES];
 
@@ -550,7 +540,7 @@ int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t
   return run_gemm(a);
 }
 
-size_t w4a4_expanded_codes_bytes(int T, int K) { return (T < 1 || K < 128) ? 0 : (size_t)T * K; }
+size_t w4a4_expanded_codes_bytes(int T, int K) { return (T < 1 || K < 128) ? 0 : xe_bytes(T, K); }
 size_t w4a4_expanded_sums_bytes(int T, int K) {
   return (T < 1 || K < 128) ? 0 : (size_t)((T + 15) / 16) * (K / 128) * 16 * 4;
 }

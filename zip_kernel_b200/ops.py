@@ -233,13 +233,15 @@ def fused_dense_sparse_cuda_int4(
 
 def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor):
     """Quantised activations in the layout the GEMM kernels read: returns
-    ``(XE (T, K) int8, sumxf (ceil(T/16), K/128, 16) fp32)``.  Build once and reuse
-    across the linears that share an input (no counterpart in the reference)."""
+    ``(XE, sumxf)`` - an opaque int8 buffer of expanded codes (group-major, see
+    include/w4a4_b200.h) and ``(ceil(T/16), K/128, 16)`` fp32 group sums.  Build once
+    and reuse across the linears that share an input (no counterpart in the
+    reference)."""
     assert X_s4.is_cuda and X_s4.dtype == torch.int8 and sum_X.dtype == torch.int32
     T, K = int(X_s4.shape[0]), int(X_s4.shape[1]) * 2
     X = X_s4.contiguous()
     sm = sum_X.contiguous()
-    XE = torch.empty((T, K), dtype=torch.int8, device=X.device)
+    XE = torch.empty((int(_L.w4a4_expanded_codes_bytes(T, K)),), dtype=torch.int8, device=X.device)
     sumxf = torch.zeros(((T + 15) // 16, K // BCOL, 16), dtype=torch.float32, device=X.device)
     with torch.cuda.device(X.device):
         _lib.check(_L.w4a4_expand_activations(X.data_ptr(), sm.data_ptr(), XE.data_ptr(), sumxf.data_ptr(),
@@ -255,8 +257,9 @@ def fused_dense_sparse_expanded_cuda(
     """:func:`fused_dense_sparse_cuda_int4` on activations already expanded by
     :func:`expand_activations_cuda`; a single kernel launch."""
     d_out, d_in = int(d_out), int(d_in)
-    T = int(XE.shape[0])
-    assert XE.is_cuda and XE.dtype == torch.int8 and XE.shape == (T, d_in) and XE.is_contiguous()
+    T = int(scale_x.shape[0])
+    assert XE.is_cuda and XE.dtype == torch.int8 and XE.is_contiguous()
+    assert XE.numel() >= int(_L.w4a4_expanded_codes_bytes(T, d_in)), "XE was built for another shape"
     assert sumxf.dtype == torch.float32 and sumxf.is_contiguous()
     W = W_low_packed.contiguous()
     nnz = int(W_high_blocks_packed.shape[0]) if W_high_blocks_packed.numel() else 0

@@ -263,7 +263,6 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
     const int tig = lane & 3;
     const int r_a = warp * 16 + gid;      // local rows of this thread's fragments
     const int r_b = r_a + 8;
-    grid_dependency_wait();               // scale_x, and the workspace of earlier launches
 
     // Per-thread constant offsets inside a slot.  An activation tile is a stack of
     // 128-byte lines (one per token) whose 16-byte chunks sit at chunk ^ (token & 7);
@@ -275,6 +274,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
       xs0[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig) ^ (xr & 7)) << 4);
       xs1[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig + 1) ^ (xr & 7)) << 4);
     }
+
+    const uint32_t stage_a = smem_u32(stage_buf), sumx_a = smem_u32(sumx_ring), szs_a = smem_u32(szs);
 
     float2 y[NT][2];
 #pragma unroll
@@ -343,15 +344,27 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
-        szs[(lhalf * 8 + 2 * i) * ROWS + lrow] = make_float2(s2.x * 0.0625f, s2.x * z2.x);
-        szs[(lhalf * 8 + 2 * i + 1) * ROWS + lrow] = make_float2(s2.y * 0.0625f, s2.y * z2.y);
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * 0.0625f, s2.x * z2.x));
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * 0.0625f, s2.y * z2.y));
       }
     };
 
     int j_w = d_lo, did_sparse = 0;
     Span cur, nxt;
     bool have = walk(j_w, did_sparse, cur);
+    // weights' scales and zeros do not depend on the preceding kernel: their first
+    // window is on its way before this warp waits for that kernel
     if (have) fetch_sz(cur);
+    grid_dependency_wait();               // scale_x (read in the epilogue) is written by the preceding kernel
+    // activation scales of this thread's output columns, fetched now so that the epilogue does not wait for them
+    float sxv[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int tok = tok0 + nt * 8 + tig * 2 + h;
+        sxv[nt][h] = (S == 1 && p.scale_x && tok < p.T) ? __half2float(ld_plain(p.scale_x + tok)) : 0.f;
+      }
     // A wait that gives up clears `ok` for the whole warp; the loops still run to
     // their end (skipping the work) so that every barrier below is reached.
     while (have) {
@@ -368,29 +381,29 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           const int st = consumed % STAGES;
           if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (consumed / STAGES) & 1, SITE_DEC_FULL));
           if (!ok) continue;
-          const unsigned char* slot = stage_buf + st * STAGE_BYTES;
-          const unsigned char* wrow_a = slot + r_a * (2 * GROUP_BYTES) + tig * 16;
-          const unsigned char* wrow_b = slot + r_b * (2 * GROUP_BYTES) + tig * 16;
-          const float* sums = reinterpret_cast<const float*>(sumx_ring + st * 2 * SUMX_BYTES);
+          const uint32_t slot = stage_a + st * STAGE_BYTES;
+          const uint32_t wrow_a = slot + r_a * (2 * GROUP_BYTES) + tig * 16;
+          const uint32_t wrow_b = slot + r_b * (2 * GROUP_BYTES) + tig * 16;
+          const uint32_t sums = sumx_a + st * 2 * SUMX_BYTES;
           uint4 wa[2], wb[2];
 #pragma unroll
           for (int h = 0; h < 2; ++h) {
-            wa[h] = *reinterpret_cast<const uint4*>(wrow_a + h * GROUP_BYTES);
-            wb[h] = *reinterpret_cast<const uint4*>(wrow_b + h * GROUP_BYTES);
+            wa[h] = lds_v4(wrow_a + h * GROUP_BYTES);
+            wb[h] = lds_v4(wrow_b + h * GROUP_BYTES);
           }
-          const float2 sza0 = szs[(g & (SZ_CHUNK - 1)) * ROWS + r_a];
-          const float2 szb0 = szs[(g & (SZ_CHUNK - 1)) * ROWS + r_b];
-          const float2 sza1 = szs[((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_a];
-          const float2 szb1 = szs[((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_b];
+          const float2 sza0 = lds_f2(szs_a + ((g & (SZ_CHUNK - 1)) * ROWS + r_a) * 8);
+          const float2 szb0 = lds_f2(szs_a + ((g & (SZ_CHUNK - 1)) * ROWS + r_b) * 8);
+          const float2 sza1 = lds_f2(szs_a + (((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_a) * 8);
+          const float2 szb1 = lds_f2(szs_a + (((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_b) * 8);
           int acc0[NT][4], acc1[NT][4];
           {
             uint4 q0[NT], q1[NT];
             float2 sx[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              q0[nt] = *reinterpret_cast<const uint4*>(slot + xs0[nt]);
-              q1[nt] = *reinterpret_cast<const uint4*>(slot + xs1[nt]);
-              sx[nt] = p.sumxf ? *reinterpret_cast<const float2*>(sums + nt * 8 + tig * 2) : make_float2(0.f, 0.f);
+              q0[nt] = lds_v4(slot + xs0[nt]);
+              q1[nt] = lds_v4(slot + xs1[nt]);
+              sx[nt] = p.sumxf ? lds_f2(sums + (nt * 8 + tig * 2) * 4) : make_float2(0.f, 0.f);
             }
             group_mma<NT>(acc0, wa[0], wb[0], q0, q1);
             group_fold<NT>(y, acc0, sza0.x, szb0.x, sza0.y, szb0.y, sx);
@@ -400,10 +413,9 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
             float2 sx[NT];
 #pragma unroll
             for (int nt = 0; nt < NT; ++nt) {
-              q0[nt] = *reinterpret_cast<const uint4*>(slot + X_TILE_BYTES + xs0[nt]);
-              q1[nt] = *reinterpret_cast<const uint4*>(slot + X_TILE_BYTES + xs1[nt]);
-              sx[nt] = (p.sumxf && two) ? *reinterpret_cast<const float2*>(sums + TOK + nt * 8 + tig * 2)
-                                        : make_float2(0.f, 0.f);
+              q0[nt] = lds_v4(slot + X_TILE_BYTES + xs0[nt]);
+              q1[nt] = lds_v4(slot + X_TILE_BYTES + xs1[nt]);
+              sx[nt] = (p.sumxf && two) ? lds_f2(sums + (TOK + nt * 8 + tig * 2) * 4) : make_float2(0.f, 0.f);
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[st]);      // every shared-memory read of this slot is done
@@ -439,15 +451,15 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           const int st = consumed % STAGES;
           if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (consumed / STAGES) & 1, SITE_DEC_FULL));
           if (!ok) continue;
-          const unsigned char* slot = stage_buf + st * STAGE_BYTES;
-          const uint4 wa = *reinterpret_cast<const uint4*>(slot + r_a * GROUP_BYTES + tig * 16);
-          const uint4 wb = *reinterpret_cast<const uint4*>(slot + r_b * GROUP_BYTES + tig * 16);
+          const uint32_t slot = stage_a + st * STAGE_BYTES;
+          const uint4 wa = lds_v4(slot + r_a * GROUP_BYTES + tig * 16);
+          const uint4 wb = lds_v4(slot + r_b * GROUP_BYTES + tig * 16);
           uint4 q0[NT], q1[NT];
           float2 sx[NT];
 #pragma unroll
           for (int nt = 0; nt < NT; ++nt) {
-            q0[nt] = *reinterpret_cast<const uint4*>(slot + xs0[nt]);
-            q1[nt] = *reinterpret_cast<const uint4*>(slot + xs1[nt]);
+            q0[nt] = lds_v4(slot + xs0[nt]);
+            q1[nt] = lds_v4(slot + xs1[nt]);
             sx[nt] = make_float2(0.f, 0.f);
           }
           __syncwarp();
@@ -488,20 +500,18 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
             const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
             if (row < p.N && tok < p.T) {
               const float v = (i & 1) ? y[nt][i >> 1].y : y[nt][i >> 1].x;
-              const float sxs = __half2float(ld_plain(p.scale_x + tok));
-              p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v * sxs);
+              p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v * sxv[nt][i & 1]);
             }
           }
       }
     } else if (p.Y != nullptr) {
       // park this CTA's 128 x 16 partial tile in its own shared memory (the ring is
       // drained: every copy that was issued has been consumed)
-      float* red = reinterpret_cast<float*>(stage_buf);
       asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");   // nobody still reads the last slot
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
-        *reinterpret_cast<float2*>(red + r_a * TOK + nt * 8 + tig * 2) = y[nt][0];
-        *reinterpret_cast<float2*>(red + r_b * TOK + nt * 8 + tig * 2) = y[nt][1];
+        sts_f2(stage_a + (r_a * TOK + nt * 8 + tig * 2) * 4, y[nt][0]);
+        sts_f2(stage_a + (r_b * TOK + nt * 8 + tig * 2) * 4, y[nt][1]);
       }
     }
   }
@@ -510,18 +520,24 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
     // Every thread of every CTA of the cluster reaches both barriers: no path
     // above returns early.  CTA k then owns rows [k*128/S, (k+1)*128/S) of the tile.
     __syncwarp();
+    constexpr int NCOL = NT * 8;
+    static_assert(THREADS % NCOL == 0, "a thread keeps one output column through the reduction loop");
+    // the column's activation scale travels while the cluster gathers (most of the
+    // producer warp has not passed the dependency wait, so it waits here: a no-op by now)
+    const int col = tid % NCOL;
+    if (warp == CONSUMER_WARPS) grid_dependency_wait();
+    const float sxs = (p.scale_x && tok0 + col < p.T) ? __half2float(ld_plain(p.scale_x + tok0 + col)) : 0.f;
     cluster_sync_all();
     const float* red = reinterpret_cast<const float*>(stage_buf);
-    constexpr int NCOL = NT * 8;
     const int rl_lo = rank * ROWS / S, rl_hi = (rank + 1) * ROWS / S;
     for (int i = tid; i < (rl_hi - rl_lo) * NCOL; i += THREADS) {
-      const int rl = rl_lo + i / NCOL, col = i % NCOL;
+      const int rl = rl_lo + i / NCOL;
       const int row = row0 + rl, tok = tok0 + col;
       if (row >= p.N || tok >= p.T) continue;
       float v = 0.f;
+#pragma unroll 8
       for (int c = 0; c < S; ++c) v += ld_dsmem_f32(red + rl * TOK + col, (uint32_t)c);
-      v *= __half2float(ld_plain(p.scale_x + tok));
-      p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v);
+      p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] = __float2half_rn(v * sxs);
     }
     cluster_sync_all();     // peers may not retire while their tiles are still being read
   }

@@ -260,6 +260,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   } else if (warp < WARP_FOLD0) {
     // ------------------------------------------------------------ unpack warps
     const int ut = tid - WARP_UNPACK0 * 32;      // 0..127
+    const uint32_t wp_a = smem_u32(wp_ring), a_a = smem_u32(a_ring);
     bool ok = true;
     int ws = 0, as = 0;
     uint32_t wph = 0, aph = 1;
@@ -268,18 +269,20 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], aph, SITE_PRE_AEMPTY));
       if (ok) {
         tc_fence_after();      // the slot was last read by tcgen05.mma
-        const unsigned char* src = wp_ring + ws * WP_BYTES;
-        unsigned char* dst = a_ring + as * A_BYTES;
+        const uint32_t src = wp_a + ws * WP_BYTES;
+        const uint32_t dst = a_a + as * A_BYTES;
+        uint4 w[4];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) w[pass] = lds_v4(src + (pass * 128 + ut) * 16);
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass) {
           const int item = pass * 128 + ut;      // 16 packed bytes = 32 codes
           const int row = item >> 2, pc = item & 3;
-          const uint4 w = *reinterpret_cast<const uint4*>(src + item * 16);
-          const uint4 o0 = make_uint4(nib_lo_x16(w.x), nib_hi_x16(w.x), nib_lo_x16(w.y), nib_hi_x16(w.y));
-          const uint4 o1 = make_uint4(nib_lo_x16(w.z), nib_hi_x16(w.z), nib_lo_x16(w.w), nib_hi_x16(w.w));
-          unsigned char* drow = dst + row * BCOL;
-          *reinterpret_cast<uint4*>(drow + (((2 * pc) ^ (row & 7)) << 4)) = o0;
-          *reinterpret_cast<uint4*>(drow + (((2 * pc + 1) ^ (row & 7)) << 4)) = o1;
+          const uint4 o0 = make_uint4(nib_lo_x16(w[pass].x), nib_hi_x16(w[pass].x), nib_lo_x16(w[pass].y), nib_hi_x16(w[pass].y));
+          const uint4 o1 = make_uint4(nib_lo_x16(w[pass].z), nib_hi_x16(w[pass].z), nib_lo_x16(w[pass].w), nib_hi_x16(w[pass].w));
+          const uint32_t drow = dst + row * BCOL;
+          sts_v4(drow + (((2 * pc) ^ (row & 7)) << 4), o0);
+          sts_v4(drow + (((2 * pc + 1) ^ (row & 7)) << 4), o1);
         }
         fence_proxy_async_smem();                // generic-proxy writes -> visible to the tensor core
       }
@@ -299,6 +302,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int rl = quarter * 32 + lane;          // local row
     const int row = row0 + rl;
     const int c0 = chalf * COLS_PER_FOLD;
+    const uint32_t szs_a = smem_u32(szs), sums_a = smem_u32(sums);
     grid_dependency_wait();
     for (int i = ft; i < TN; i += FOLD_THREADS)
       sxs[i] = (tok0 + i < p.T && p.scale_x) ? __half2float(ld_plain(p.scale_x + tok0 + i)) : 0.f;
@@ -349,8 +353,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
-        szs[(lhalf * 8 + 2 * i) * ROWS + lrow] = make_float2(s2.x * 0.0625f, s2.x * z2.x);
-        szs[(lhalf * 8 + 2 * i + 1) * ROWS + lrow] = make_float2(s2.y * 0.0625f, s2.y * z2.y);
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * 0.0625f, s2.x * z2.x));
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * 0.0625f, s2.y * z2.y));
       }
 #pragma unroll
       for (int k = 0; k < SUMS_PER_THREAD; ++k) sums[ft + k * FOLD_THREADS] = psum[k];
@@ -369,7 +373,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       float f = 0.f, c = 0.f;
       int blk = 0;
       if (is_dense) {
-        const float2 v = szs[(n % SZ_CHUNK) * ROWS + rl];
+        const float2 v = lds_f2(szs_a + ((n % SZ_CHUNK) * ROWS + rl) * 8);
         f = v.x;
         c = v.y;
       } else {
@@ -382,16 +386,19 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (n >> 1) & 1, SITE_PRE_ACCFULL));
       if (!ok) continue;
       tc_fence_after();
-      const float* srow = sums + (n % SZ_CHUNK) * TN + c0;
+      const uint32_t srow = sums_a + ((n % SZ_CHUNK) * TN + c0) * 4;
 #pragma unroll
       for (int cc = 0; cc < COLS_PER_FOLD; cc += 32) {
         uint32_t a[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TN + c0 + cc, a);
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          const float2 sx = is_dense ? *reinterpret_cast<const float2*>(srow + cc + i) : make_float2(0.f, 0.f);
-          const float2 t = fma2(make_float2(-c, -c), sx, y2[(cc + i) >> 1]);
-          y2[(cc + i) >> 1] = fma2(make_float2(__int2float_rn((int)a[i]), __int2float_rn((int)a[i + 1])), make_float2(f, f), t);
+        for (int i = 0; i < 32; i += 4) {
+          // the same four group sums for every lane: one broadcast 128-bit load
+          const float4 sx = is_dense ? lds_f4(srow + (cc + i) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+          const float2 t0 = fma2(make_float2(-c, -c), make_float2(sx.x, sx.y), y2[(cc + i) >> 1]);
+          const float2 t1 = fma2(make_float2(-c, -c), make_float2(sx.z, sx.w), y2[((cc + i) >> 1) + 1]);
+          y2[(cc + i) >> 1] = fma2(make_float2(__int2float_rn((int)a[i]), __int2float_rn((int)a[i + 1])), make_float2(f, f), t0);
+          y2[((cc + i) >> 1) + 1] = fma2(make_float2(__int2float_rn((int)a[i + 2]), __int2float_rn((int)a[i + 3])), make_float2(f, f), t1);
         }
         if (DUMP) {
 #pragma unroll

@@ -226,7 +226,6 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   // expanded activations: given by the caller, or built here from the packed codes
   const void* XE = a.XE;
   const float* sumxf = a.sumxf;
-  bool pdl = a.pdl;
   if (XE == nullptr) {
     const WsLayout wl = ws_layout(a.T, a.K);
     if (a.ws == nullptr || a.ws_bytes < wl.total)
@@ -236,7 +235,6 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
     if (rc) return rc;
     XE = ws + wl.xe;
     sumxf = a.sum_X ? reinterpret_cast<float*>(ws + wl.sumxf) : nullptr;
-    pdl = true;
   }
   if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
 
@@ -283,7 +281,6 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(decode): %s", cudaGetErrorString(e));
 
-  (void)pdl;
   e = launch_ex(kern, dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
                 plan.split, tm_low, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));

@@ -103,6 +103,18 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int si
   return false;
 }
 
+// The same for a role with slack (a producer that runs ahead of its consumer): it
+// sleeps between polls from the first miss on, so that its polling does not take
+// issue slots from the warps that do the arithmetic.  The bound in time is the same.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int site) {
+  for (uint32_t i = 0; i < WAIT_POLL_LIMIT; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(i > 4096 ? 64 : 32);
+  }
+  record_error(site, parity);
+  return false;
+}
+
 // ---------------------------------------------------------------- proxies / PDL
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -46,10 +46,15 @@ constexpr int X_BYTES = TN * BCOL;                // 16384
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
 constexpr int TMEM_COLS = 2 * TN;                 // two int32 accumulator buffers
 
-constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_UNPACK0 = 2, N_UNPACK_WARPS = 4, WARP_FOLD0 = 6, N_FOLD_WARPS = 8;
-constexpr int THREADS = (WARP_FOLD0 + N_FOLD_WARPS) * 32;   // 448
+#ifndef W4A4_FOLD_WARPS
+#define W4A4_FOLD_WARPS 8
+#endif
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_UNPACK0 = 2, N_UNPACK_WARPS = 4, WARP_FOLD0 = 6;
+constexpr int N_FOLD_WARPS = W4A4_FOLD_WARPS;     // a multiple of 4: a warp reads only its quarter of the TMEM lanes
+constexpr int THREADS = (WARP_FOLD0 + N_FOLD_WARPS) * 32;
 constexpr int FOLD_THREADS = N_FOLD_WARPS * 32;
-constexpr int COLS_PER_FOLD = TN / 2;             // a fold thread owns one row and half of the tokens
+constexpr int COLS_PER_FOLD = TN / (N_FOLD_WARPS / 4);   // a fold thread owns one row and this many tokens
+static_assert(N_FOLD_WARPS % 4 == 0 && COLS_PER_FOLD % 32 == 0, "fold warps tile the accumulator in 32-lane x 32-column pieces");
 
 enum : int {
   SITE_PRE_WEMPTY = 16, SITE_PRE_WFULL, SITE_PRE_AEMPTY, SITE_PRE_AFULL, SITE_PRE_XEMPTY, SITE_PRE_XFULL,
@@ -218,12 +223,12 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       uint32_t wph = 1, xph = 1;
       for (int n = 0; n < n_steps && ok; ++n) {
         if (n >= n_pre) {
-          ok = mbar_wait(&w_empty[ws], wph, SITE_PRE_WEMPTY);
+          ok = mbar_wait_relaxed(&w_empty[ws], wph, SITE_PRE_WEMPTY);
           if (!ok) break;
           issue_w(n, ws);
         }
         if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
-        ok = mbar_wait(&x_empty[xs], xph, SITE_PRE_XEMPTY);
+        ok = mbar_wait_relaxed(&x_empty[xs], xph, SITE_PRE_XEMPTY);
         if (!ok) break;
         const int g = n < p.nd ? n : ld_plain(p.hp_col_indices + b_lo + n - p.nd);
         mbar_arrive_expect_tx(&x_full[xs], X_BYTES);
@@ -240,9 +245,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       uint32_t ph = 0, xph = 0;
       for (int n = 0; n < n_steps && ok; ++n) {
         const int buf = n & 1;
-        ok = mbar_wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, SITE_PRE_ACCEMPTY);
-        if (ok) ok = mbar_wait(&a_full[st], ph, SITE_PRE_AFULL);
-        if (ok) ok = mbar_wait(&x_full[xs], xph, SITE_PRE_XFULL);
+        ok = mbar_wait_relaxed(&acc_empty[buf], ((n >> 1) & 1) ^ 1, SITE_PRE_ACCEMPTY);
+        if (ok) ok = mbar_wait_relaxed(&a_full[st], ph, SITE_PRE_AFULL);
+        if (ok) ok = mbar_wait_relaxed(&x_full[xs], xph, SITE_PRE_XFULL);
         if (!ok) break;
         tc_fence_after();
         const uint64_t adesc = smem_desc_sw128(a_ring + st * A_BYTES);
@@ -265,8 +270,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     int ws = 0, as = 0;
     uint32_t wph = 0, aph = 1;
     for (int n = 0; n < n_steps; ++n) {
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&w_full[ws], wph, SITE_PRE_WFULL));
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&a_empty[as], aph, SITE_PRE_AEMPTY));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&w_full[ws], wph, SITE_PRE_WFULL));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&a_empty[as], aph, SITE_PRE_AEMPTY));
       if (ok) {
         tc_fence_after();      // the slot was last read by tcgen05.mma
         const uint32_t src = wp_a + ws * WP_BYTES;
@@ -298,7 +303,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     // ------------------------------------------------------------ fold warps
     const int ft = tid - WARP_FOLD0 * 32;        // 0..255
     const int quarter = warp & 3;                // TMEM lanes this warp may read: 32*quarter .. +31
-    const int chalf = (warp - WARP_FOLD0) >> 2;  // which half of the tokens
+    const int chalf = (warp - WARP_FOLD0) >> 2;  // which share of the tokens
     const int rl = quarter * 32 + lane;          // local row
     const int row = row0 + rl;
     const int c0 = chalf * COLS_PER_FOLD;
@@ -330,7 +335,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       ps = pz = make_uint4(0, 0, 0, 0);
       const int grow = row0 + lrow;
       const int g = gwin + lhalf * 8;
-      if (p.scale_u4 == nullptr || grow >= p.N || g >= p.ng) return;
+      if (p.scale_u4 == nullptr || ft >= 2 * ROWS || grow >= p.N || g >= p.ng) return;
       const __half* srow = p.scale_u4 + (size_t)grow * p.ng;
       const __half* zrow = p.zero_u4 ? p.zero_u4 + (size_t)grow * p.ng : nullptr;
       if (p.sz_vec) {
@@ -352,6 +357,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const __half2* hz = reinterpret_cast<const __half2*>(&pz);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
+        if (ft >= 2 * ROWS) break;
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
         sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * 0.0625f, s2.x * z2.x));
         sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * 0.0625f, s2.y * z2.y));

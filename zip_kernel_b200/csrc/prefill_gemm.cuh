@@ -11,15 +11,23 @@
 // Per K-group of 128 (and per residual block of the block-row, which is just one
 // more K-step):
 //   * the producer warp issues two non-multicast asynchronous copies: the packed
-//     weight tile (TMA, 128 x 64 bytes) and the tokens' expanded codes (one bulk
-//     copy of TN x 128 bytes: the expanded layout is group-major and pre-swizzled,
-//     i.e. already the K-major operand layout tcgen05 reads);
-//   * four unpack warps widen the weight tile into a second shared-memory ring
-//     in the same swizzled K-major layout (s8 lanes scaled by 16, three logic ops
-//     per 8 codes, same element permutation as the activations);
-//   * one thread issues four tcgen05.mma kind::i8 (K = 32 each) into a fresh
-//     int32 accumulator in TMEM (two accumulator buffers alternate) and commits
-//     to mbarriers that release the operand slots and publish the accumulator;
+//     weight tile (TMA, 128 x 64 bytes, 64-byte swizzle so that a thread can read
+//     its whole row without bank conflicts) and the tokens' expanded codes (one
+//     bulk copy of TN x 128 bytes: the expanded layout is group-major and
+//     pre-swizzled, i.e. already the K-major operand layout tcgen05 reads);
+//   * four unpack warps widen the weight tile (s8 lanes scaled by 16, three logic
+//     ops per 8 codes, same element permutation as the activations) and store it
+//     straight into TENSOR MEMORY with tcgen05.st: thread = weight row = TMEM
+//     lane, 32 columns of four s8 each.  The MMA takes its A operand from there,
+//     so the widened weights never touch shared memory: per K-step shared memory
+//     carries 24 KB of copies, 8 KB of unpack reads and 16 KB of B-operand reads
+//     instead of 96 KB, and shared-memory bandwidth is what a 128 x 128 tile
+//     runs out of first;
+//   * one thread issues four tcgen05.mma kind::i8 (K = 32 each, A from TMEM, B
+//     from shared memory) into a fresh int32 accumulator in TMEM (two accumulator
+//     buffers alternate) and commits ONCE to a ring of "step done" mbarriers:
+//     the fold warps (accumulator ready), the unpack warps (A buffer free again)
+//     and the producer (activation slot free again) all wait on that ring;
 //   * eight fold warps read the accumulator with tcgen05.ld and fold it in fp32:
 //     y += acc * (s/16) - (s*z) * sumX  (per-(row, group) scales make this drain
 //     per group inherent to the contract), keeping y (128 x TN fp32) in registers.
@@ -38,13 +46,14 @@ namespace pre {
 constexpr int ROWS = 128;                 // MMA M
 constexpr int TN = 128;                   // tokens per CTA = MMA N
 constexpr int W_STAGES = 6;               // packed weight tiles in flight (8 KB each)
-constexpr int A_STAGES = 2;               // widened weight tiles (16 KB each, produced locally)
-constexpr int X_STAGES = 6;               // activation tiles in flight (16 KB each)
+constexpr int A_BUFS = 2;                 // widened weight tiles in tensor memory
+constexpr int X_STAGES = 6;               // activation tiles in flight (16 KB each) = depth of the "step done" ring
 constexpr int WP_BYTES = ROWS * GROUP_BYTES;      // 8192
-constexpr int A_BYTES = ROWS * BCOL;              // 16384
 constexpr int X_BYTES = TN * BCOL;                // 16384
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
-constexpr int TMEM_COLS = 2 * TN;                 // two int32 accumulator buffers
+constexpr int A_COLS = BCOL / 4;                  // 32 TMEM columns hold one widened row of 128 s8
+constexpr int A_COL0 = 2 * TN;                    // after the two int32 accumulator buffers
+constexpr int TMEM_COLS = 512;                    // power of two >= 2 * TN + A_BUFS * A_COLS
 
 #ifndef W4A4_FOLD_WARPS
 #define W4A4_FOLD_WARPS 8
@@ -85,11 +94,11 @@ inline bool supported(int T, int K, int N) { return T >= 1 && K >= 128 && N >= 1
 
 struct SmemLayout {
   static constexpr size_t wp = 0;
-  static constexpr size_t a = wp + (size_t)W_STAGES * WP_BYTES;
-  static constexpr size_t x = a + (size_t)A_STAGES * A_BYTES;
+  static constexpr size_t x = wp + (size_t)W_STAGES * WP_BYTES;
   static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float2 [SZ_CHUNK][128]
-  static constexpr size_t sums = sz + (size_t)SZ_CHUNK * ROWS * 8;              // float  [SZ_CHUNK][TN]
-  static constexpr size_t sxs = sums + (size_t)SZ_CHUNK * TN * 4;               // float  [TN]
+  static constexpr size_t sums = sz + (size_t)SZ_CHUNK * ROWS * 8;              // float  [2][SZ_CHUNK][TN]
+  static constexpr size_t raw = sums + (size_t)2 * SZ_CHUNK * TN * 4;           // 2 x 16 bytes per (row, half): fp16 scales, zeros
+  static constexpr size_t sxs = raw + (size_t)2 * ROWS * 32;                    // float  [TN]
   static constexpr size_t bars = sxs + (size_t)TN * 4;
   static constexpr size_t total = bars + 256;
 };
@@ -125,6 +134,26 @@ __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC), "r"(accumulate)
       : "memory");
 }
+// the same with the A operand in tensor memory (row = lane, four s8 per 32-bit column)
+__device__ __forceinline__ void umma_i8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(IDESC), "r"(accumulate)
+      : "memory");
+}
+// 32 consecutive 32-bit columns of the calling thread's TMEM lane
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,"
+      "%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
 // arrives on the mbarrier once every tcgen05.mma issued so far by this thread has completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -159,7 +188,6 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* wp_ring = sm + SmemLayout::wp;
-  unsigned char* a_ring = sm + SmemLayout::a;
   unsigned char* x_ring = sm + SmemLayout::x;
   float2* szs = reinterpret_cast<float2*>(sm + SmemLayout::sz);
   float* sums = reinterpret_cast<float*>(sm + SmemLayout::sums);
@@ -167,12 +195,10 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SmemLayout::bars);
   uint64_t* w_full = bars;                      // [W_STAGES]
   uint64_t* w_empty = w_full + W_STAGES;        // [W_STAGES]
-  uint64_t* a_full = w_empty + W_STAGES;        // [A_STAGES]
-  uint64_t* a_empty = a_full + A_STAGES;        // [A_STAGES]
-  uint64_t* x_full = a_empty + A_STAGES;        // [X_STAGES]
-  uint64_t* x_empty = x_full + X_STAGES;        // [X_STAGES]
-  uint64_t* acc_full = x_empty + X_STAGES;      // [2]
-  uint64_t* acc_empty = acc_full + 2;           // [2]
+  uint64_t* a_full = w_empty + W_STAGES;        // [A_BUFS]   widened tile stored to tensor memory
+  uint64_t* x_full = a_full + A_BUFS;           // [X_STAGES]
+  uint64_t* done = x_full + X_STAGES;           // [X_STAGES] the MMAs of step n (slot n % X_STAGES) have completed
+  uint64_t* acc_empty = done + X_STAGES;        // [2]
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
 
   grid_launch_dependents();
@@ -185,9 +211,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   if (tid == 0) {
     for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
-    for (int i = 0; i < A_STAGES; ++i) { mbar_init(&a_full[i], N_UNPACK_WARPS); mbar_init(&a_empty[i], 1); }
-    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&x_full[i], 1); mbar_init(&x_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], N_FOLD_WARPS); }
+    for (int i = 0; i < A_BUFS; ++i) mbar_init(&a_full[i], N_UNPACK_WARPS);
+    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&x_full[i], 1); mbar_init(&done[i], 1); }
+    for (int i = 0; i < 2; ++i) mbar_init(&acc_empty[i], N_FOLD_WARPS);
     mbar_fence_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_wh);
@@ -220,7 +246,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int n = 0; n < n_pre; ++n) issue_w(n, n);
       grid_dependency_wait();
       int ws = 0, xs = 0;
-      uint32_t wph = 1, xph = 1;
+      uint32_t wph = 1;
       for (int n = 0; n < n_steps && ok; ++n) {
         if (n >= n_pre) {
           ok = mbar_wait_relaxed(&w_empty[ws], wph, SITE_PRE_WEMPTY);
@@ -228,76 +254,79 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           issue_w(n, ws);
         }
         if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
-        ok = mbar_wait_relaxed(&x_empty[xs], xph, SITE_PRE_XEMPTY);
+        // the slot is free once the MMAs of step n - X_STAGES have completed
+        if (n >= X_STAGES) ok = mbar_wait_relaxed(&done[xs], ((n - X_STAGES) / X_STAGES) & 1, SITE_PRE_XEMPTY);
         if (!ok) break;
         const int g = n < p.nd ? n : ld_plain(p.hp_col_indices + b_lo + n - p.nd);
         mbar_arrive_expect_tx(&x_full[xs], X_BYTES);
         // TN consecutive tokens of one group: contiguous and already in operand layout
         bulk_load_1d(x_ring + xs * X_BYTES, p.XE + ((size_t)g * p.t_pad + tok0) * BCOL, X_BYTES, &x_full[xs]);
-        if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
+        if (++xs == X_STAGES) xs = 0;
       }
     }
   } else if (warp == WARP_MMA) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       bool ok = true;
-      int st = 0, xs = 0;
-      uint32_t ph = 0, xph = 0;
+      int xs = 0;
+      uint32_t xph = 0;
       for (int n = 0; n < n_steps && ok; ++n) {
-        const int buf = n & 1;
+        const int buf = n & 1;          // accumulator buffer and A buffer alternate together
         ok = mbar_wait_relaxed(&acc_empty[buf], ((n >> 1) & 1) ^ 1, SITE_PRE_ACCEMPTY);
-        if (ok) ok = mbar_wait_relaxed(&a_full[st], ph, SITE_PRE_AFULL);
+        if (ok) ok = mbar_wait_relaxed(&a_full[buf], (n >> 1) & 1, SITE_PRE_AFULL);
         if (ok) ok = mbar_wait_relaxed(&x_full[xs], xph, SITE_PRE_XFULL);
         if (!ok) break;
         tc_fence_after();
-        const uint64_t adesc = smem_desc_sw128(a_ring + st * A_BYTES);
         const uint64_t bdesc = smem_desc_sw128(x_ring + xs * X_BYTES);
         const uint32_t d = tmem_base + buf * TN;
+        const uint32_t a = tmem_base + A_COL0 + buf * A_COLS;
 #pragma unroll
-        for (int j = 0; j < 4; ++j) umma_i8(d, adesc + j * 2, bdesc + j * 2, j > 0);   // +32 bytes per K = 32
-        umma_commit(&a_empty[st]);
-        umma_commit(&x_empty[xs]);
-        umma_commit(&acc_full[buf]);
-        if (++st == A_STAGES) { st = 0; ph ^= 1; }
+        for (int j = 0; j < 4; ++j) umma_i8_ta(d, a + j * 8, bdesc + j * 2, j > 0);   // K = 32: 8 columns of A, 32 bytes of B
+        umma_commit(&done[xs]);
         if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
       }
     }
   } else if (warp < WARP_FOLD0) {
     // ------------------------------------------------------------ unpack warps
-    const int ut = tid - WARP_UNPACK0 * 32;      // 0..127
-    const uint32_t wp_a = smem_u32(wp_ring), a_a = smem_u32(a_ring);
+    // thread = weight row = TMEM lane: warp w may touch lanes 32 * (w % 4) .. + 31
+    const int urow = (warp & 3) * 32 + lane;
+    const uint32_t wp_a = smem_u32(wp_ring);
+    const uint32_t a_lane = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + A_COL0;
     bool ok = true;
-    int ws = 0, as = 0;
-    uint32_t wph = 0, aph = 1;
+    int ws = 0;
+    uint32_t wph = 0;
     for (int n = 0; n < n_steps; ++n) {
+      const int buf = n & 1;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&w_full[ws], wph, SITE_PRE_WFULL));
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&a_empty[as], aph, SITE_PRE_AEMPTY));
+      // the A buffer was last read by the MMAs of step n - 2
+      if (ok && n >= A_BUFS)
+        ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&done[(n - A_BUFS) % X_STAGES], ((n - A_BUFS) / X_STAGES) & 1, SITE_PRE_AEMPTY));
       if (ok) {
-        tc_fence_after();      // the slot was last read by tcgen05.mma
-        const uint32_t src = wp_a + ws * WP_BYTES;
-        const uint32_t dst = a_a + as * A_BYTES;
+        tc_fence_after();
+        // the row's 64 packed bytes: four 16-byte chunks, stored at chunk ^ ((row >> 1) & 3) by the 64-byte swizzle
+        const uint32_t src = wp_a + ws * WP_BYTES + urow * GROUP_BYTES;
         uint4 w[4];
 #pragma unroll
-        for (int pass = 0; pass < 4; ++pass) w[pass] = lds_v4(src + (pass * 128 + ut) * 16);
+        for (int c = 0; c < 4; ++c) w[c] = lds_v4(src + ((c ^ ((urow >> 1) & 3)) << 4));
+        uint32_t v[32];
 #pragma unroll
-        for (int pass = 0; pass < 4; ++pass) {
-          const int item = pass * 128 + ut;      // 16 packed bytes = 32 codes
-          const int row = item >> 2, pc = item & 3;
-          const uint4 o0 = make_uint4(nib_lo_x16(w[pass].x), nib_hi_x16(w[pass].x), nib_lo_x16(w[pass].y), nib_hi_x16(w[pass].y));
-          const uint4 o1 = make_uint4(nib_lo_x16(w[pass].z), nib_hi_x16(w[pass].z), nib_lo_x16(w[pass].w), nib_hi_x16(w[pass].w));
-          const uint32_t drow = dst + row * BCOL;
-          sts_v4(drow + (((2 * pc) ^ (row & 7)) << 4), o0);
-          sts_v4(drow + (((2 * pc + 1) ^ (row & 7)) << 4), o1);
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t q[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            v[(c * 4 + e) * 2] = nib_lo_x16(q[e]);
+            v[(c * 4 + e) * 2 + 1] = nib_hi_x16(q[e]);
+          }
         }
-        fence_proxy_async_smem();                // generic-proxy writes -> visible to the tensor core
+        tmem_st32(a_lane + buf * A_COLS, v);
+        tc_fence_before();
       }
       __syncwarp();
       if (ok && lane == 0) {
         mbar_arrive(&w_empty[ws]);
-        mbar_arrive(&a_full[as]);
+        mbar_arrive(&a_full[buf]);
       }
       if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
-      if (++as == A_STAGES) { as = 0; aph ^= 1; }
     }
   } else {
     // ------------------------------------------------------------ fold warps
@@ -317,64 +346,71 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
     for (int i = 0; i < COLS_PER_FOLD / 2; ++i) y2[i] = make_float2(0.f, 0.f);
 
-    // scale/zero window: thread ft fetches 8 groups of row ft/2; sums window: 16 groups x TN tokens
+    // Scale/zero/sums windows of 16 groups.  The next window travels as cp.async
+    // copies while the current one is folded, so it occupies no registers: thread ft
+    // copies the fp16 scales and zeros of 8 groups of row ft/2 into a staging slot of
+    // its own, and 4-byte pieces of the tokens' group sums straight into the other
+    // half of the double-buffered sums table.  At the window boundary each thread
+    // turns its slot into (scale/16, scale*zero) pairs of the shared table.
     const int lrow = ft >> 1, lhalf = ft & 1;
-    constexpr int SUMS_PER_THREAD = SZ_CHUNK * TN / FOLD_THREADS;   // 8
-    uint4 ps, pz;
-    float psum[SUMS_PER_THREAD];
-    auto fetch_sz = [&](int gwin) {
-      // group sums of the CTA's tokens for the window's groups
+    constexpr int SUMS_PER_THREAD = SZ_CHUNK * TN / FOLD_THREADS;
+    const uint32_t raw_a = smem_u32(sm + SmemLayout::raw) + ft * 32;
+    auto issue_window = [&](int gwin, int sel) {
 #pragma unroll
       for (int k = 0; k < SUMS_PER_THREAD; ++k) {
         const int i = ft + k * FOLD_THREADS;
         const int gl = i / TN, t = i - gl * TN;
         const int g = gwin + gl, tok = tok0 + t;
-        psum[k] = 0.f;
-        if (p.sumxf && g < p.ng && tok < p.T) psum[k] = ld_plain(p.sumxf + ((size_t)(tok >> 4) * p.ng + g) * 16 + (tok & 15));
+        const uint32_t dst = sums_a + (sel * SZ_CHUNK * TN + i) * 4;
+        if (p.sumxf && g < p.ng && tok < p.T) cp_async_4(dst, p.sumxf + ((size_t)(tok >> 4) * p.ng + g) * 16 + (tok & 15));
+        else sts_f1(dst, 0.f);
       }
-      ps = pz = make_uint4(0, 0, 0, 0);
-      const int grow = row0 + lrow;
-      const int g = gwin + lhalf * 8;
-      if (p.scale_u4 == nullptr || ft >= 2 * ROWS || grow >= p.N || g >= p.ng) return;
-      const __half* srow = p.scale_u4 + (size_t)grow * p.ng;
-      const __half* zrow = p.zero_u4 ? p.zero_u4 + (size_t)grow * p.ng : nullptr;
-      if (p.sz_vec) {
-        ps = *reinterpret_cast<const uint4*>(srow + g);
-        if (zrow) pz = *reinterpret_cast<const uint4*>(zrow + g);
-      } else {
-        __half hs[8], hz[8];
+      if (ft < 2 * ROWS) {
+        const int grow = row0 + lrow;
+        const int g = gwin + lhalf * 8;
+        const bool live = p.scale_u4 != nullptr && grow < p.N && g < p.ng;
+        const __half* srow = p.scale_u4 + (size_t)grow * p.ng;
+        const __half* zrow = p.zero_u4 ? p.zero_u4 + (size_t)grow * p.ng : nullptr;
+        if (live && p.sz_vec) {
+          cp_async_16(raw_a, srow + g);
+          if (zrow) cp_async_16(raw_a + 16, zrow + g);
+          else sts_v4(raw_a + 16, make_uint4(0, 0, 0, 0));
+        } else {
+          __align__(16) __half hs[8], hz[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          hs[i] = (g + i < p.ng) ? srow[g + i] : __float2half(0.f);
-          hz[i] = (g + i < p.ng && zrow) ? zrow[g + i] : __float2half(0.f);
+          for (int i = 0; i < 8; ++i) {
+            hs[i] = (live && g + i < p.ng) ? srow[g + i] : __float2half(0.f);
+            hz[i] = (live && g + i < p.ng && zrow) ? zrow[g + i] : __float2half(0.f);
+          }
+          sts_v4(raw_a, *reinterpret_cast<uint4*>(&hs[0]));
+          sts_v4(raw_a + 16, *reinterpret_cast<uint4*>(&hz[0]));
         }
-        ps = *reinterpret_cast<uint4*>(&hs[0]);
-        pz = *reinterpret_cast<uint4*>(&hz[0]);
       }
+      cp_async_commit();
     };
-    auto park_window = [&](int gwin) {
+    auto park_window = [&]() {
+      if (ft >= 2 * ROWS) return;
+      const uint4 ps = lds_v4(raw_a), pz = lds_v4(raw_a + 16);
       const __half2* hs = reinterpret_cast<const __half2*>(&ps);
       const __half2* hz = reinterpret_cast<const __half2*>(&pz);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        if (ft >= 2 * ROWS) break;
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
         sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * 0.0625f, s2.x * z2.x));
         sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * 0.0625f, s2.y * z2.y));
       }
-#pragma unroll
-      for (int k = 0; k < SUMS_PER_THREAD; ++k) sums[ft + k * FOLD_THREADS] = psum[k];
     };
 
     bool ok = true;
-    if (p.nd > 0) fetch_sz(0);
+    if (p.nd > 0) issue_window(0, 0);
     for (int n = 0; n < n_steps; ++n) {
       const bool is_dense = n < p.nd;
       if (is_dense && (n % SZ_CHUNK) == 0) {
+        cp_async_wait_all();                                                // this thread's pieces of the window have landed
         asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");   // previous window no longer read
-        park_window(n);
-        if (n + SZ_CHUNK < p.nd) fetch_sz(n + SZ_CHUNK);
-        asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");
+        park_window();
+        if (n + SZ_CHUNK < p.nd) issue_window(n + SZ_CHUNK, ((n / SZ_CHUNK) + 1) & 1);
+        asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");   // table and sums of this window visible to all
       }
       float f = 0.f, c = 0.f;
       int blk = 0;
@@ -389,10 +425,10 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
               p.sparse_weight;
       }
       const int buf = n & 1;
-      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&acc_full[buf], (n >> 1) & 1, SITE_PRE_ACCFULL));
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&done[n % X_STAGES], (n / X_STAGES) & 1, SITE_PRE_ACCFULL));
       if (!ok) continue;
       tc_fence_after();
-      const uint32_t srow = sums_a + ((n % SZ_CHUNK) * TN + c0) * 4;
+      const uint32_t srow = sums_a + ((((n / SZ_CHUNK) & 1) * SZ_CHUNK + (n % SZ_CHUNK)) * TN + c0) * 4;
 #pragma unroll
       for (int cc = 0; cc < COLS_PER_FOLD; cc += 32) {
         uint32_t a[32];

@@ -314,10 +314,10 @@ int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
   CUtensorMap tm_w, tm_wh;
   // the operand that is switched off borrows the other one's map and is never read
   int rc = make_map(&tm_w, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
-                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
   if (rc) return rc;
   rc = make_map(&tm_wh, has_sparse ? a.W_high : a.W_low, has_sparse ? 64 : (uint64_t)a.K / 2,
-                has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+                has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
   if (rc) return rc;
 
   pre::Params p;

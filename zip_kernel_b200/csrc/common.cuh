@@ -56,6 +56,10 @@ __device__ __forceinline__ float4 lds_f4(uint32_t a) {
   asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
   return v;
 }
+// two packed fp32 pairs (the operand form of the f32x2 instructions) with one load
+__device__ __forceinline__ void lds_f32x2_pair(uint32_t a, unsigned long long& lo, unsigned long long& hi) {
+  asm volatile("ld.shared.v2.u64 {%0,%1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(a));
+}
 __device__ __forceinline__ void sts_v4(uint32_t a, const uint4& v) {
   asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
@@ -74,6 +78,33 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void sts_f1(uint32_t a, float v) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(v) : "memory"); }
+
+// ---------------------------------------------------------------- packed fp32 pairs
+// The f32x2 instructions take two floats in one 64-bit register.  Values that
+// live in that form (accumulators, broadcast scales) are kept as 64-bit integers
+// so that no pack/unpack moves surround every instruction.
+typedef unsigned long long f32x2_t;
+__device__ __forceinline__ f32x2_t pack_f32x2(float lo, float hi) {
+  f32x2_t d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "f"(lo), "f"(hi));
+  return d;
+}
+__device__ __forceinline__ float2 unpack_f32x2(f32x2_t v) {
+  float2 d;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(v));
+  return d;
+}
+__device__ __forceinline__ f32x2_t fma_f32x2(f32x2_t a, f32x2_t b, f32x2_t c) {
+  f32x2_t d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+// two int32 -> one packed pair of floats
+__device__ __forceinline__ f32x2_t cvt_s32x2_f32x2(uint32_t lo, uint32_t hi) {
+  f32x2_t d;
+  asm("{\n\t.reg .f32 l, h;\n\tcvt.rn.f32.s32 l, %1;\n\tcvt.rn.f32.s32 h, %2;\n\tmov.b64 %0, {l, h};\n\t}" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
 
 // ---------------------------------------------------------------- mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {

@@ -342,9 +342,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       sxs[i] = (tok0 + i < p.T && p.scale_x) ? __half2float(ld_plain(p.scale_x + tok0 + i)) : 0.f;
     asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");
 
-    float2 y2[COLS_PER_FOLD / 2];
+    f32x2_t y2[COLS_PER_FOLD / 2];      // the thread's row x COLS_PER_FOLD tokens, two tokens per register pair
 #pragma unroll
-    for (int i = 0; i < COLS_PER_FOLD / 2; ++i) y2[i] = make_float2(0.f, 0.f);
+    for (int i = 0; i < COLS_PER_FOLD / 2; ++i) y2[i] = 0ull;
 
     // Scale/zero/sums windows of 16 groups.  The next window travels as cp.async
     // copies while the current one is folded, so it occupies no registers: thread ft
@@ -429,18 +429,26 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (!ok) continue;
       tc_fence_after();
       const uint32_t srow = sums_a + ((((n / SZ_CHUNK) & 1) * SZ_CHUNK + (n % SZ_CHUNK)) * TN + c0) * 4;
+      const f32x2_t f2 = pack_f32x2(f, f), nc2 = pack_f32x2(-c, -c);
 #pragma unroll
       for (int cc = 0; cc < COLS_PER_FOLD; cc += 32) {
         uint32_t a[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TN + c0 + cc, a);
+        if (is_dense) {
 #pragma unroll
-        for (int i = 0; i < 32; i += 4) {
-          // the same four group sums for every lane: one broadcast 128-bit load
-          const float4 sx = is_dense ? lds_f4(srow + (cc + i) * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-          const float2 t0 = fma2(make_float2(-c, -c), make_float2(sx.x, sx.y), y2[(cc + i) >> 1]);
-          const float2 t1 = fma2(make_float2(-c, -c), make_float2(sx.z, sx.w), y2[((cc + i) >> 1) + 1]);
-          y2[(cc + i) >> 1] = fma2(make_float2(__int2float_rn((int)a[i]), __int2float_rn((int)a[i + 1])), make_float2(f, f), t0);
-          y2[((cc + i) >> 1) + 1] = fma2(make_float2(__int2float_rn((int)a[i + 2]), __int2float_rn((int)a[i + 3])), make_float2(f, f), t1);
+          for (int i = 0; i < 32; i += 4) {
+            // the same four group sums for every lane: one broadcast 128-bit load
+            f32x2_t sx0, sx1;
+            lds_f32x2_pair(srow + (cc + i) * 4, sx0, sx1);
+            const f32x2_t t0 = fma_f32x2(nc2, sx0, y2[(cc + i) >> 1]);
+            const f32x2_t t1 = fma_f32x2(nc2, sx1, y2[((cc + i) >> 1) + 1]);
+            y2[(cc + i) >> 1] = fma_f32x2(cvt_s32x2_f32x2(a[i], a[i + 1]), f2, t0);
+            y2[((cc + i) >> 1) + 1] = fma_f32x2(cvt_s32x2_f32x2(a[i + 2], a[i + 3]), f2, t1);
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; i += 2)
+            y2[(cc + i) >> 1] = fma_f32x2(cvt_s32x2_f32x2(a[i], a[i + 1]), f2, y2[(cc + i) >> 1]);
         }
         if (DUMP) {
 #pragma unroll
@@ -477,8 +485,10 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         for (int i = 0; i < COLS_PER_FOLD; i += 8) {
           __align__(16) __half2 h[4];
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            h[k] = __floats2half2_rn(y2[(i >> 1) + k].x * sxs[c0 + i + 2 * k], y2[(i >> 1) + k].y * sxs[c0 + i + 2 * k + 1]);
+          for (int k = 0; k < 4; ++k) {
+            const float2 v = unpack_f32x2(y2[(i >> 1) + k]);
+            h[k] = __floats2half2_rn(v.x * sxs[c0 + i + 2 * k], v.y * sxs[c0 + i + 2 * k + 1]);
+          }
           *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<uint4*>(h);
         }
       } else {
@@ -487,7 +497,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const int tok = tok0 + c0 + i;
           if (tok < p.T)
             p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] =
-                __float2half_rn(((i & 1) ? y2[i >> 1].y : y2[i >> 1].x) * sxs[c0 + i]);
+                __float2half_rn(((i & 1) ? unpack_f32x2(y2[i >> 1]).y : unpack_f32x2(y2[i >> 1]).x) * sxs[c0 + i]);
         }
       }
     }

@@ -38,7 +38,11 @@ DENSITY = 0.05
 L2_BYTES = 126 * 1024 * 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per GEMM launch (mean over the
 # workload's launches) from the profiler capture summarised under profiles/
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {
+    "decode": 30.49e6,            # profiles/decode_gemm_kernel_dram_traffic.md
+    "gate_up_m16": 66.16e6,       # profiles/decode_gemm_kernel_gate_up_m16.md
+    "prefill_gate_up": 299.8e6,   # profiles/prefill_gemm_kernel_gate_up_m2048.md
+}
 
 
 def workload_items(name):

@@ -41,6 +41,7 @@ struct QuantParams {
   int t_pad;              // tokens rounded up to 16: row pitch of the expanded layout
   int vec_ok;             // 1 when every row start is 16-byte aligned
   int C;                  // CTAs (cluster size) per token; divides K/128
+  int stage_row;          // 1: perm given and the dynamic shared memory holds the whole raw row behind the slice
 };
 
 __device__ __forceinline__ uint2 expand_word(uint32_t w) { return make_uint2(nib_lo_s8(w), nib_hi_s8(w)); }
@@ -69,21 +70,16 @@ __device__ __forceinline__ float half_abs_max8(const uint4& v, float m) {
   return m;
 }
 
-__global__ void __launch_bounds__(QUANT_THREADS)
-act_quant_kernel(const QuantParams p) {
-  extern __shared__ __align__(16) unsigned char quant_smem[];
+// Quantises slice `rank` (of p.C) of token t with a CTA of NTHREADS threads.  Every
+// thread of the CTA calls it; for p.C > 1 the CTAs of a cluster call it together
+// with rank = their cluster rank.  `quant_smem` (16-byte aligned) holds the slice
+// (2 * K / C bytes) and, when p.stage_row is set, the raw row behind it.
+template <int NTHREADS>
+__device__ __forceinline__ void quant_token(const QuantParams& p, int t, int rank, unsigned char* quant_smem,
+                                            float* warp_max, float* peer_max) {
+  constexpr int QUANT_THREADS = NTHREADS;
   uint4* row = reinterpret_cast<uint4*>(quant_smem);          // this CTA's chunks of 8 halfs
-  __shared__ float warp_max[QUANT_THREADS / 32];
-  __shared__ float peer_max[8];
-
-  // Let the next kernel in the stream be scheduled early; then wait until the
-  // producer of X (and every earlier user of the output buffers) has finished.
-  grid_launch_dependents();
-  grid_dependency_wait();
-
   const int C = p.C;
-  const int t = blockIdx.x / C;
-  const int rank = blockIdx.x - t * C;
   const int tid = threadIdx.x;
   const int nchunk_row = p.K >> 3;
   const int c_lo = rank * (nchunk_row / C), c_hi = c_lo + nchunk_row / C;   // slice, a multiple of 16 chunks
@@ -94,6 +90,42 @@ act_quant_kernel(const QuantParams p) {
     const uint4* src = reinterpret_cast<const uint4*>(xrow);
     for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
       uint4 v = ld_plain(src + c);
+      row[c - c_lo] = v;
+      m = half_abs_max8(v, m);
+    }
+  } else if (p.stage_row) {
+    // Column permutation: the whole row is brought into shared memory with coalesced
+    // 128-bit loads (one global round trip, in flight together with the first
+    // permutation indices) and the gather runs on shared memory; a gather from global
+    // memory costs a second, dependent round trip and one L1 wavefront per element.
+    __half* raw = reinterpret_cast<__half*>(row + (c_hi - c_lo));
+    const bool perm_vec = (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
+    int4 pa = make_int4(0, 0, 0, 0), pb = pa;
+    if (c_lo + tid < c_hi && perm_vec) {
+      pa = ld_plain(reinterpret_cast<const int4*>(p.perm) + (c_lo + tid) * 2);
+      pb = ld_plain(reinterpret_cast<const int4*>(p.perm) + (c_lo + tid) * 2 + 1);
+    }
+    if (p.vec_ok) {
+      const uint4* src = reinterpret_cast<const uint4*>(xrow);
+      for (int c = tid; c < nchunk_row; c += QUANT_THREADS) reinterpret_cast<uint4*>(raw)[c] = ld_plain(src + c);
+    } else {
+      for (int k = tid; k < p.K; k += QUANT_THREADS) raw[k] = xrow[k];
+    }
+    __syncthreads();
+    for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
+      if (c != c_lo + tid || !perm_vec) {
+        if (perm_vec) {
+          pa = ld_plain(reinterpret_cast<const int4*>(p.perm) + c * 2);
+          pb = ld_plain(reinterpret_cast<const int4*>(p.perm) + c * 2 + 1);
+        } else {
+          pa = make_int4(p.perm[c * 8], p.perm[c * 8 + 1], p.perm[c * 8 + 2], p.perm[c * 8 + 3]);
+          pb = make_int4(p.perm[c * 8 + 4], p.perm[c * 8 + 5], p.perm[c * 8 + 6], p.perm[c * 8 + 7]);
+        }
+      }
+      __align__(16) __half h[8];
+      h[0] = raw[pa.x]; h[1] = raw[pa.y]; h[2] = raw[pa.z]; h[3] = raw[pa.w];
+      h[4] = raw[pb.x]; h[5] = raw[pb.y]; h[6] = raw[pb.z]; h[7] = raw[pb.w];
+      uint4 v = *reinterpret_cast<uint4*>(h);
       row[c - c_lo] = v;
       m = half_abs_max8(v, m);
     }
@@ -174,6 +206,19 @@ act_quant_kernel(const QuantParams p) {
       if (sumsf) sumsf[(c >> 4) * 16] = (float)sum;
     }
   }
+}
+
+__global__ void __launch_bounds__(QUANT_THREADS)
+act_quant_kernel(const QuantParams p) {
+  extern __shared__ __align__(16) unsigned char quant_dyn_smem[];
+  __shared__ float warp_max[QUANT_THREADS / 32];
+  __shared__ float peer_max[8];
+  // Let the next kernel in the stream be scheduled early; then wait until the
+  // producer of X (and every earlier user of the output buffers) has finished.
+  grid_launch_dependents();
+  grid_dependency_wait();
+  const int t = blockIdx.x / p.C;
+  quant_token<QUANT_THREADS>(p, t, blockIdx.x - t * p.C, quant_dyn_smem, warp_max, peer_max);
 }
 
 // Builds the expanded layout and the transposed float group sums from already

@@ -377,8 +377,11 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   for (int c = 8; c > 1; c >>= 1)
     if (ng % c == 0 && (long long)T * c <= 2LL * sm_count) { C = c; break; }
   q.C = C;
-  const size_t smem = (size_t)K * 2 / C;
+  size_t smem = (size_t)K * 2 / C;
   if (smem > 200 * 1024) return fail(W4A4_ERR_UNSUPPORTED, "K=%d exceeds the quantisation kernel's row buffer", K);
+  // with a column permutation and one CTA per token the raw row is staged behind the slice when it fits
+  q.stage_row = (perm != nullptr && C == 1 && smem + (size_t)K * 2 <= 200 * 1024) ? 1 : 0;
+  if (q.stage_row) smem += (size_t)K * 2;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(quant): %s", cudaGetErrorString(e));

@@ -192,6 +192,101 @@ def run_reference(args, items):
     }
 
 
+# ----------------------------------------------------------------------------- sharded 70B linears
+LLAMA2_70B = [("qkv", 8192, 10240), ("o", 8192, 8192), ("gate_up", 8192, 57344), ("down", 28672, 8192)]
+
+
+def run_sharded(args, rank, world, device):
+    """Llama-2-70B linears split column-parallel over the ranks (block-row
+    granularity, activations replicated, every rank quantises itself), at M = 1
+    (graph-replayed, weights rotated past L2) and M = 4096, each with and without
+    the all-gather of the fp16 output shards.  Total work is fixed: strong scaling."""
+    import torch.distributed as dist
+    from zip_kernel_b200 import ops, sharding, synth
+
+    def ev_time(fn, reps, warm):
+        for _ in range(warm):
+            fn()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / reps
+        if world > 1:
+            t = torch.tensor([ms], device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms * 1e3     # us
+
+    shards, nnz_per_rank = {}, {}
+    for name, K, N in LLAMA2_70B:
+        W = synth.make_container(N, K, DENSITY, seed=synth.shape_seed(0, K, N))
+        sh = sharding.shard_container(W, rank, world) if world > 1 else W
+        sharding.check_shard_metadata(N, K, sh, rank, world) if world > 1 else None
+        shard_bytes = sh.W_low_packed.numel()
+        n_sets = max(2, -(-2 * L2_BYTES // max(4 * shard_bytes, 1)) + 1)     # the four linears rotate together
+        shards[name] = [sh.to(device) for _ in range(min(n_sets, 8))]
+        nnz_per_rank[name] = sh.n_hp_blocks
+        del W
+    res = {"per_linear_us": {}, "allgather_us": {}}
+    ops_total = {}
+    for M in (1, 4096):
+        Xs = {name: synth.make_activations(M, K, seed=synth.shape_seed(M, K, N) + 1).to(device) for name, K, N in LLAMA2_70B}
+        for name, K, N in LLAMA2_70B:
+            ops.reserve_workspace(device, M, K, shards[name][0].d_out, shards[name][0].n_hp_blocks)
+
+        def linear(name, r):
+            W = shards[name][r % len(shards[name])]
+            return ops.fused_dense_sparse_e2e_cuda(Xs[name], W.perm, W.W_low_packed, W.W_high_blocks_packed,
+                                                   W.hp_row_offsets, W.hp_col_indices, W.scale_u4, W.zero_u4,
+                                                   W.d_out, W.d_in)            # (d_out_r, M): contiguous rows of the full output
+        ops_total[M] = sum(2 * M * K * N for _, K, N in LLAMA2_70B)
+        per = {}
+        for name, K, N in LLAMA2_70B:
+            n_sets = len(shards[name])
+            if M == 1:
+                side = torch.cuda.Stream()
+                with torch.cuda.stream(side):
+                    ops.reserve_workspace(device, M, K, shards[name][0].d_out, shards[name][0].n_hp_blocks)
+                    for r in range(n_sets):
+                        linear(name, r)
+                    torch.cuda.synchronize()
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        for r in range(n_sets):
+                            linear(name, r)
+                torch.cuda.synchronize()
+                per[name] = ev_time(g.replay, 30, 3) / n_sets
+            else:
+                cnt = [0]
+                def one():
+                    cnt[0] += 1
+                    linear(name, cnt[0])
+                per[name] = ev_time(one, 10, 3)
+            if world > 1:
+                y = linear(name, 0)
+                full = torch.empty((N, M), dtype=torch.float16, device=device)
+                equal = len(set(sharding.shard_sizes(N, world))) == 1
+                def gather():
+                    if equal:
+                        dist.all_gather_into_tensor(full, y)
+                    else:
+                        sharding.gather_output(y, N, token_major=False)
+                res["allgather_us"][f"{name}_M{M}"] = ev_time(gather, 20, 3)
+            res["per_linear_us"][f"{name}_M{M}"] = per[name]
+        res[f"tops_M{M}"] = ops_total[M] / (sum(per.values()) * 1e-6) / 1e12
+        if world > 1:
+            t_g = sum(per.values()) + sum(res["allgather_us"][f"{n}_M{M}"] for n, _, _ in LLAMA2_70B)
+            res[f"tops_M{M}_with_allgather"] = ops_total[M] / (t_g * 1e-6) / 1e12
+    res["residual_blocks_per_rank"] = nnz_per_rank
+    return res
+
+
 # ----------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
@@ -202,13 +297,14 @@ def main():
     ap.add_argument("--workload", default="decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
-    items = workload_items(args.workload)
+    items = workload_items(args.workload) if args.workload != "cfg3_sharded" else []
     args.workload_desc = {
         "decode": "Llama-3-8B linears (qkv,o,gate_up,down) x M in {1,4,16}, 5% residual blocks",
         "prefill": "Llama-3-8B linears (qkv,o,gate_up,down) x M=2048, 5% residual blocks",
         "cfg0": "single linear 4096->4096, M=16, 5% residual blocks",
         "gate_up_m16": "single linear 4096->28672, M=16, 5% residual blocks",
         "prefill_gate_up": "single linear 4096->28672, M=2048, 5% residual blocks",
+        "cfg3_sharded": "Llama-2-70B linears (qkv,o,gate_up,down), M in {1,4096}, column-parallel shards, 5% residual blocks",
     }[args.workload]
 
     rank = int(os.environ.get("RANK", "0"))
@@ -227,6 +323,17 @@ def main():
     device = torch.device("cuda", local_rank)
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
+    if args.workload == "cfg3_sharded":
+        res = run_sharded(args, rank, world, device)
+        if rank == 0:
+            print(json.dumps({"metric": "w4a4_fused_linear_effective_tops", "value": res["tops_M1"], "unit": "TOPS",
+                              "n_gpus": world, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                              "dtype": "s4xs4->s32", "data": "synthetic",
+                              "config": {"workload": args.workload_desc, "parallelism": f"column-parallel x{world}"},
+                              **res}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     w_bytes = sum(k * n // 2 for _, k, n in {(i[2], i[3]): (0, i[2], i[3]) for i in items}.values())
     n_sets = max(2, -(-2 * L2_BYTES // max(w_bytes, 1)) + 1)

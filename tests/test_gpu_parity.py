@@ -244,3 +244,23 @@ def test_v9_linear_module(ops):
     assert rel < 2e-2
     with pytest.raises(ValueError):
         v9_linear.v9_linear_forward(X3[..., :256], Wc)
+
+
+def test_host_staged_graph_forward(ops):
+    """Pinned host activations in, pinned host result out through one replayed graph:
+    same bits as the eager module forward, also after the input buffer is refilled."""
+    from zip_kernel_b200 import backend, v9_linear
+    W, X = make_case(4, 384, 512, 0.2, perm_seed=6)
+    Wc = cuda_container(W)
+    Xh = X.clone().pin_memory()
+    Yh = torch.empty((4, 384), dtype=torch.float16).pin_memory()
+    for scale in (1.0, -0.5):                     # second pass replays the captured graph on new contents
+        Xh.copy_(X * scale)
+        out = backend.v9_linear_forward_host_graph(Xh, Wc, Yh)
+        torch.cuda.synchronize()
+        assert out is Yh
+        ref = v9_linear.v9_linear_forward(Xh.cuda(), Wc).cpu()
+        assert torch.equal(Yh, ref)
+    with pytest.raises(ValueError):
+        backend.v9_linear_forward_host_graph(X, Wc, Yh)          # not pinned
+    backend.clear_cuda_graph_cache()

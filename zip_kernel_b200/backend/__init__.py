@@ -10,7 +10,7 @@ from .weight_loader import (CutlassPackValidationError, CutlassV9Tensors,
                             pack_v9_weights_for_cutlass)
 from .graph_cache import (clear_cuda_graph_cache, cuda_graph_cache_stats, get_cuda_graph_policy,
                           prewarm_cuda_graph_cache, set_cuda_graph_policy,
-                          v9_linear_forward_cuda_graph)
+                          v9_linear_forward_cuda_graph, v9_linear_forward_host_graph)
 from .policy import get_backend_status, set_backend_policy
 from .registry import BackendKernel
 
@@ -45,6 +45,7 @@ __all__ = [
     "get_backend_status",
     "BackendKernel",
     "v9_linear_forward_cuda_graph",
+    "v9_linear_forward_host_graph",
     "set_cuda_graph_policy",
     "get_cuda_graph_policy",
     "prewarm_cuda_graph_cache",

@@ -244,6 +244,69 @@ def v9_linear_forward_cuda_graph(X_fp16: torch.Tensor, W: V9WeightContainer) -> 
     return _replay(entry, X_fp16)
 
 
+# ---------------------------------------------------------------------------
+# Host-staged forward: pinned host activations in, pinned host result out, one
+# graph launch.  Not in the reference (its callers keep activations on the
+# device); it serves callers whose activations arrive in pinned host memory -
+# the copy in, the quantisation + GEMM and the copy out are captured together,
+# so a call costs one graph launch instead of five launches and their Python.
+# ---------------------------------------------------------------------------
+_host_graphs: "OrderedDict[Tuple[int, int, int, Tuple[int, ...], int], Tuple[Any, torch.Tensor, torch.Tensor]]" = OrderedDict()
+_HOST_GRAPH_CAPACITY = 256
+
+
+def v9_linear_forward_host_graph(X_pinned: torch.Tensor, W: V9WeightContainer, Y_pinned: torch.Tensor,
+                                 device: Optional[torch.device] = None) -> torch.Tensor:
+    """``Y_pinned[...] = v9_linear_forward(X_pinned.to(device), W)`` as one replayed
+    CUDA graph on the current stream of ``device`` (default: the weights' device).
+
+    ``X_pinned (..., d_in)`` fp16 and ``Y_pinned (..., d_out)`` fp16 must be pinned
+    host tensors whose storage stays where it is between calls: the graph bakes
+    their addresses in (refill ``X_pinned`` in place before each call).  The
+    result is complete once the stream has been synchronised.  The first call for
+    a (weights, input buffer, output buffer, shape) combination captures."""
+    if not (X_pinned.is_pinned() and Y_pinned.is_pinned()):
+        raise ValueError("X_pinned and Y_pinned must be pinned host tensors")
+    if X_pinned.dtype != torch.float16 or Y_pinned.dtype != torch.float16:
+        raise ValueError("X_pinned and Y_pinned must be fp16")
+    if tuple(Y_pinned.shape) != tuple(X_pinned.shape[:-1]) + (W.d_out,):
+        raise ValueError(f"Y_pinned must have shape {tuple(X_pinned.shape[:-1]) + (W.d_out,)}")
+    dev = device if device is not None else W.W_low_packed.device
+    key = (id(W), X_pinned.data_ptr(), Y_pinned.data_ptr(), tuple(X_pinned.shape), _device_index(W.W_low_packed))
+    hit = _host_graphs.get(key)
+    if hit is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("v9_linear_forward_host_graph cannot capture inside another capture")
+        from .. import ops
+        T = 1
+        for s_ in X_pinned.shape[:-1]:
+            T *= int(s_)
+        x_static = torch.empty(tuple(X_pinned.shape), dtype=torch.float16, device=dev)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            ops.reserve_workspace(dev, T, W.d_in, W.d_out, W.n_hp_blocks)
+            for _ in range(2):
+                x_static.copy_(X_pinned, non_blocking=True)
+                Y_pinned.copy_(_eager(x_static, W), non_blocking=True)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                x_static.copy_(X_pinned, non_blocking=True)
+                y_static = _eager(x_static, W)
+                Y_pinned.copy_(y_static, non_blocking=True)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        hit = (graph, x_static, y_static)
+        _host_graphs[key] = hit
+        weakref.finalize(W, _host_graphs.pop, key, None)
+        while len(_host_graphs) > _HOST_GRAPH_CAPACITY:
+            _host_graphs.popitem(last=False)
+    else:
+        _host_graphs.move_to_end(key)
+    hit[0].replay()
+    return Y_pinned
+
+
 def set_cuda_graph_policy(policy: str) -> str:
     """``'off'`` (eager), ``'auto'`` (power-of-two T up to 128) or ``'force'`` (every
     T up to 128).  Returns the previous policy."""
@@ -283,6 +346,7 @@ def cuda_graph_cache_stats() -> Dict[str, Any]:
 
 
 def clear_cuda_graph_cache() -> None:
+    _host_graphs.clear()
     _cache.clear()
 
 

@@ -48,13 +48,24 @@ constexpr int ROWS = 128;
 constexpr int CONSUMER_WARPS = 8;
 constexpr int CONSUMER_THREADS = CONSUMER_WARPS * 32;
 constexpr int THREADS = CONSUMER_THREADS + 32;
-constexpr int STAGES = 4;
-constexpr int TOK = 16;                           // tokens per CTA pass
 constexpr int W_TILE_BYTES = ROWS * 2 * GROUP_BYTES;   // 16384: 128 rows x two groups
 constexpr int BLK_BYTES = BROW * GROUP_BYTES;     // 8192: one residual block
-constexpr int X_TILE_BYTES = TOK * BCOL;          // 2048 (16 tokens x 128 codes) per group
-constexpr int SUMX_BYTES = TOK * 4;               // 64 per group
-constexpr int STAGE_BYTES = W_TILE_BYTES + 2 * X_TILE_BYTES;   // group sums live in a ring of their own
+constexpr int MAX_STAGES = 4;
+// Tile geometry of an instantiation: NT = 8-token MMA tiles per CTA pass.  Up to
+// 16 tokens a pass covers 16 tokens and the ring is 4 deep; NT = 4 covers 32
+// tokens per pass (weights are streamed once for up to 32 tokens) with a 3-deep
+// ring so that two CTAs still share an SM.
+template <int NT>
+struct Tile {
+  static constexpr int TOK = NT > 2 ? 32 : 16;            // tokens per CTA pass
+  static constexpr int STAGES = NT > 2 ? 3 : 4;
+  static constexpr int NTH = NT > 2 ? 2 : NT;             // MMA tiles handled together (register budget)
+  static constexpr int HALVES = NT / NTH;
+  static constexpr int X_TILE_BYTES = TOK * BCOL;         // per group
+  static constexpr int SUMX_BYTES = TOK * 4;              // per group: one 64-byte piece per 16 tokens
+  static constexpr int STAGE_BYTES = W_TILE_BYTES + 2 * X_TILE_BYTES;   // group sums live in a ring of their own
+  static constexpr size_t SMEM = 1024 + (size_t)STAGES * STAGE_BYTES + STAGES * 2 * SUMX_BYTES + 16 * ROWS * 8 + 256;
+};
 constexpr int MAX_CLUSTER = 8;                    // portable cluster size limit
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero staged per span
 constexpr int SZ_BYTES = SZ_CHUNK * ROWS * 8;     // float2 (scale/16, scale*zero) per (group, row)
@@ -84,7 +95,8 @@ struct Params {
   float sparse_weight;      // 16 (fused) or 1 (sparse-only op)
 };
 
-inline size_t smem_bytes() { return 1024 + (size_t)STAGES * STAGE_BYTES + STAGES * 2 * SUMX_BYTES + SZ_BYTES + 256; }
+inline size_t smem_bytes(int nt) { return nt > 2 ? Tile<4>::SMEM : Tile<1>::SMEM; }
+inline int tokens_per_pass(int nt) { return nt > 2 ? Tile<4>::TOK : Tile<1>::TOK; }
 
 // ---- thread-block cluster helpers (no multicast; plain distributed-shared-memory loads)
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -123,29 +135,39 @@ __device__ __forceinline__ void mma_m16n8k32_s8_first(int (&d)[4], uint32_t a0, 
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
 }
 
-// One group of one warp: 16 rows x 128 codes against NT*8 tokens.
-template <int NT>
-__device__ __forceinline__ void group_mma(int (&acc)[NT][4], const uint4& wa, const uint4& wb, const uint4 (&q0)[NT],
-                                          const uint4 (&q1)[NT]) {
+// The A fragments of one group of one warp (16 rows x 128 codes): nibbles widened to s8 lanes x 16.
+struct AFrag { uint32_t a[4][4]; };
+__device__ __forceinline__ AFrag unpack_a(const uint4& wa, const uint4& wb) {
   const uint32_t wa_[4] = {wa.x, wa.y, wa.z, wa.w};
   const uint32_t wb_[4] = {wb.x, wb.y, wb.z, wb.w};
+  AFrag f;
 #pragma unroll
   for (int jj = 0; jj < 4; ++jj) {
-    const uint32_t a0 = nib_lo_x16(wa_[jj]), a1 = nib_lo_x16(wb_[jj]);
-    const uint32_t a2 = nib_hi_x16(wa_[jj]), a3 = nib_hi_x16(wb_[jj]);
+    f.a[jj][0] = nib_lo_x16(wa_[jj]);
+    f.a[jj][1] = nib_lo_x16(wb_[jj]);
+    f.a[jj][2] = nib_hi_x16(wa_[jj]);
+    f.a[jj][3] = nib_hi_x16(wb_[jj]);
+  }
+  return f;
+}
+// One group of one warp against NT*8 tokens.
+template <int NT>
+__device__ __forceinline__ void group_mma(int (&acc)[NT][4], const AFrag& f, const uint4 (&q0)[NT], const uint4 (&q1)[NT]) {
+#pragma unroll
+  for (int jj = 0; jj < 4; ++jj) {
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
       const uint32_t b0_[4] = {q0[nt].x, q0[nt].z, q1[nt].x, q1[nt].z};
       const uint32_t b1_[4] = {q0[nt].y, q0[nt].w, q1[nt].y, q1[nt].w};
-      if (jj == 0) mma_m16n8k32_s8_first(acc[nt], a0, a1, a2, a3, b0_[jj], b1_[jj]);
-      else         mma_m16n8k32_s8(acc[nt], a0, a1, a2, a3, b0_[jj], b1_[jj]);
+      if (jj == 0) mma_m16n8k32_s8_first(acc[nt], f.a[jj][0], f.a[jj][1], f.a[jj][2], f.a[jj][3], b0_[jj], b1_[jj]);
+      else         mma_m16n8k32_s8(acc[nt], f.a[jj][0], f.a[jj][1], f.a[jj][2], f.a[jj][3], b0_[jj], b1_[jj]);
     }
   }
 }
 
 // y += acc * f - c * sumx   for the thread's two rows (a: acc[0..1], b: acc[2..3])
 template <int NT>
-__device__ __forceinline__ void group_fold(float2 (&y)[NT][2], const int (&acc)[NT][4], float fa, float fb, float ca,
+__device__ __forceinline__ void group_fold(float2 (*y)[2], const int (&acc)[NT][4], float fa, float fb, float ca,
                                            float cb, const float2 (&sx)[NT]) {
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
@@ -159,14 +181,17 @@ __device__ __forceinline__ void group_fold(float2 (&y)[NT][2], const int (&acc)[
 template <int NT, bool DUMP>
 __global__ void __launch_bounds__(THREADS, 2)
 decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
+  using TL = Tile<NT>;
+  constexpr int TOK = TL::TOK, STAGES = TL::STAGES, NTH = TL::NTH, HALVES = TL::HALVES;
+  constexpr int X_TILE_BYTES = TL::X_TILE_BYTES, SUMX_BYTES = TL::SUMX_BYTES, STAGE_BYTES = TL::STAGE_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* stage_buf = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* sumx_ring = stage_buf + STAGES * STAGE_BYTES;
   float2* szs = reinterpret_cast<float2*>(sumx_ring + STAGES * 2 * SUMX_BYTES);   // [16 groups][128 rows] (s/16, s*z)
   uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(szs) + SZ_BYTES);
-  uint64_t* empty = full + STAGES;
-  int* misc = reinterpret_cast<int*>(empty + STAGES);     // [1] = a wait gave up
+  uint64_t* empty = full + MAX_STAGES;
+  int* misc = reinterpret_cast<int*>(empty + MAX_STAGES);     // [1] = a wait gave up
 
   // the next kernel in the stream may be scheduled as soon as every CTA got here;
   // it waits for this grid's completion before it touches anything we use
@@ -199,7 +224,9 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
     // ------------------------------------------------------------ producer
     if (lane == 0) {
       const bool with_sums = p.sumxf != nullptr;
-      const float* sums_base = with_sums ? p.sumxf + (size_t)tt * p.ng * TOK : nullptr;
+      // the sums table is cut into 16-token tiles; a pass covers TOK / 16 of them (the last pass maybe fewer)
+      const int tiles16 = (p.T + 15) >> 4;
+      const int n_u = with_sums ? min(TOK / 16, tiles16 - tt * (TOK / 16)) : 0;
       bool ok = true;
       // The weight copy of a step does not depend on the preceding kernel in the
       // stream, the activation copies do.  Dense step j covers groups 2j, 2j+1.
@@ -207,16 +234,18 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
       auto x_src = [&](int g) { return p.XE + ((size_t)g * p.t_pad + tok0) * BCOL; };
       auto dense_w = [&](int j, int st) {
         const int n_grp = (2 * j + 1 < p.ng) ? 2 : 1;
-        mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + n_grp * XG_BYTES + (with_sums ? n_grp * SUMX_BYTES : 0));
+        mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + n_grp * XG_BYTES + n_u * n_grp * 64);
         tma_load_2d(stage_buf + st * STAGE_BYTES, &tm_low, 2 * j * GROUP_BYTES, row0, &full[st]);
       };
       auto dense_x = [&](int j, int st) {
         unsigned char* xt = stage_buf + st * STAGE_BYTES + W_TILE_BYTES;
         bulk_load_1d(xt, x_src(2 * j), XG_BYTES, &full[st]);
         if (2 * j + 1 < p.ng) bulk_load_1d(xt + X_TILE_BYTES, x_src(2 * j + 1), XG_BYTES, &full[st]);
-        if (with_sums)
-          bulk_load_1d(sumx_ring + st * 2 * SUMX_BYTES, sums_base + 2 * j * TOK,
-                       ((2 * j + 1 < p.ng) ? 2 : 1) * SUMX_BYTES, &full[st]);
+        // slot layout of the sums: [16-token tile][group of the step][16 tokens]
+        for (int u = 0; u < n_u; ++u)
+          bulk_load_1d(sumx_ring + st * 2 * SUMX_BYTES + u * 128,
+                       p.sumxf + ((size_t)(tt * (TOK / 16) + u) * p.ng + 2 * j) * 16,
+                       ((2 * j + 1 < p.ng) ? 2 : 1) * 64, &full[st]);
       };
       // ring fill: weight tiles first, then wait for the activations' producer kernel
       const int n_dense = d_hi - d_lo;
@@ -267,13 +296,10 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
     // Per-thread constant offsets inside a slot.  An activation tile is a stack of
     // 128-byte lines (one per token) whose 16-byte chunks sit at chunk ^ (token & 7);
     // a dense step holds one tile per group, X_TILE_BYTES apart.
-    int xs0[NT], xs1[NT];
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const int xr = nt * 8 + gid;
-      xs0[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig) ^ (xr & 7)) << 4);
-      xs1[nt] = W_TILE_BYTES + xr * BCOL + (((2 * tig + 1) ^ (xr & 7)) << 4);
-    }
+    // token nt * 8 + gid: (token & 7) == gid for every nt, so MMA tile nt sits 8 lines further on
+    const int xs0 = W_TILE_BYTES + gid * BCOL + (((2 * tig) ^ gid) << 4);
+    const int xs1 = W_TILE_BYTES + gid * BCOL + (((2 * tig + 1) ^ gid) << 4);
+    constexpr int XNT = 8 * BCOL;         // bytes between consecutive MMA tiles of tokens
 
     const uint32_t stage_a = smem_u32(stage_buf), sumx_a = smem_u32(sumx_ring), szs_a = smem_u32(szs);
 
@@ -395,48 +421,47 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           const float2 szb0 = lds_f2(szs_a + ((g & (SZ_CHUNK - 1)) * ROWS + r_b) * 8);
           const float2 sza1 = lds_f2(szs_a + (((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_a) * 8);
           const float2 szb1 = lds_f2(szs_a + (((g + 1) & (SZ_CHUNK - 1)) * ROWS + r_b) * 8);
-          int acc0[NT][4], acc1[NT][4];
-          {
-            uint4 q0[NT], q1[NT];
-            float2 sx[NT];
+          // group gg of the step, MMA tiles of tokens in bunches of NTH: A fragments are widened once per group
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              q0[nt] = lds_v4(slot + xs0[nt]);
-              q1[nt] = lds_v4(slot + xs1[nt]);
-              sx[nt] = p.sumxf ? lds_f2(sums + (nt * 8 + tig * 2) * 4) : make_float2(0.f, 0.f);
+          for (int gg = 0; gg < 2; ++gg) {
+            const AFrag fa = unpack_a(wa[gg], wb[gg]);
+            const float2 sza = gg ? sza1 : sza0, szb = gg ? szb1 : szb0;
+#pragma unroll
+            for (int hh = 0; hh < HALVES; ++hh) {
+              uint4 q0[NTH], q1[NTH];
+              float2 sx[NTH];
+#pragma unroll
+              for (int nt = 0; nt < NTH; ++nt) {
+                const int xo = gg * X_TILE_BYTES + (hh * NTH + nt) * XNT;
+                q0[nt] = lds_v4(slot + xo + xs0);
+                q1[nt] = lds_v4(slot + xo + xs1);
+                // sums slot: [16-token tile][group][16]; tokens of bunch hh lie in tile (hh * NTH * 8) / 16
+                const int t_in = (hh * NTH + nt) * 8 + tig * 2;
+                sx[nt] = (p.sumxf && (gg == 0 || two)) ? lds_f2(sums + (((t_in >> 4) * 2 + gg) * 16 + (t_in & 15)) * 4)
+                                                      : make_float2(0.f, 0.f);
+              }
+              if (gg == 1 && hh == HALVES - 1) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty[st]);      // every shared-memory read of this slot is done
+              }
+              int acc[NTH][4];
+              group_mma<NTH>(acc, fa, q0, q1);
+              group_fold<NTH>(y + hh * NTH, acc, sza.x, szb.x, sza.y, szb.y, sx);
+              if (DUMP && p.acc_dump) {
+#pragma unroll
+                for (int nt = 0; nt < NTH; ++nt)
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    const int rl = (i & 2) ? r_b : r_a;
+                    const int tok = tok0 + (hh * NTH + nt) * 8 + tig * 2 + (i & 1);
+                    if (tok >= p.T || g + gg >= p.ng || row0 + rl >= p.N) continue;
+                    // parity aid, not a hot path: every store is range-checked
+                    const size_t idx = ((size_t)(g + gg) * p.N + row0 + rl) * p.T + tok;
+                    if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = acc[nt][i] >> 4;
+                    else record_error(SITE_DEC_DUMP, 1);
+                  }
+              }
             }
-            group_mma<NT>(acc0, wa[0], wb[0], q0, q1);
-            group_fold<NT>(y, acc0, sza0.x, szb0.x, sza0.y, szb0.y, sx);
-          }
-          {
-            uint4 q0[NT], q1[NT];
-            float2 sx[NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; ++nt) {
-              q0[nt] = lds_v4(slot + X_TILE_BYTES + xs0[nt]);
-              q1[nt] = lds_v4(slot + X_TILE_BYTES + xs1[nt]);
-              sx[nt] = (p.sumxf && two) ? lds_f2(sums + (TOK + nt * 8 + tig * 2) * 4) : make_float2(0.f, 0.f);
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty[st]);      // every shared-memory read of this slot is done
-            group_mma<NT>(acc1, wa[1], wb[1], q0, q1);
-            group_fold<NT>(y, acc1, sza1.x, szb1.x, sza1.y, szb1.y, sx);
-          }
-          if (DUMP && p.acc_dump) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-              for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const int rl = (i & 2) ? r_b : r_a;
-                  const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
-                  if (tok >= p.T || g + h >= p.ng || row0 + rl >= p.N) continue;
-                  // parity aid, not a hot path: every store is range-checked
-                  const size_t idx = ((size_t)(g + h) * p.N + row0 + rl) * p.T + tok;
-                  if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = (h ? acc1[nt][i] : acc0[nt][i]) >> 4;
-                  else record_error(SITE_DEC_DUMP, 1);
-                }
           }
         }
       } else {
@@ -454,32 +479,38 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           const uint32_t slot = stage_a + st * STAGE_BYTES;
           const uint4 wa = lds_v4(slot + r_a * GROUP_BYTES + tig * 16);
           const uint4 wb = lds_v4(slot + r_b * GROUP_BYTES + tig * 16);
-          uint4 q0[NT], q1[NT];
-          float2 sx[NT];
-#pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            q0[nt] = lds_v4(slot + xs0[nt]);
-            q1[nt] = lds_v4(slot + xs1[nt]);
-            sx[nt] = make_float2(0.f, 0.f);
-          }
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&empty[st]);
-          int acc[NT][4];
-          group_mma<NT>(acc, wa, wb, q0, q1);
+          const AFrag fa = unpack_a(wa, wb);
           const float w = 0.0625f * p.sparse_weight;
-          group_fold<NT>(y, acc, s_a * w, s_b * w, 0.f, 0.f, sx);
-          if (DUMP && p.acc_hi_dump) {
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt)
+          for (int hh = 0; hh < HALVES; ++hh) {
+            uint4 q0[NTH], q1[NTH];
+            float2 sx[NTH];
 #pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const int rl = (i & 2) ? r_b : r_a;
-                const int tok = tok0 + nt * 8 + tig * 2 + (i & 1);
-                if (tok >= p.T) continue;
-                const size_t idx = ((size_t)blk * BROW + rl) * p.T + tok;
-                if (blk >= 0 && blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = acc[nt][i] >> 4;
-                else record_error(SITE_DEC_DUMP, 2);
-              }
+            for (int nt = 0; nt < NTH; ++nt) {
+              q0[nt] = lds_v4(slot + (hh * NTH + nt) * XNT + xs0);
+              q1[nt] = lds_v4(slot + (hh * NTH + nt) * XNT + xs1);
+              sx[nt] = make_float2(0.f, 0.f);
+            }
+            if (hh == HALVES - 1) {
+              __syncwarp();
+              if (lane == 0) mbar_arrive(&empty[st]);
+            }
+            int acc[NTH][4];
+            group_mma<NTH>(acc, fa, q0, q1);
+            group_fold<NTH>(y + hh * NTH, acc, s_a * w, s_b * w, 0.f, 0.f, sx);
+            if (DUMP && p.acc_hi_dump) {
+#pragma unroll
+              for (int nt = 0; nt < NTH; ++nt)
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const int rl = (i & 2) ? r_b : r_a;
+                  const int tok = tok0 + (hh * NTH + nt) * 8 + tig * 2 + (i & 1);
+                  if (tok >= p.T) continue;
+                  const size_t idx = ((size_t)blk * BROW + rl) * p.T + tok;
+                  if (blk >= 0 && blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = acc[nt][i] >> 4;
+                  else record_error(SITE_DEC_DUMP, 2);
+                }
+            }
           }
         }
       }

@@ -117,11 +117,11 @@ WsLayout ws_layout(int T, int K) {
 struct DecodePlan {
   int row_tiles, tok_tiles, split;   // split = CTAs (cluster size) per block-row
 };
-DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count) {
+DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_per_pass) {
   using namespace w4a4;
   DecodePlan p;
   p.row_tiles = (N + dec::ROWS - 1) / dec::ROWS;
-  p.tok_tiles = (T + dec::TOK - 1) / dec::TOK;
+  p.tok_tiles = (T + tokens_per_pass - 1) / tokens_per_pass;
   // Largest power-of-two cluster that keeps the grid within the two CTAs per SM that
   // fit at once (a grid that needs a second wave costs far more than it gains;
   // measured on the Llama-3-8B decode shapes with dependent launches enabled).
@@ -220,7 +220,16 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   const int ng = a.K / BCOL;
   const int row_tiles = (a.N + dec::ROWS - 1) / dec::ROWS;
   const int dense_steps = a.do_dense ? (ng + 1) / 2 : 0;      // two groups per dense step
-  DecodePlan plan = plan_decode(a.T, a.N, dense_steps > 0 ? dense_steps : 1, dev->sm_count);
+  // MMA tiles of 8 tokens per CTA pass: 1 or 2 up to 16 tokens.  Beyond, passes of 16 tokens re-read the
+  // weights from L2, which is cheap; one pass of 32 tokens (4 tiles) halves the number of steps but each
+  // step is bound by instruction issue, so it only pays for 17..32 tokens on the large shapes (measured:
+  // gate_up 36.2 -> 31.6 us, down 20.3 -> 18.6 us at 32 tokens; qkv and 48 tokens lose).
+  static const int env_nt = getenv("W4A4_DECODE_NT") ? atoi(getenv("W4A4_DECODE_NT")) : 0;
+  int nt = a.T > 8 ? 2 : 1;
+  if (a.T > 16 && a.T <= 32 && (a.K >= 8192 || row_tiles >= dev->sm_count)) nt = 4;
+  if (env_nt == 1 || env_nt == 2 || env_nt == 4) nt = env_nt;
+  if (nt == 1 && a.T > 8) nt = 2;
+  DecodePlan plan = plan_decode(a.T, a.N, dense_steps > 0 ? dense_steps : 1, dev->sm_count, dec::tokens_per_pass(nt));
   if ((long long)plan.row_tiles * plan.split > 2147483647LL)
     return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d is too large", a.N);
   // expanded activations: given by the caller, or built here from the packed codes
@@ -238,7 +247,6 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   }
   if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
 
-  const bool nt2 = a.T > 8;
   CUtensorMap tm_low;
   // dense weights: 128 rows x two groups (128 bytes) per copy; unused (but valid) when the dense part is off
   int rc = make_map(&tm_low, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
@@ -274,10 +282,10 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   p.split = plan.split;
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
 
-  const size_t smem = dec::smem_bytes();
+  const size_t smem = dec::smem_bytes(nt);
   void (*kern)(const CUtensorMap, const dec::Params) =
-      dump ? (nt2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
-           : (nt2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
+      dump ? (nt == 4 ? dec::decode_gemm_kernel<4, true> : nt == 2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
+           : (nt == 4 ? dec::decode_gemm_kernel<4, false> : nt == 2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(decode): %s", cudaGetErrorString(e));
 

@@ -74,7 +74,11 @@ __device__ __forceinline__ float half_abs_max8(const uint4& v, float m) {
 // thread of the CTA calls it; for p.C > 1 the CTAs of a cluster call it together
 // with rank = their cluster rank.  `quant_smem` (16-byte aligned) holds the slice
 // (2 * K / C bytes) and, when p.stage_row is set, the raw row behind it.
-template <int NTHREADS>
+// With WAIT_DEP the function itself waits for the preceding kernel in the stream
+// (programmatic dependent launch) - after it has fetched the thread's first
+// permutation indices, which belong to the weights and do not depend on that
+// kernel: the dependent part of the load phase is then one global round trip.
+template <int NTHREADS, bool WAIT_DEP>
 __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int rank, unsigned char* quant_smem,
                                             float* warp_max, float* peer_max) {
   constexpr int QUANT_THREADS = NTHREADS;
@@ -84,6 +88,21 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
   const int nchunk_row = p.K >> 3;
   const int c_lo = rank * (nchunk_row / C), c_hi = c_lo + nchunk_row / C;   // slice, a multiple of 16 chunks
   const __half* xrow = p.X + (long long)t * p.ldx;
+
+  // source columns of chunk c (8 consecutive permuted positions)
+  const bool perm_vec = (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
+  auto load_perm = [&](int c, int4& pa, int4& pb) {
+    if (perm_vec) {
+      pa = ld_plain(reinterpret_cast<const int4*>(p.perm) + c * 2);
+      pb = ld_plain(reinterpret_cast<const int4*>(p.perm) + c * 2 + 1);
+    } else {
+      pa = make_int4(p.perm[c * 8], p.perm[c * 8 + 1], p.perm[c * 8 + 2], p.perm[c * 8 + 3]);
+      pb = make_int4(p.perm[c * 8 + 4], p.perm[c * 8 + 5], p.perm[c * 8 + 6], p.perm[c * 8 + 7]);
+    }
+  };
+  int4 pa = make_int4(0, 0, 0, 0), pb = pa;
+  if (p.perm != nullptr && c_lo + tid < c_hi) load_perm(c_lo + tid, pa, pb);
+  if (WAIT_DEP) grid_dependency_wait();
 
   float m = 0.f;
   if (p.perm == nullptr && p.vec_ok) {
@@ -99,12 +118,6 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
     // permutation indices) and the gather runs on shared memory; a gather from global
     // memory costs a second, dependent round trip and one L1 wavefront per element.
     __half* raw = reinterpret_cast<__half*>(row + (c_hi - c_lo));
-    const bool perm_vec = (reinterpret_cast<uintptr_t>(p.perm) & 15) == 0;
-    int4 pa = make_int4(0, 0, 0, 0), pb = pa;
-    if (c_lo + tid < c_hi && perm_vec) {
-      pa = ld_plain(reinterpret_cast<const int4*>(p.perm) + (c_lo + tid) * 2);
-      pb = ld_plain(reinterpret_cast<const int4*>(p.perm) + (c_lo + tid) * 2 + 1);
-    }
     if (p.vec_ok) {
       const uint4* src = reinterpret_cast<const uint4*>(xrow);
       for (int c = tid; c < nchunk_row; c += QUANT_THREADS) reinterpret_cast<uint4*>(raw)[c] = ld_plain(src + c);
@@ -113,15 +126,7 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
     }
     __syncthreads();
     for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
-      if (c != c_lo + tid || !perm_vec) {
-        if (perm_vec) {
-          pa = ld_plain(reinterpret_cast<const int4*>(p.perm) + c * 2);
-          pb = ld_plain(reinterpret_cast<const int4*>(p.perm) + c * 2 + 1);
-        } else {
-          pa = make_int4(p.perm[c * 8], p.perm[c * 8 + 1], p.perm[c * 8 + 2], p.perm[c * 8 + 3]);
-          pb = make_int4(p.perm[c * 8 + 4], p.perm[c * 8 + 5], p.perm[c * 8 + 6], p.perm[c * 8 + 7]);
-        }
-      }
+      if (c != c_lo + tid) load_perm(c, pa, pb);
       __align__(16) __half h[8];
       h[0] = raw[pa.x]; h[1] = raw[pa.y]; h[2] = raw[pa.z]; h[3] = raw[pa.w];
       h[4] = raw[pb.x]; h[5] = raw[pb.y]; h[6] = raw[pb.z]; h[7] = raw[pb.w];
@@ -132,12 +137,13 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
   } else {
     for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
       __align__(16) __half h[8];
+      if (p.perm) {
+        if (c != c_lo + tid) load_perm(c, pa, pb);
+        h[0] = xrow[pa.x]; h[1] = xrow[pa.y]; h[2] = xrow[pa.z]; h[3] = xrow[pa.w];
+        h[4] = xrow[pb.x]; h[5] = xrow[pb.y]; h[6] = xrow[pb.z]; h[7] = xrow[pb.w];
+      } else {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int k = c * 8 + j;
-        int src = k;
-        if (p.perm) src = p.perm[k];
-        h[j] = xrow[src];
+        for (int j = 0; j < 8; ++j) h[j] = xrow[c * 8 + j];
       }
       uint4 v = *reinterpret_cast<uint4*>(h);
       row[c - c_lo] = v;
@@ -215,10 +221,10 @@ act_quant_kernel(const QuantParams p) {
   __shared__ float peer_max[8];
   // Let the next kernel in the stream be scheduled early; then wait until the
   // producer of X (and every earlier user of the output buffers) has finished.
+  // (the wait for the producer of X and for every earlier user of the output buffers happens inside)
   grid_launch_dependents();
-  grid_dependency_wait();
   const int t = blockIdx.x / p.C;
-  quant_token<QUANT_THREADS>(p, t, blockIdx.x - t * p.C, quant_dyn_smem, warp_max, peer_max);
+  quant_token<QUANT_THREADS, true>(p, t, blockIdx.x - t * p.C, quant_dyn_smem, warp_max, peer_max);
 }
 
 // Builds the expanded layout and the transposed float group sums from already

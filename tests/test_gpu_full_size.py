@@ -126,3 +126,25 @@ def test_full_size_accumulators_on_row_slice(ops):
     b0 = int(W.hp_row_offsets[7])
     ref_hi = O.block_accumulators(Wn["W_high_blocks_packed"], Wn["hp_col_indices"], xs4)
     assert np.array_equal(np_(acc_hi)[b0:b0 + ref_hi.shape[0]], ref_hi)
+
+
+@pytest.mark.parametrize("T", [17, 20, 32])
+def test_32_token_pass_of_the_streaming_kernel(ops, T):
+    """17..32 tokens on a long-K shape take one 32-token pass per CTA (four MMA tiles):
+    outputs against the oracle, accumulators bit for bit."""
+    K, N = 8192, 384
+    W, X = make_case(T, N, K, 0.1, perm_seed=4)
+    Wd = W.to(torch.device("cuda"))
+    Wn = container_np(W)
+    q = ops.activation_quant_cuda(X.cuda(), Wd.perm)
+    xs4, sx, sumx = (np_(t) for t in q)
+    Y = fused(ops, Wd, q, force="stream")
+    assert_close_fp16(np_(Y), oracle_fused(Wn, xs4, sumx, sx), f"T={T} one 32-token pass")
+    acc, acc_hi = ops.dump_accumulators(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
+                                        Wd.hp_col_indices, q[0], N, K, force="stream")
+    assert np.array_equal(np_(acc), O.group_accumulators(Wn["W_low_packed"], xs4))
+    assert np.array_equal(np_(acc_hi), O.block_accumulators(Wn["W_high_blocks_packed"], Wn["hp_col_indices"], xs4))
+    # the split over a cluster and the 32-token pass together: a shape with few block-rows
+    Ye = ops.fused_dense_sparse_e2e_cuda(X.cuda(), Wd.perm, Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
+                                         Wd.hp_col_indices, Wd.scale_u4, Wd.zero_u4, N, K)
+    assert torch.equal(Ye, Y)

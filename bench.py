@@ -358,22 +358,14 @@ def main():
                                                  W.hp_col_indices, it["XE"], it["sumxf"], W.scale_u4,
                                                  W.zero_u4, q[1], W.d_out, W.d_in, token_major=True)
 
-    e2e_streams = [torch.cuda.Stream() for _ in range(3)]
-
     def e2e_step(r):
-        # public host-staged call: pinned activations in, pinned result out (copy in, quantisation +
-        # GEMM and copy out are one replayed graph per linear).  The twelve linears are independent
-        # requests with buffers of their own, so they are issued round-robin on three streams and one
-        # linear's copies overlap another's kernels; the step ends when every result is on the host.
-        cur = torch.cuda.current_stream()
-        for s_ in e2e_streams:
-            s_.wait_stream(cur)
-        for i, it in enumerate(data):
-            with torch.cuda.stream(e2e_streams[i % len(e2e_streams)]):
-                backend.v9_linear_forward_host_graph(it["X_host"], it["W"][r], it["Y_host"])
-        for s_ in e2e_streams:
-            cur.wait_stream(s_)
-        cur.synchronize()
+        # public host-staged call: pinned activations in, pinned results out.  The twelve linears of a
+        # step are independent requests with buffers of their own; the batch call captures copy in,
+        # quantisation + GEMM and copy out of all of them as one graph (three parallel branches, so one
+        # linear's copies overlap another's kernels) and replays it.  The step ends when every result is
+        # on the host.
+        backend.v9_linear_forward_host_graph_many([(it["X_host"], it["W"][r], it["Y_host"]) for it in data])
+        torch.cuda.current_stream().synchronize()
 
     # eager warm-up (also sizes every workspace before capture)
     for it in data:

@@ -264,3 +264,23 @@ def test_host_staged_graph_forward(ops):
     with pytest.raises(ValueError):
         backend.v9_linear_forward_host_graph(X, Wc, Yh)          # not pinned
     backend.clear_cuda_graph_cache()
+
+
+def test_host_staged_batch_graph(ops):
+    """Several host-staged linears as one graph: every result equals the eager forward."""
+    from zip_kernel_b200 import backend, v9_linear
+    reqs, refs = [], []
+    for i, (T, N, K) in enumerate([(1, 256, 512), (4, 384, 256), (16, 128, 1024), (2, 256, 256)]):
+        W, X = make_case(T, N, K, 0.2, perm_seed=i)
+        Wc = cuda_container(W)
+        Xh = X.clone().pin_memory()
+        Yh = torch.zeros((T, N), dtype=torch.float16).pin_memory()
+        reqs.append((Xh, Wc, Yh))
+    for rep in range(2):                                  # capture, then replay on refilled inputs
+        for Xh, _, _ in reqs:
+            Xh.mul_(-0.5 if rep else 1.0)
+        backend.v9_linear_forward_host_graph_many(reqs, n_streams=3)
+        torch.cuda.synchronize()
+        for Xh, Wc, Yh in reqs:
+            assert torch.equal(Yh, v9_linear.v9_linear_forward(Xh.cuda(), Wc).cpu())
+    backend.clear_cuda_graph_cache()

@@ -10,7 +10,8 @@ from .weight_loader import (CutlassPackValidationError, CutlassV9Tensors,
                             pack_v9_weights_for_cutlass)
 from .graph_cache import (clear_cuda_graph_cache, cuda_graph_cache_stats, get_cuda_graph_policy,
                           prewarm_cuda_graph_cache, set_cuda_graph_policy,
-                          v9_linear_forward_cuda_graph, v9_linear_forward_host_graph)
+                          v9_linear_forward_cuda_graph, v9_linear_forward_host_graph,
+                          v9_linear_forward_host_graph_many)
 from .policy import get_backend_status, set_backend_policy
 from .registry import BackendKernel
 
@@ -46,6 +47,7 @@ __all__ = [
     "BackendKernel",
     "v9_linear_forward_cuda_graph",
     "v9_linear_forward_host_graph",
+    "v9_linear_forward_host_graph_many",
     "set_cuda_graph_policy",
     "get_cuda_graph_policy",
     "prewarm_cuda_graph_cache",

@@ -307,6 +307,76 @@ def v9_linear_forward_host_graph(X_pinned: torch.Tensor, W: V9WeightContainer, Y
     return Y_pinned
 
 
+_host_batch_graphs: "OrderedDict[Tuple, Tuple[Any, list]]" = OrderedDict()
+_HOST_BATCH_CAPACITY = 32
+
+
+def v9_linear_forward_host_graph_many(requests, n_streams: int = 3,
+                                      device: Optional[torch.device] = None) -> None:
+    """Several independent host-staged linears as ONE replayed CUDA graph.
+
+    ``requests``: sequence of ``(X_pinned, W, Y_pinned)`` with the conventions of
+    ``v9_linear_forward_host_graph``; every request needs buffers of its own.  Inside
+    the graph the requests are dealt round-robin onto ``n_streams`` parallel branches,
+    so one request's copies overlap another's kernels, and the whole batch costs one
+    graph launch on the host.  Results are complete once the current stream has been
+    synchronised.  The first call for a given batch captures."""
+    reqs = list(requests)
+    if not reqs:
+        return
+    for X, W, Y in reqs:
+        if not (X.is_pinned() and Y.is_pinned()):
+            raise ValueError("X_pinned and Y_pinned must be pinned host tensors")
+        if X.dtype != torch.float16 or Y.dtype != torch.float16:
+            raise ValueError("X_pinned and Y_pinned must be fp16")
+        if tuple(Y.shape) != tuple(X.shape[:-1]) + (W.d_out,):
+            raise ValueError(f"Y_pinned must have shape {tuple(X.shape[:-1]) + (W.d_out,)}")
+    dev = device if device is not None else reqs[0][1].W_low_packed.device
+    key = (int(n_streams),) + tuple((id(W), X.data_ptr(), Y.data_ptr(), tuple(X.shape)) for X, W, Y in reqs)
+    hit = _host_batch_graphs.get(key)
+    if hit is None:
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("v9_linear_forward_host_graph_many cannot capture inside another capture")
+        from .. import ops
+        statics = [torch.empty(tuple(X.shape), dtype=torch.float16, device=dev) for X, _, _ in reqs]
+        main = torch.cuda.Stream(device=dev)
+        branches = [torch.cuda.Stream(device=dev) for _ in range(max(1, min(int(n_streams), len(reqs))))]
+        keep = []
+
+        def issue():
+            for b in branches:
+                b.wait_stream(main)
+            for i, (X, W, Y) in enumerate(reqs):
+                with torch.cuda.stream(branches[i % len(branches)]):
+                    statics[i].copy_(X, non_blocking=True)
+                    y = _eager(statics[i], W)
+                    Y.copy_(y, non_blocking=True)
+                    keep.append(y)
+            for b in branches:
+                main.wait_stream(b)
+
+        main.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(main):
+            for i, (X, W, _) in enumerate(reqs):          # the scratch is per stream: size it on every branch first
+                T = X.numel() // X.shape[-1]
+                with torch.cuda.stream(branches[i % len(branches)]):
+                    ops.reserve_workspace(dev, T, W.d_in, W.d_out, W.n_hp_blocks)
+            issue()
+            main.synchronize()
+            keep.clear()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=main):
+                issue()
+        torch.cuda.current_stream(dev).wait_stream(main)
+        hit = (graph, [statics, keep, branches])
+        _host_batch_graphs[key] = hit
+        while len(_host_batch_graphs) > _HOST_BATCH_CAPACITY:
+            _host_batch_graphs.popitem(last=False)
+    else:
+        _host_batch_graphs.move_to_end(key)
+    hit[0].replay()
+
+
 def set_cuda_graph_policy(policy: str) -> str:
     """``'off'`` (eager), ``'auto'`` (power-of-two T up to 128) or ``'force'`` (every
     T up to 128).  Returns the previous policy."""
@@ -347,6 +417,7 @@ def cuda_graph_cache_stats() -> Dict[str, Any]:
 
 def clear_cuda_graph_cache() -> None:
     _host_graphs.clear()
+    _host_batch_graphs.clear()
     _cache.clear()
 
 

@@ -24,8 +24,8 @@
 //     instead of 96 KB, and shared-memory bandwidth is what a 128 x 128 tile
 //     runs out of first;
 //   * one thread issues four tcgen05.mma kind::i8 (K = 32 each, A from TMEM, B
-//     from shared memory) into a fresh int32 accumulator in TMEM (two accumulator
-//     buffers alternate) and commits ONCE to a ring of "step done" mbarriers:
+//     from shared memory) into a fresh int32 accumulator in TMEM (three accumulator
+//     buffers rotate) and commits ONCE to a ring of "step done" mbarriers:
 //     the fold warps (accumulator ready), the unpack warps (A buffer free again)
 //     and the producer (activation slot free again) all wait on that ring;
 //   * eight fold warps read the accumulator with tcgen05.ld and fold it in fp32:
@@ -52,8 +52,13 @@ constexpr int WP_BYTES = ROWS * GROUP_BYTES;      // 8192
 constexpr int X_BYTES = TN * BCOL;                // 16384
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
 constexpr int A_COLS = BCOL / 4;                  // 32 TMEM columns hold one widened row of 128 s8
-constexpr int A_COL0 = 2 * TN;                    // after the two int32 accumulator buffers
-constexpr int TMEM_COLS = 512;                    // power of two >= 2 * TN + A_BUFS * A_COLS
+#ifndef W4A4_ACC_BUFS
+#define W4A4_ACC_BUFS 3
+#endif
+constexpr int ACC_BUFS = W4A4_ACC_BUFS;           // int32 accumulator buffers: the MMAs run this many steps ahead of the fold
+constexpr int A_COL0 = ACC_BUFS * TN;             // after the accumulator buffers
+constexpr int TMEM_COLS = 512;                    // power of two >= ACC_BUFS * TN + A_BUFS * A_COLS
+static_assert(ACC_BUFS * TN + A_BUFS * A_COLS <= TMEM_COLS, "tensor memory budget");
 
 #ifndef W4A4_FOLD_WARPS
 #define W4A4_FOLD_WARPS 8
@@ -198,8 +203,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   uint64_t* a_full = w_empty + W_STAGES;        // [A_BUFS]   widened tile stored to tensor memory
   uint64_t* x_full = a_full + A_BUFS;           // [X_STAGES]
   uint64_t* done = x_full + X_STAGES;           // [X_STAGES] the MMAs of step n (slot n % X_STAGES) have completed
-  uint64_t* acc_empty = done + X_STAGES;        // [2]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint64_t* acc_empty = done + X_STAGES;        // [ACC_BUFS]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
 
   grid_launch_dependents();
   const int tid = threadIdx.x;
@@ -213,7 +218,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
     for (int i = 0; i < A_BUFS; ++i) mbar_init(&a_full[i], N_UNPACK_WARPS);
     for (int i = 0; i < X_STAGES; ++i) { mbar_init(&x_full[i], 1); mbar_init(&done[i], 1); }
-    for (int i = 0; i < 2; ++i) mbar_init(&acc_empty[i], N_FOLD_WARPS);
+    for (int i = 0; i < ACC_BUFS; ++i) mbar_init(&acc_empty[i], N_FOLD_WARPS);
     mbar_fence_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_wh);
@@ -271,15 +276,15 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       int xs = 0;
       uint32_t xph = 0;
       for (int n = 0; n < n_steps && ok; ++n) {
-        const int buf = n & 1;          // accumulator buffer and A buffer alternate together
-        ok = mbar_wait_relaxed(&acc_empty[buf], ((n >> 1) & 1) ^ 1, SITE_PRE_ACCEMPTY);
-        if (ok) ok = mbar_wait_relaxed(&a_full[buf], (n >> 1) & 1, SITE_PRE_AFULL);
+        const int buf = n % ACC_BUFS, ab = n % A_BUFS;
+        ok = mbar_wait_relaxed(&acc_empty[buf], ((n / ACC_BUFS) & 1) ^ 1, SITE_PRE_ACCEMPTY);
+        if (ok) ok = mbar_wait_relaxed(&a_full[ab], (n / A_BUFS) & 1, SITE_PRE_AFULL);
         if (ok) ok = mbar_wait_relaxed(&x_full[xs], xph, SITE_PRE_XFULL);
         if (!ok) break;
         tc_fence_after();
         const uint64_t bdesc = smem_desc_sw128(x_ring + xs * X_BYTES);
         const uint32_t d = tmem_base + buf * TN;
-        const uint32_t a = tmem_base + A_COL0 + buf * A_COLS;
+        const uint32_t a = tmem_base + A_COL0 + ab * A_COLS;
 #pragma unroll
         for (int j = 0; j < 4; ++j) umma_i8_ta(d, a + j * 8, bdesc + j * 2, j > 0);   // K = 32: 8 columns of A, 32 bytes of B
         umma_commit(&done[xs]);
@@ -296,7 +301,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     int ws = 0;
     uint32_t wph = 0;
     for (int n = 0; n < n_steps; ++n) {
-      const int buf = n & 1;
+      const int buf = n % A_BUFS;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&w_full[ws], wph, SITE_PRE_WFULL));
       // the A buffer was last read by the MMAs of step n - 2
       if (ok && n >= A_BUFS)
@@ -424,7 +429,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           f = __half2float(ld_plain(p.scale_u4 + (size_t)row * p.ng + ld_plain(p.hp_col_indices + blk))) * 0.0625f *
               p.sparse_weight;
       }
-      const int buf = n & 1;
+      const int buf = n % ACC_BUFS;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&done[n % X_STAGES], (n / X_STAGES) & 1, SITE_PRE_ACCFULL));
       if (!ok) continue;
       tc_fence_after();

@@ -40,8 +40,8 @@ L2_BYTES = 126 * 1024 * 1024
 # workload's launches) from the profiler capture summarised under profiles/
 NCU_TRAFFIC_BYTES = {
     "decode": 30.49e6,            # profiles/decode_gemm_kernel_dram_traffic.md
-    "gate_up_m16": 66.16e6,       # profiles/decode_gemm_kernel_gate_up_m16.md
-    "prefill_gate_up": 299.8e6,   # profiles/prefill_gemm_kernel_gate_up_m2048.md
+    "gate_up_m16": 65.82e6,       # profiles/decode_gemm_kernel_gate_up_m16.md
+    "prefill_gate_up": 303.6e6,   # profiles/prefill_gemm_kernel_gate_up_m2048.md
 }
 
 

@@ -59,7 +59,7 @@ template <int NT>
 struct Tile {
   static constexpr int TOK = NT > 2 ? 32 : 16;            // tokens per CTA pass
   static constexpr int STAGES = NT > 2 ? 3 : 4;
-  static constexpr int NTH = NT > 2 ? 2 : NT;             // MMA tiles handled together (register budget)
+  static constexpr int NTH = NT > 2 ? 2 : NT;             // MMA tiles handled together (register pressure)
   static constexpr int HALVES = NT / NTH;
   static constexpr int X_TILE_BYTES = TOK * BCOL;         // per group
   static constexpr int SUMX_BYTES = TOK * 4;              // per group: one 64-byte piece per 16 tokens

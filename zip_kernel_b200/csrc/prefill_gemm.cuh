@@ -58,7 +58,7 @@ constexpr int A_COLS = BCOL / 4;                  // 32 TMEM columns hold one wi
 constexpr int ACC_BUFS = W4A4_ACC_BUFS;           // int32 accumulator buffers: the MMAs run this many steps ahead of the fold
 constexpr int A_COL0 = ACC_BUFS * TN;             // after the accumulator buffers
 constexpr int TMEM_COLS = 512;                    // power of two >= ACC_BUFS * TN + A_BUFS * A_COLS
-static_assert(ACC_BUFS * TN + A_BUFS * A_COLS <= TMEM_COLS, "tensor memory budget");
+static_assert(ACC_BUFS * TN + A_BUFS * A_COLS <= TMEM_COLS, "tensor memory capacity");
 
 #ifndef W4A4_FOLD_WARPS
 #define W4A4_FOLD_WARPS 8

@@ -24,13 +24,24 @@
 //     instead of 96 KB, and shared-memory bandwidth is what a 128 x 128 tile
 //     runs out of first;
 //   * one thread issues four tcgen05.mma kind::i8 (K = 32 each, A from TMEM, B
-//     from shared memory) into a fresh int32 accumulator in TMEM (three accumulator
-//     buffers rotate) and commits ONCE to a ring of "step done" mbarriers:
+//     from shared memory) into a fresh int32 accumulator in TMEM (two accumulator
+//     buffers alternate).  It waits on ONE "ready" mbarrier per step, on which the
+//     activation copy, the unpack warps and the fold warps (accumulator buffer
+//     folded) all arrive, and commits ONCE to a ring of "step done" mbarriers that
 //     the fold warps (accumulator ready), the unpack warps (A buffer free again)
-//     and the producer (activation slot free again) all wait on that ring;
+//     and the producer (activation slot free again) wait on: its loop is a chain
+//     of dependent instructions of a single thread that competes for issue slots
+//     with twelve busy warps, so it is kept as short as it can be;
 //   * eight fold warps read the accumulator with tcgen05.ld and fold it in fp32:
-//     y += acc * (s/16) - (s*z) * sumX  (per-(row, group) scales make this drain
-//     per group inherent to the contract), keeping y (128 x TN fp32) in registers.
+//     y += acc * (s/16), keeping y (128 x TN fp32) in registers as packed pairs;
+//   * the zero-point term  Z[n,t] = sum_g (s*z)[n,g] * sumX[t,g]  is a small GEMM of
+//     its own and runs on the tensor core too: per window of 16 groups the fold
+//     warps lay out (s*z) - exact in fp32, split into two 11-bit halves - and the
+//     tokens' group sums (below 2^11) as tf32 operand tiles, the MMA thread issues
+//     four tcgen05.mma kind::tf32 into a third, fp32 accumulator, and the epilogue
+//     subtracts it once.  The conversions and FMAs of the fold issue at half rate
+//     on this part and saturate the SM's schedulers long before the tensor pipe is
+//     busy, so every operation taken out of the per-group fold counts.
 // Epilogue: y * scale_x -> fp16 -> Y.  Every mbarrier wait is bounded; a wait
 // that gives up records an error, all roles fall through to the common exit and
 // the TMEM allocation is released.
@@ -52,13 +63,12 @@ constexpr int WP_BYTES = ROWS * GROUP_BYTES;      // 8192
 constexpr int X_BYTES = TN * BCOL;                // 16384
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
 constexpr int A_COLS = BCOL / 4;                  // 32 TMEM columns hold one widened row of 128 s8
-#ifndef W4A4_ACC_BUFS
-#define W4A4_ACC_BUFS 3
-#endif
-constexpr int ACC_BUFS = W4A4_ACC_BUFS;           // int32 accumulator buffers: the MMAs run this many steps ahead of the fold
+constexpr int ACC_BUFS = 2;                       // int32 accumulator buffers: the MMAs run this many steps ahead of the fold
 constexpr int A_COL0 = ACC_BUFS * TN;             // after the accumulator buffers
-constexpr int TMEM_COLS = 512;                    // power of two >= ACC_BUFS * TN + A_BUFS * A_COLS
-static_assert(ACC_BUFS * TN + A_BUFS * A_COLS <= TMEM_COLS, "tensor memory capacity");
+constexpr int Z_COL0 = A_COL0 + A_BUFS * A_COLS;  // fp32 accumulator of the zero-point term (TN columns)
+constexpr int TMEM_COLS = 512;                    // power of two >= ACC_BUFS * TN + A_BUFS * A_COLS + TN
+static_assert(Z_COL0 + TN <= TMEM_COLS, "tensor memory capacity");
+constexpr int ZT_BYTES = ROWS * 128;              // one tf32 operand tile of the zero-point term: 128 rows x 32 values
 
 #ifndef W4A4_FOLD_WARPS
 #define W4A4_FOLD_WARPS 8
@@ -101,8 +111,9 @@ struct SmemLayout {
   static constexpr size_t wp = 0;
   static constexpr size_t x = wp + (size_t)W_STAGES * WP_BYTES;
   static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float2 [SZ_CHUNK][128]
-  static constexpr size_t sums = sz + (size_t)SZ_CHUNK * ROWS * 8;              // float  [2][SZ_CHUNK][TN]
-  static constexpr size_t raw = sums + (size_t)2 * SZ_CHUNK * TN * 4;           // 2 x 16 bytes per (row, half): fp16 scales, zeros
+  static constexpr size_t zb = sz + (size_t)SZ_CHUNK * ROWS * 8;                // tf32 [2][TN tokens][32]: group sums, twice (K-major, swizzled)
+  static constexpr size_t za = zb + (size_t)2 * ZT_BYTES;                       // tf32 [128 rows][32]: high and low half of scale * zero
+  static constexpr size_t raw = za + (size_t)ZT_BYTES;                          // 2 x 16 bytes per (row, half): fp16 scales, zeros
   static constexpr size_t sxs = raw + (size_t)2 * ROWS * 32;                    // float  [TN]
   static constexpr size_t bars = sxs + (size_t)TN * 4;
   static constexpr size_t total = bars + 256;
@@ -132,6 +143,15 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
 }
 // kind::i8, s8 x s8 -> s32, both operands K-major, M = 128, N = TN
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+// kind::tf32, tf32 x tf32 -> f32, both operands K-major, M = 128, N = TN (K = 8 per instruction)
+constexpr uint32_t IDESC_TF32 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC_TF32), "r"(accumulate)
+      : "memory");
+}
 __device__ __forceinline__ void umma_i8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
   asm volatile(
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -195,16 +215,21 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   unsigned char* wp_ring = sm + SmemLayout::wp;
   unsigned char* x_ring = sm + SmemLayout::x;
   float2* szs = reinterpret_cast<float2*>(sm + SmemLayout::sz);
-  float* sums = reinterpret_cast<float*>(sm + SmemLayout::sums);
+  unsigned char* zb_tiles = sm + SmemLayout::zb;
+  unsigned char* za_tile = sm + SmemLayout::za;
   float* sxs = reinterpret_cast<float*>(sm + SmemLayout::sxs);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SmemLayout::bars);
   uint64_t* w_full = bars;                      // [W_STAGES]
   uint64_t* w_empty = w_full + W_STAGES;        // [W_STAGES]
-  uint64_t* a_full = w_empty + W_STAGES;        // [A_BUFS]   widened tile stored to tensor memory
-  uint64_t* x_full = a_full + A_BUFS;           // [X_STAGES]
-  uint64_t* done = x_full + X_STAGES;           // [X_STAGES] the MMAs of step n (slot n % X_STAGES) have completed
-  uint64_t* acc_empty = done + X_STAGES;        // [ACC_BUFS]
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + ACC_BUFS);
+  // ready[n % X_STAGES]: everything step n's MMAs need is in place - the activation tile has landed (1
+  // arrival + its bytes), the widened weights are in tensor memory (one arrival per unpack warp) and the
+  // accumulator buffer has been folded (one arrival per fold warp).  The issuing thread is a single
+  // thread competing for issue slots with twelve busy warps: one wait per step instead of three.
+  uint64_t* ready = w_empty + W_STAGES;         // [X_STAGES]
+  uint64_t* done = ready + X_STAGES;            // [X_STAGES] the MMAs of step n (slot n % X_STAGES) have completed
+  uint64_t* z_full = done + X_STAGES;           // operand tiles of a window's zero-point term are in shared memory
+  uint64_t* z_done = z_full + 1;                // ... and its MMAs have completed
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(z_done + 1);
 
   grid_launch_dependents();
   const int tid = threadIdx.x;
@@ -216,9 +241,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   if (tid == 0) {
     for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
-    for (int i = 0; i < A_BUFS; ++i) mbar_init(&a_full[i], N_UNPACK_WARPS);
-    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&x_full[i], 1); mbar_init(&done[i], 1); }
-    for (int i = 0; i < ACC_BUFS; ++i) mbar_init(&acc_empty[i], N_FOLD_WARPS);
+    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&ready[i], 1 + N_UNPACK_WARPS + N_FOLD_WARPS); mbar_init(&done[i], 1); }
+    mbar_init(z_full, N_FOLD_WARPS);
+    mbar_init(z_done, 1);
     mbar_fence_init();
     tma_prefetch_desc(&tm_w);
     tma_prefetch_desc(&tm_wh);
@@ -236,6 +261,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     b_hi = ld_plain(p.hp_row_offsets + r + 1);
   }
   const int n_steps = p.nd + (b_hi - b_lo);
+  const int n_windows = (p.nd + SZ_CHUNK - 1) / SZ_CHUNK;     // zero-point term: one small tf32 MMA batch per window of 16 groups
 
   if (warp == WARP_TMA) {
     // ------------------------------------------------------------ TMA producer
@@ -263,9 +289,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (n >= X_STAGES) ok = mbar_wait_relaxed(&done[xs], ((n - X_STAGES) / X_STAGES) & 1, SITE_PRE_XEMPTY);
         if (!ok) break;
         const int g = n < p.nd ? n : ld_plain(p.hp_col_indices + b_lo + n - p.nd);
-        mbar_arrive_expect_tx(&x_full[xs], X_BYTES);
+        mbar_arrive_expect_tx(&ready[xs], X_BYTES);
         // TN consecutive tokens of one group: contiguous and already in operand layout
-        bulk_load_1d(x_ring + xs * X_BYTES, p.XE + ((size_t)g * p.t_pad + tok0) * BCOL, X_BYTES, &x_full[xs]);
+        bulk_load_1d(x_ring + xs * X_BYTES, p.XE + ((size_t)g * p.t_pad + tok0) * BCOL, X_BYTES, &ready[xs]);
         if (++xs == X_STAGES) xs = 0;
       }
     }
@@ -275,21 +301,48 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       bool ok = true;
       int xs = 0;
       uint32_t xph = 0;
-      for (int n = 0; n < n_steps && ok; ++n) {
-        const int buf = n % ACC_BUFS, ab = n % A_BUFS;
-        ok = mbar_wait_relaxed(&acc_empty[buf], ((n / ACC_BUFS) & 1) ^ 1, SITE_PRE_ACCEMPTY);
-        if (ok) ok = mbar_wait_relaxed(&a_full[ab], (n / A_BUFS) & 1, SITE_PRE_AFULL);
-        if (ok) ok = mbar_wait_relaxed(&x_full[xs], xph, SITE_PRE_XFULL);
-        if (!ok) break;
+      int z_next = 0;
+      // Z[n, t] += sum over the window's 16 groups of (scale * zero)[n, g] * sumX[t, g]: both factors
+      // as tf32 (the product of two fp16 values split into two 11-bit halves; sums below 2^11 are
+      // exact), four MMAs of K = 8 over the 32 values of an operand row
+      auto issue_zero_term = [&](int k) {
+        bool zok = mbar_wait_relaxed(z_full, k & 1, SITE_PRE_AFULL);
+        if (!zok) return false;
         tc_fence_after();
-        const uint64_t bdesc = smem_desc_sw128(x_ring + xs * X_BYTES);
-        const uint32_t d = tmem_base + buf * TN;
-        const uint32_t a = tmem_base + A_COL0 + ab * A_COLS;
+        const uint64_t za_desc = smem_desc_sw128(za_tile);
+        const uint64_t zb_desc = smem_desc_sw128(zb_tiles + (k & 1) * ZT_BYTES);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) umma_i8_ta(d, a + j * 8, bdesc + j * 2, j > 0);   // K = 32: 8 columns of A, 32 bytes of B
+        for (int j = 0; j < 4; ++j) umma_tf32(tmem_base + Z_COL0, za_desc + j * 2, zb_desc + j * 2, (k > 0 || j > 0) ? 1u : 0u);
+        umma_commit(z_done);
+        return true;
+      };
+      int buf = 0, ab = 0;
+      const uint64_t bdesc0 = smem_desc_sw128(x_ring);
+      const uint32_t d0 = tmem_base, a0 = tmem_base + A_COL0;
+      const bool with_z = p.Y != nullptr && n_windows > 0;
+      int z_due = ACC_BUFS;          // step at which the next window's zero-point MMAs are issued
+      for (int n = 0; n < n_steps && ok; ++n) {
+        // a window's tiles are ready once the fold warps have passed its boundary, which they
+        // have when they return the accumulator of the window's first step
+        if (with_z && n == z_due && z_next < n_windows) {
+          ok = issue_zero_term(z_next++);
+          z_due += SZ_CHUNK;
+          if (!ok) break;
+        }
+        if (!mbar_wait(&ready[xs], xph, SITE_PRE_XFULL)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t bdesc = bdesc0 + (uint64_t)(xs * (X_BYTES >> 4));
+        const uint32_t d = d0 + buf * TN, a = a0 + ab * A_COLS;
+        umma_i8_ta(d, a, bdesc, 0);                    // K = 32 each: 8 columns of A, 32 bytes of B
+        umma_i8_ta(d, a + 8, bdesc + 2, 1);
+        umma_i8_ta(d, a + 16, bdesc + 4, 1);
+        umma_i8_ta(d, a + 24, bdesc + 6, 1);
         umma_commit(&done[xs]);
         if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
+        if (++buf == ACC_BUFS) buf = 0;
+        ab ^= 1;
       }
+      while (ok && p.Y != nullptr && z_next < n_windows) ok = issue_zero_term(z_next++);
     }
   } else if (warp < WARP_FOLD0) {
     // ------------------------------------------------------------ unpack warps
@@ -329,7 +382,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       __syncwarp();
       if (ok && lane == 0) {
         mbar_arrive(&w_empty[ws]);
-        mbar_arrive(&a_full[buf]);
+        mbar_arrive(&ready[n % X_STAGES]);
       }
       if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
     }
@@ -341,7 +394,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int rl = quarter * 32 + lane;          // local row
     const int row = row0 + rl;
     const int c0 = chalf * COLS_PER_FOLD;
-    const uint32_t szs_a = smem_u32(szs), sums_a = smem_u32(sums);
+    const uint32_t szs_a = smem_u32(szs), zb_a = smem_u32(zb_tiles), za_a = smem_u32(za_tile);
     grid_dependency_wait();
     for (int i = ft; i < TN; i += FOLD_THREADS)
       sxs[i] = (tok0 + i < p.T && p.scale_x) ? __half2float(ld_plain(p.scale_x + tok0 + i)) : 0.f;
@@ -366,9 +419,17 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const int i = ft + k * FOLD_THREADS;
         const int gl = i / TN, t = i - gl * TN;
         const int g = gwin + gl, tok = tok0 + t;
-        const uint32_t dst = sums_a + (sel * SZ_CHUNK * TN + i) * 4;
-        if (p.sumxf && g < p.ng && tok < p.T) cp_async_4(dst, p.sumxf + ((size_t)(tok >> 4) * p.ng + g) * 16 + (tok & 15));
-        else sts_f1(dst, 0.f);
+        // operand row = token, value gl and again gl + 16 (for the low half of scale * zero); 16-byte chunks swizzled by row
+        const uint32_t rowa = zb_a + sel * ZT_BYTES + t * 128 + (gl & 3) * 4;
+        const uint32_t d0 = rowa + ((((gl >> 2)) ^ (t & 7)) << 4), d1 = rowa + ((((gl >> 2) + 4) ^ (t & 7)) << 4);
+        if (p.sumxf && g < p.ng && tok < p.T) {
+          const float* src = p.sumxf + ((size_t)(tok >> 4) * p.ng + g) * 16 + (tok & 15);
+          cp_async_4(d0, src);
+          cp_async_4(d1, src);
+        } else {
+          sts_f1(d0, 0.f);
+          sts_f1(d1, 0.f);
+        }
       }
       if (ft < 2 * ROWS) {
         const int grow = row0 + lrow;
@@ -398,31 +459,53 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const uint4 ps = lds_v4(raw_a), pz = lds_v4(raw_a + 16);
       const __half2* hs = reinterpret_cast<const __half2*>(&ps);
       const __half2* hz = reinterpret_cast<const __half2*>(&pz);
+      float chi[8], clo[8];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
-        sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * 0.0625f, s2.x * z2.x));
-        sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * 0.0625f, s2.y * z2.y));
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * 0.0625f, 0.f));
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * 0.0625f, 0.f));
+        // scale * zero is exact in fp32 (two 11-bit significands); its upper 11 bits and the exact rest are both tf32 values
+        const float c0_ = s2.x * z2.x, c1_ = s2.y * z2.y;
+        chi[2 * i] = __uint_as_float(__float_as_uint(c0_) & 0xFFFFE000u);
+        chi[2 * i + 1] = __uint_as_float(__float_as_uint(c1_) & 0xFFFFE000u);
+        clo[2 * i] = c0_ - chi[2 * i];
+        clo[2 * i + 1] = c1_ - chi[2 * i + 1];
+      }
+      // operand row = weight row: values lhalf * 8 .. + 7 (upper halves) and 16 + lhalf * 8 .. (rests)
+      const uint32_t rowa = za_a + lrow * 128;
+#pragma unroll
+      for (int q = 0; q < 2; ++q) {
+        sts_v4(rowa + (((lhalf * 2 + q) ^ (lrow & 7)) << 4),
+               make_uint4(__float_as_uint(chi[4 * q]), __float_as_uint(chi[4 * q + 1]), __float_as_uint(chi[4 * q + 2]), __float_as_uint(chi[4 * q + 3])));
+        sts_v4(rowa + (((4 + lhalf * 2 + q) ^ (lrow & 7)) << 4),
+               make_uint4(__float_as_uint(clo[4 * q]), __float_as_uint(clo[4 * q + 1]), __float_as_uint(clo[4 * q + 2]), __float_as_uint(clo[4 * q + 3])));
       }
     };
 
     bool ok = true;
     if (p.nd > 0) issue_window(0, 0);
+    // the accumulator buffers start out free: this warp's share of the first steps' readiness
+    if (lane == 0)
+      for (int i = 0; i < ACC_BUFS && i < n_steps; ++i) mbar_arrive(&ready[i % X_STAGES]);
     for (int n = 0; n < n_steps; ++n) {
       const bool is_dense = n < p.nd;
       if (is_dense && (n % SZ_CHUNK) == 0) {
+        const int k = n / SZ_CHUNK;
         cp_async_wait_all();                                                // this thread's pieces of the window have landed
+        // the previous window's zero-point MMAs read the weight-side tile and the sums tile that is refilled next
+        if (ok && k > 0 && p.Y != nullptr) ok = __all_sync(0xffffffffu, mbar_wait(z_done, (k - 1) & 1, SITE_PRE_AEMPTY));
         asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");   // previous window no longer read
         park_window();
-        if (n + SZ_CHUNK < p.nd) issue_window(n + SZ_CHUNK, ((n / SZ_CHUNK) + 1) & 1);
-        asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");   // table and sums of this window visible to all
+        fence_proxy_async_smem();                                           // this thread's tile pieces -> visible to the tensor core
+        if (n + SZ_CHUNK < p.nd) issue_window(n + SZ_CHUNK, (k + 1) & 1);
+        asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");   // table of this window visible to all
+        if (lane == 0) mbar_arrive(z_full);
       }
-      float f = 0.f, c = 0.f;
+      float f = 0.f;
       int blk = 0;
       if (is_dense) {
-        const float2 v = lds_f2(szs_a + ((n % SZ_CHUNK) * ROWS + rl) * 8);
-        f = v.x;
-        c = v.y;
+        f = lds_f2(szs_a + ((n % SZ_CHUNK) * ROWS + rl) * 8).x;
       } else {
         blk = b_lo + n - p.nd;
         if (p.scale_u4 && row < p.N)
@@ -433,28 +516,15 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&done[n % X_STAGES], (n / X_STAGES) & 1, SITE_PRE_ACCFULL));
       if (!ok) continue;
       tc_fence_after();
-      const uint32_t srow = sums_a + ((((n / SZ_CHUNK) & 1) * SZ_CHUNK + (n % SZ_CHUNK)) * TN + c0) * 4;
-      const f32x2_t f2 = pack_f32x2(f, f), nc2 = pack_f32x2(-c, -c);
+      const f32x2_t f2 = pack_f32x2(f, f);
 #pragma unroll
       for (int cc = 0; cc < COLS_PER_FOLD; cc += 32) {
         uint32_t a[32];
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TN + c0 + cc, a);
-        if (is_dense) {
+        // y += acc * (scale / 16): the zero-point term is accumulated by the tensor core (see the MMA thread)
 #pragma unroll
-          for (int i = 0; i < 32; i += 4) {
-            // the same four group sums for every lane: one broadcast 128-bit load
-            f32x2_t sx0, sx1;
-            lds_f32x2_pair(srow + (cc + i) * 4, sx0, sx1);
-            const f32x2_t t0 = fma_f32x2(nc2, sx0, y2[(cc + i) >> 1]);
-            const f32x2_t t1 = fma_f32x2(nc2, sx1, y2[((cc + i) >> 1) + 1]);
-            y2[(cc + i) >> 1] = fma_f32x2(cvt_s32x2_f32x2(a[i], a[i + 1]), f2, t0);
-            y2[((cc + i) >> 1) + 1] = fma_f32x2(cvt_s32x2_f32x2(a[i + 2], a[i + 3]), f2, t1);
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; i += 2)
-            y2[(cc + i) >> 1] = fma_f32x2(cvt_s32x2_f32x2(a[i], a[i + 1]), f2, y2[(cc + i) >> 1]);
-        }
+        for (int i = 0; i < 32; i += 2)
+          y2[(cc + i) >> 1] = fma_f32x2(cvt_s32x2_f32x2(a[i], a[i + 1]), f2, y2[(cc + i) >> 1]);
         if (DUMP) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -477,7 +547,29 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      // the buffer is free again: it will be written by step n + ACC_BUFS
+      if (lane == 0 && n + ACC_BUFS < n_steps) mbar_arrive(&ready[(n + ACC_BUFS) % X_STAGES]);
+    }
+
+    // ---------------------------------------------------------- zero-point term
+    // y -= Z, the tensor core's sum over all groups of (scale * zero) * sumX (every lane takes part in the TMEM reads)
+    if (p.Y != nullptr && n_windows > 0) {
+      if (ok) ok = __all_sync(0xffffffffu, mbar_wait(z_done, (n_windows - 1) & 1, SITE_PRE_ACCFULL));
+      if (ok) {
+        tc_fence_after();
+        const f32x2_t minus1 = pack_f32x2(-1.f, -1.f);
+#pragma unroll
+        for (int cc = 0; cc < COLS_PER_FOLD; cc += 32) {
+          uint32_t z[32];
+          tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Z_COL0 + c0 + cc, z);
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            f32x2_t zz;
+            asm("mov.b64 %0, {%1, %2};" : "=l"(zz) : "r"(z[i]), "r"(z[i + 1]));
+            y2[(cc + i) >> 1] = fma_f32x2(zz, minus1, y2[(cc + i) >> 1]);
+          }
+        }
+      }
     }
 
     // ---------------------------------------------------------- epilogue

@@ -141,6 +141,43 @@ int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t*
                            int32_t* acc_hi, int T, int K, int N, int nnz, int flags, void* workspace,
                            size_t workspace_bytes, void* stream);
 
+/* Prepared weights for many-token calls (prefill).  sm_100a tensor cores have no
+ * 4-bit integer MMA, so the many-token kernel widens every weight nibble on the SM
+ * on every call, and that widening - not the tensor pipe - bounds it.  A caller
+ * with memory to spare can widen ONCE, after loading the weights (a load-time step,
+ * where the reference has its adapter backend/weight_loader.py:111
+ * pack_v9_weights_for_cutlass; no counterpart in its bindings):
+ * w4a4_prepare_weights turns a packed array (W_low, or W_high) into one byte per
+ * code - the e4m3 encoding of the code, exact for -8..7, each packed 32-bit word
+ * becoming its four even-indexed codes followed by its four odd-indexed ones, row
+ * shape kept - of w4a4_prepared_weights_bytes(packed_bytes) = 2 x packed_bytes
+ * bytes.  The *_prepared entry points take the packed arrays AND the prepared ones:
+ * calls that go to the tensor-core kernel then run e4m3 x e4m3 MMAs with fp32
+ * accumulation on the prepared bytes (the products and sums are small integers,
+ * exact in fp32, so every accumulator and every output bit equals the packed
+ * path's); calls with few tokens stream the packed arrays as before.  NULL
+ * prepared pointers (both, or the one of an operand in use) select the packed path.
+ * Prepared pointers must be 16-byte aligned. */
+size_t w4a4_prepared_weights_bytes(size_t packed_bytes);
+int w4a4_prepare_weights(const void* packed, void* prepared, size_t packed_bytes, void* stream);
+int w4a4_fused_dense_sparse_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
+                                     const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                     const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
+                                     const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y,
+                                     int T, int K, int N, int nnz, int flags, void* workspace,
+                                     size_t workspace_bytes, void* stream);
+int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const int32_t* perm, const void* W_low,
+                                           const void* W_high, const void* W_low_prepared,
+                                           const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                           const int32_t* hp_col_indices, const void* scale_u4,
+                                           const void* zero_u4, void* Y, int T, int K, int N, int nnz,
+                                           int flags, void* workspace, size_t workspace_bytes, void* stream);
+int w4a4_dump_accumulators_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
+                                    const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                    const int32_t* hp_col_indices, const void* X_s4, int32_t* acc,
+                                    int32_t* acc_hi, int T, int K, int N, int nnz, int flags, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
 /* No counterpart in the reference (its launchers allocate split-K partials with
  * torch::empty, fused_dense_sparse_mma_int4.cu:1873-1879).
  *

@@ -1,0 +1,114 @@
+"""Prepared weights: the many-token kernel on weights widened once to one e4m3 byte per
+code (tcgen05 kind::f8f6f4, fp32 accumulation) must give the packed path's accumulators
+and outputs bit for bit - the products and sums are small integers, exact in fp32."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import w4a4_oracle as O
+from helpers import assert_close_fp16, container_np, make_case, np_, oracle_fused
+
+pytestmark = pytest.mark.gpu
+
+# e4m3 encodings (sign, 4 exponent bits of bias 7, 3 mantissa bits) of the integers -8..7
+E4M3 = {0: 0x00, 1: 0x38, 2: 0x40, 3: 0x44, 4: 0x48, 5: 0x4A, 6: 0x4C, 7: 0x4E, 8: 0x50}
+
+
+def e4m3_of_codes(codes):
+    table = np.array([(0x80 | E4M3[-v]) if v < 0 else E4M3[v] for v in range(-8, 8)], dtype=np.uint8)
+    return table[np.asarray(codes, dtype=np.int64) + 8]
+
+
+def prepared_reference(packed):
+    """One byte per code; every packed 32-bit word (8 codes) becomes its even-indexed codes, then its odd-indexed ones."""
+    b = np.ascontiguousarray(packed).view(np.uint8).reshape(-1, 4)
+    lo = (b & 0xF).astype(np.int8)
+    hi = (b >> 4).astype(np.int8)
+    lo = np.where(lo >= 8, lo - 16, lo)
+    hi = np.where(hi >= 8, hi - 16, hi)
+    out = np.concatenate([e4m3_of_codes(lo), e4m3_of_codes(hi)], axis=1)            # (words, 8)
+    return out.reshape(packed.shape[:-1] + (packed.shape[-1] * 2,))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from zip_kernel_b200 import ops as _ops
+    return _ops
+
+
+def prepare(ops, Wd):
+    return ops.prepare_weights_cuda(Wd.W_low_packed), ops.prepare_weights_cuda(Wd.W_high_blocks_packed)
+
+
+def fused(ops, Wd, q, **kw):
+    return ops.fused_dense_sparse_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices,
+                                       q[0], Wd.scale_u4, Wd.zero_u4, q[2], q[1], Wd.d_out, Wd.d_in, **kw)
+
+
+def test_prepared_bytes(ops):
+    W, _ = make_case(4, 300, 512, 0.2)
+    Wd = W.to(torch.device("cuda"))
+    lo, hi = prepare(ops, Wd)
+    assert lo.shape == (300, 512) and hi.shape == (W.W_high_blocks_packed.shape[0], 128, 128)
+    assert np.array_equal(np_(lo), prepared_reference(np_(W.W_low_packed)))
+    assert np.array_equal(np_(hi), prepared_reference(np_(W.W_high_blocks_packed)))
+    # every code value in every nibble position
+    allv = torch.arange(256, dtype=torch.uint8).view(torch.int8).repeat(4).reshape(8, 128).cuda()
+    assert np.array_equal(np_(ops.prepare_weights_cuda(allv)), prepared_reference(np_(allv)))
+
+
+@pytest.mark.parametrize("T,N,K,density", [(300, 200, 384, 0.3), (129, 384, 1024, 0.1), (64, 128, 128, 1.0)])
+def test_prepared_accumulators_bit_exact(ops, T, N, K, density):
+    W, X = make_case(T, N, K, density, perm_seed=6)
+    Wd = W.to(torch.device("cuda"))
+    Wn = container_np(W)
+    q = ops.activation_quant_cuda(X.cuda(), Wd.perm)
+    acc, acc_hi = ops.dump_accumulators(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices,
+                                        q[0], N, K, force="tensor", prepared=prepare(ops, Wd))
+    xs4 = np_(q[0])
+    assert np.array_equal(np_(acc), O.group_accumulators(Wn["W_low_packed"], xs4))
+    assert np.array_equal(np_(acc_hi), O.block_accumulators(Wn["W_high_blocks_packed"], Wn["hp_col_indices"], xs4))
+
+
+@pytest.mark.parametrize("T,N,K,density", [(300, 200, 384, 0.3), (2048, 1024, 4096, 0.05), (257, 6144, 2048, 0.0)])
+def test_prepared_outputs_equal_packed(ops, T, N, K, density):
+    W, X = make_case(T, N, K, density, perm_seed=8)
+    Wd = W.to(torch.device("cuda"))
+    prep = prepare(ops, Wd)
+    Xd = X.cuda()
+    q = ops.activation_quant_cuda(Xd, Wd.perm)
+    Yp = fused(ops, Wd, q, force="tensor")
+    Yf = fused(ops, Wd, q, force="tensor", prepared=prep)
+    assert torch.equal(Yf, Yp)
+    args = (Xd, Wd.perm, Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices,
+            Wd.scale_u4, Wd.zero_u4, N, K)
+    Ye = ops.fused_dense_sparse_e2e_cuda(*args, force="tensor", prepared=prep)
+    assert torch.equal(Ye, Yp)
+    Yt = ops.fused_dense_sparse_e2e_cuda(*args, force="tensor", prepared=prep, token_major=True)
+    assert torch.equal(Yt.t(), Yp)
+    if T <= 512:
+        xs4, sx, sumx = (np_(t) for t in q)
+        assert_close_fp16(np_(Yf), oracle_fused(container_np(W), xs4, sumx, sx), "prepared vs oracle")
+
+
+def test_prepared_few_tokens_take_the_packed_stream(ops):
+    T, N, K = 8, 512, 1024
+    W, X = make_case(T, N, K, 0.1, perm_seed=1)
+    Wd = W.to(torch.device("cuda"))
+    prep = prepare(ops, Wd)
+    args = (X.cuda(), Wd.perm, Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices,
+            Wd.scale_u4, Wd.zero_u4, N, K)
+    assert torch.equal(ops.fused_dense_sparse_e2e_cuda(*args, prepared=prep), ops.fused_dense_sparse_e2e_cuda(*args))
+
+
+def test_prepared_full_size_gate_up(ops):
+    T, K, N = 2048, 4096, 28672
+    W, X = make_case(T, N, K, 0.05, perm_seed=9)
+    Wd = W.to(torch.device("cuda"))
+    prep = prepare(ops, Wd)
+    args = (X.cuda(), Wd.perm, Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices,
+            Wd.scale_u4, Wd.zero_u4, N, K)
+    assert torch.equal(ops.fused_dense_sparse_e2e_cuda(*args, prepared=prep), ops.fused_dense_sparse_e2e_cuda(*args))
+    from zip_kernel_b200 import _lib
+    assert _lib.device_error(torch.device("cuda")) == 0

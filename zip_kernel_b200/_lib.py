@@ -39,6 +39,11 @@ SIGNATURES = {
     "w4a4_fused_quant_dense_sparse": (_INT, [_PTR, _LL] + [_PTR] * 8 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_fused_dense_sparse_noalloc": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR]),
     "w4a4_dump_accumulators": (_INT, [_PTR] * 7 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_prepared_weights_bytes": (_SZ, [_SZ]),
+    "w4a4_prepare_weights": (_INT, [_PTR, _PTR, _SZ, _PTR]),
+    "w4a4_fused_dense_sparse_prepared": (_INT, [_PTR] * 12 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_fused_quant_dense_sparse_prepared": (_INT, [_PTR, _LL] + [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_dump_accumulators_prepared": (_INT, [_PTR] * 9 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
 }
 
 FLAG_OUT_TOKEN_MAJOR = 0x1

@@ -42,9 +42,16 @@ struct QuantParams {
   int vec_ok;             // 1 when every row start is 16-byte aligned
   int C;                  // CTAs (cluster size) per token; divides K/128
   int stage_row;          // 1: perm given and the dynamic shared memory holds the whole raw row behind the slice
+  int fmt;                // bytes of XE: 0 = s8 codes, 1 = e4m3 encodings of the codes (fp8 tensor-core path)
 };
 
-__device__ __forceinline__ uint2 expand_word(uint32_t w) { return make_uint2(nib_lo_s8(w), nib_hi_s8(w)); }
+// One packed word (8 codes) -> 8 bytes: its four even-indexed codes, then its four odd-indexed ones;
+// fmt 0: sign-extended s8, fmt 1: e4m3.
+__device__ __forceinline__ uint2 expand_word(uint32_t w, int fmt = 0) {
+  uint2 r = make_uint2(nib_lo_s8(w), nib_hi_s8(w));
+  if (fmt == 1) r = make_uint2(s8x4_to_e4m3x4(r.x), s8x4_to_e4m3x4(r.y));
+  return r;
+}
 
 // Expanded activation layout ("XE") read by both GEMM kernels: one byte per code,
 // group-major, [K/128][t_pad][128 bytes].  The 128 bytes of one (group, token)
@@ -203,7 +210,7 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
         word |= (uint32_t)(i1 & 0xF) << (8 * i + 4);
       }
       if (out) out[c] = word;
-      if (p.XE) *reinterpret_cast<uint2*>(p.XE + xe_offset(t, c, p.t_pad)) = expand_word(word);
+      if (p.XE) *reinterpret_cast<uint2*>(p.XE + xe_offset(t, c, p.t_pad)) = expand_word(word, p.fmt);
     }
 #pragma unroll
     for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
@@ -236,6 +243,7 @@ struct ExpandParams {
   int8_t* XE;           // group-major expanded codes (see xe_offset)
   float* sumxf;         // [ceil(T/16)][K/128][16]
   int T, K, t_pad;
+  int fmt;              // as QuantParams::fmt
 };
 
 __global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandParams p) {
@@ -247,7 +255,7 @@ __global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandPar
   const int wpr = p.K >> 3;     // packed words per token
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride) {
     const int t = (int)(i / wpr), c = (int)(i - (long long)t * wpr);
-    *reinterpret_cast<uint2*>(p.XE + xe_offset(t, c, p.t_pad)) = expand_word(ld_plain(src + i));
+    *reinterpret_cast<uint2*>(p.XE + xe_offset(t, c, p.t_pad)) = expand_word(ld_plain(src + i), p.fmt);
   }
   if (p.sum_X) {
     const int ng = p.K >> 7;
@@ -257,6 +265,15 @@ __global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandPar
       p.sumxf[((long long)(t >> 4) * ng + g) * 16 + (t & 15)] = (float)ld_plain(p.sum_X + i);
     }
   }
+}
+
+// Weights prepared for the fp8 tensor-core path: every packed word of nibbles (dense rows or residual
+// blocks alike) becomes its 8 codes as e4m3 bytes in the same even-then-odd order as the activations,
+// so a row of K codes is K bytes and the row-major shape is kept.
+__global__ void __launch_bounds__(256) prepare_weights_kernel(const uint32_t* packed, uint2* out, long long words) {
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride)
+    out[i] = expand_word(ld_plain(packed + i), 1);
 }
 
 }  // namespace w4a4

@@ -215,6 +215,19 @@ __device__ __forceinline__ uint32_t sext4_bytes(uint32_t x) {
 }
 __device__ __forceinline__ uint32_t nib_lo_s8(uint32_t w) { return sext4_bytes(w & 0x0F0F0F0Fu); }
 __device__ __forceinline__ uint32_t nib_hi_s8(uint32_t w) { return sext4_bytes((w >> 4) & 0x0F0F0F0Fu); }
+// Four s8 values in [-8, 7] -> their e4m3 encodings (exact: |v| <= 8 needs at most 3 mantissa bits).
+// Two 8-entry byte tables looked up with prmt (index = value & 7), merged by the sign byte mask.
+__device__ __forceinline__ uint32_t s8x4_to_e4m3x4(uint32_t x) {
+  const uint32_t y = x & 0x07070707u;
+  const uint32_t sel = (y & 0x7u) | ((y >> 4) & 0x70u) | ((y >> 8) & 0x700u) | ((y >> 12) & 0x7000u);
+  uint32_t pos, neg, mask;
+  //            v = 0     1     2     3            4     5     6     7
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(pos) : "r"(0x44403800u), "r"(0x4E4C4A48u), "r"(sel));
+  //            v = -8    -7    -6    -5           -4    -3    -2    -1
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(neg) : "r"(0xCACCCED0u), "r"(0xB8C0C4C8u), "r"(sel));
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(mask) : "r"(x), "r"(0u), "r"(0xBA98u));   // 0xFF where the byte is negative
+  return (pos & ~mask) | (neg & mask);
+}
 
 // ---------------------------------------------------------------- legacy int8 MMA (decode path)
 // D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)

@@ -56,11 +56,9 @@ namespace pre {
 
 constexpr int ROWS = 128;                 // MMA M
 constexpr int TN = 128;                   // tokens per CTA = MMA N
-constexpr int W_STAGES = 6;               // packed weight tiles in flight (8 KB each)
 constexpr int A_BUFS = 2;                 // widened weight tiles in tensor memory
-constexpr int X_STAGES = 6;               // activation tiles in flight (16 KB each) = depth of the "step done" ring
-constexpr int WP_BYTES = ROWS * GROUP_BYTES;      // 8192
 constexpr int X_BYTES = TN * BCOL;                // 16384
+constexpr int MAX_STAGES = 6;
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
 constexpr int A_COLS = BCOL / 4;                  // 32 TMEM columns hold one widened row of 128 s8
 constexpr int ACC_BUFS = 2;                       // int32 accumulator buffers: the MMAs run this many steps ahead of the fold
@@ -107,8 +105,17 @@ struct Params {
 
 inline bool supported(int T, int K, int N) { return T >= 1 && K >= 128 && N >= 1; }
 
+// Geometry of the two instantiations.  F8 = false: packed nibbles are copied in (8 KB per step) and
+// widened on the SM.  F8 = true: the caller supplies weights prepared as e4m3 bytes (16 KB per step, the
+// A operand as it is), activations are e4m3 too, the MMA is kind::f8f6f4 with fp32 accumulators - the
+// same integers, as floats - and neither the unpack warps nor the int -> float conversion have work.
+template <bool F8>
 struct SmemLayout {
-  static constexpr size_t wp = 0;
+  static constexpr int W_STAGES = F8 ? 4 : 6;               // weight tiles in flight
+  static constexpr int X_STAGES = F8 ? 4 : 6;               // activation tiles in flight = depth of the "ready" / "step done" rings
+  static constexpr int WP_BYTES = F8 ? ROWS * BCOL : ROWS * GROUP_BYTES;
+  static_assert(!F8 || W_STAGES == X_STAGES, "with prepared weights both copies of a step share a ring slot index");
+    static constexpr size_t wp = 0;
   static constexpr size_t x = wp + (size_t)W_STAGES * WP_BYTES;
   static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float2 [SZ_CHUNK][128]
   static constexpr size_t zb = sz + (size_t)SZ_CHUNK * ROWS * 8;                // tf32 [2][TN tokens][32]: group sums, twice (K-major, swizzled)
@@ -118,7 +125,7 @@ struct SmemLayout {
   static constexpr size_t bars = sxs + (size_t)TN * 4;
   static constexpr size_t total = bars + 256;
 };
-inline size_t smem_bytes() { return 1024 + SmemLayout::total; }
+inline size_t smem_bytes(bool f8) { return 1024 + (f8 ? SmemLayout<true>::total : SmemLayout<false>::total); }
 
 // ---------------------------------------------------------------- tcgen05 wrappers
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
@@ -143,6 +150,15 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(const void* tile) {
 }
 // kind::i8, s8 x s8 -> s32, both operands K-major, M = 128, N = TN
 constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+// kind::f8f6f4, e4m3 x e4m3 -> f32, both operands K-major in shared memory, M = 128, N = TN (K = 32 per instruction)
+constexpr uint32_t IDESC_F8 = (1u << 4) | (0u << 7) | (0u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
+__device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC_F8), "r"(accumulate)
+      : "memory");
+}
 // kind::tf32, tf32 x tf32 -> f32, both operands K-major, M = 128, N = TN (K = 8 per instruction)
 constexpr uint32_t IDESC_TF32 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(TN >> 3) << 17) | ((uint32_t)(ROWS >> 4) << 24);
 __device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
@@ -206,10 +222,12 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   return d;
 }
 
-template <bool DUMP>
+template <bool DUMP, bool F8>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wh,
                     const Params p) {
+  using SmemLayout = pre::SmemLayout<F8>;
+  constexpr int W_STAGES = SmemLayout::W_STAGES, X_STAGES = SmemLayout::X_STAGES, WP_BYTES = SmemLayout::WP_BYTES;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* wp_ring = sm + SmemLayout::wp;
@@ -241,7 +259,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   if (tid == 0) {
     for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
-    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&ready[i], 1 + N_UNPACK_WARPS + N_FOLD_WARPS); mbar_init(&done[i], 1); }
+    // arrivals per step: the activation copy, then either the four unpack warps or the weight copy, then the fold warps
+    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&ready[i], (F8 ? 2 : 1 + N_UNPACK_WARPS) + N_FOLD_WARPS); mbar_init(&done[i], 1); }
     mbar_init(z_full, N_FOLD_WARPS);
     mbar_init(z_done, 1);
     mbar_fence_init();
@@ -270,9 +289,11 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       // weights do not depend on the preceding kernel: fill the packed ring first
       const int n_pre = min(W_STAGES, n_steps);
       auto issue_w = [&](int n, int st) {
-        mbar_arrive_expect_tx(&w_full[st], WP_BYTES);
-        if (n < p.nd) tma_load_2d(wp_ring + st * WP_BYTES, &tm_w, n * GROUP_BYTES, row0, &w_full[st]);
-        else          tma_load_2d(wp_ring + st * WP_BYTES, &tm_wh, 0, (b_lo + n - p.nd) * BROW, &w_full[st]);
+        // prepared weights are the A operand as it is: the copy reports to the step's readiness barrier
+        uint64_t* bar = F8 ? &ready[st] : &w_full[st];
+        mbar_arrive_expect_tx(bar, WP_BYTES);
+        if (n < p.nd) tma_load_2d(wp_ring + st * WP_BYTES, &tm_w, n * (F8 ? BCOL : GROUP_BYTES), row0, bar);
+        else          tma_load_2d(wp_ring + st * WP_BYTES, &tm_wh, 0, (b_lo + n - p.nd) * BROW, bar);
       };
       for (int n = 0; n < n_pre; ++n) issue_w(n, n);
       grid_dependency_wait();
@@ -280,7 +301,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       uint32_t wph = 1;
       for (int n = 0; n < n_steps && ok; ++n) {
         if (n >= n_pre) {
-          ok = mbar_wait_relaxed(&w_empty[ws], wph, SITE_PRE_WEMPTY);
+          // packed tiles are released by the unpack warps, prepared tiles by the completion of the MMAs that read them
+          ok = F8 ? mbar_wait_relaxed(&done[ws], ((n - W_STAGES) / W_STAGES) & 1, SITE_PRE_WEMPTY)
+                  : mbar_wait_relaxed(&w_empty[ws], wph, SITE_PRE_WEMPTY);
           if (!ok) break;
           issue_w(n, ws);
         }
@@ -317,7 +340,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         return true;
       };
       int buf = 0, ab = 0;
-      const uint64_t bdesc0 = smem_desc_sw128(x_ring);
+      const uint64_t bdesc0 = smem_desc_sw128(x_ring), adesc0 = smem_desc_sw128(wp_ring);
       const uint32_t d0 = tmem_base, a0 = tmem_base + A_COL0;
       const bool with_z = p.Y != nullptr && n_windows > 0;
       int z_due = ACC_BUFS;          // step at which the next window's zero-point MMAs are issued
@@ -333,10 +356,18 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         tc_fence_after();
         const uint64_t bdesc = bdesc0 + (uint64_t)(xs * (X_BYTES >> 4));
         const uint32_t d = d0 + buf * TN, a = a0 + ab * A_COLS;
-        umma_i8_ta(d, a, bdesc, 0);                    // K = 32 each: 8 columns of A, 32 bytes of B
-        umma_i8_ta(d, a + 8, bdesc + 2, 1);
-        umma_i8_ta(d, a + 16, bdesc + 4, 1);
-        umma_i8_ta(d, a + 24, bdesc + 6, 1);
+        if (F8) {
+          const uint64_t adesc = adesc0 + (uint64_t)(xs * (WP_BYTES >> 4));
+          umma_f8(d, adesc, bdesc, 0);                 // K = 32 each: 32 bytes of A and of B
+          umma_f8(d, adesc + 2, bdesc + 2, 1);
+          umma_f8(d, adesc + 4, bdesc + 4, 1);
+          umma_f8(d, adesc + 6, bdesc + 6, 1);
+        } else {
+          umma_i8_ta(d, a, bdesc, 0);                  // K = 32 each: 8 columns of A, 32 bytes of B
+          umma_i8_ta(d, a + 8, bdesc + 2, 1);
+          umma_i8_ta(d, a + 16, bdesc + 4, 1);
+          umma_i8_ta(d, a + 24, bdesc + 6, 1);
+        }
         umma_commit(&done[xs]);
         if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
         if (++buf == ACC_BUFS) buf = 0;
@@ -353,7 +384,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     bool ok = true;
     int ws = 0;
     uint32_t wph = 0;
-    for (int n = 0; n < n_steps; ++n) {
+    for (int n = 0; n < (F8 ? 0 : n_steps); ++n) {       // prepared weights need no widening
       const int buf = n % A_BUFS;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&w_full[ws], wph, SITE_PRE_WFULL));
       // the A buffer was last read by the MMAs of step n - 2
@@ -463,8 +494,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
-        sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * 0.0625f, 0.f));
-        sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * 0.0625f, 0.f));
+        // int8 path: the accumulators carry the factor 16 of the widened nibbles
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * (F8 ? 1.f : 0.0625f), 0.f));
+        sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * (F8 ? 1.f : 0.0625f), 0.f));
         // scale * zero is exact in fp32 (two 11-bit significands); its upper 11 bits and the exact rest are both tf32 values
         const float c0_ = s2.x * z2.x, c1_ = s2.y * z2.y;
         chi[2 * i] = __uint_as_float(__float_as_uint(c0_) & 0xFFFFE000u);
@@ -509,8 +541,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       } else {
         blk = b_lo + n - p.nd;
         if (p.scale_u4 && row < p.N)
-          f = __half2float(ld_plain(p.scale_u4 + (size_t)row * p.ng + ld_plain(p.hp_col_indices + blk))) * 0.0625f *
-              p.sparse_weight;
+          f = __half2float(ld_plain(p.scale_u4 + (size_t)row * p.ng + ld_plain(p.hp_col_indices + blk))) *
+              (F8 ? 1.f : 0.0625f) * p.sparse_weight;
       }
       const int buf = n % ACC_BUFS;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&done[n % X_STAGES], (n / X_STAGES) & 1, SITE_PRE_ACCFULL));
@@ -523,8 +555,12 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TN + c0 + cc, a);
         // y += acc * (scale / 16): the zero-point term is accumulated by the tensor core (see the MMA thread)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2)
-          y2[(cc + i) >> 1] = fma_f32x2(cvt_s32x2_f32x2(a[i], a[i + 1]), f2, y2[(cc + i) >> 1]);
+        for (int i = 0; i < 32; i += 2) {
+          f32x2_t v;
+          if (F8) asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(a[i]), "r"(a[i + 1]));     // fp32 accumulators: the integers as floats
+          else v = cvt_s32x2_f32x2(a[i], a[i + 1]);
+          y2[(cc + i) >> 1] = fma_f32x2(v, f2, y2[(cc + i) >> 1]);
+        }
         if (DUMP) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -534,12 +570,12 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (is_dense) {
               const size_t idx = ((size_t)n * p.N + row) * p.T + tok;
               if (p.acc_dump && row < p.N) {
-                if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = ((int)a[i]) >> 4;
+                if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = F8 ? (int)__uint_as_float(a[i]) : ((int)a[i]) >> 4;
                 else record_error(SITE_PRE_DUMP, 1);
               }
             } else if (p.acc_hi_dump) {
               const size_t idx = ((size_t)blk * BROW + rl) * p.T + tok;
-              if (blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = ((int)a[i]) >> 4;
+              if (blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = F8 ? (int)__uint_as_float(a[i]) : ((int)a[i]) >> 4;
               else record_error(SITE_PRE_DUMP, 2);
             }
           }

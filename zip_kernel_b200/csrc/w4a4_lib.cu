@@ -140,6 +140,8 @@ DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_p
 struct GemmArgs {
   const void* W_low;
   const void* W_high;
+  const void* W_low_prep;  // weights prepared as e4m3 bytes (w4a4_prepare_weights), or NULL: the tensor-core path
+  const void* W_high_prep; // then runs its fp8 instantiation; the streaming path always reads the packed arrays
   const int32_t* hp_row_offsets;
   const int32_t* hp_col_indices;
   const void* X_s4;        // packed activation codes, or NULL when XE is given
@@ -156,6 +158,7 @@ struct GemmArgs {
   bool do_dense;
   float sparse_weight;
   bool pdl;                // launch as programmatic dependent of the preceding kernel
+  int xe_fmt;              // bytes of the expanded codes: 0 = s8, 1 = e4m3 (goes with prepared weights)
   void* ws;
   size_t ws_bytes;
   cudaStream_t stream;
@@ -204,6 +207,7 @@ int launch_expand(const GemmArgs& a, void* XE, float* sumxf, DeviceInfo* dev) {
   e.T = a.T;
   e.K = a.K;
   e.t_pad = xe_t_pad(a.T);
+  e.fmt = a.xe_fmt;
   const long long words = (long long)a.T * (a.K / 8);
   long long blocks = (words + 255) / 256;
   if (blocks > 4LL * dev->sm_count) blocks = 4LL * dev->sm_count;
@@ -295,10 +299,22 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   return W4A4_OK;
 }
 
-int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
+// True when the call carries prepared weights for every operand it uses.
+bool has_prepared(const GemmArgs& a) {
+  const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
+  return (!a.do_dense || a.W_low_prep != nullptr) && (!has_sparse || a.W_high_prep != nullptr) &&
+         (a.W_low_prep != nullptr || a.W_high_prep != nullptr);
+}
+
+int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   using namespace w4a4;
+  GemmArgs a = a_in;
+  const bool f8 = has_prepared(a);
   const bool dump = a.acc_dump || a.acc_hi_dump;
   const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
+  if (a.XE != nullptr && (a.xe_fmt == 1) != f8)
+    return fail(W4A4_ERR_BAD_ARG, "expanded activations and weights are in different formats");
+  a.xe_fmt = f8 ? 1 : 0;
   if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
   const int ng = a.K / BCOL;
   const int row_tiles = (a.N + pre::ROWS - 1) / pre::ROWS;
@@ -320,12 +336,19 @@ int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
   if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
 
   CUtensorMap tm_w, tm_wh;
-  // the operand that is switched off borrows the other one's map and is never read
-  int rc = make_map(&tm_w, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
-                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
+  // the operand that is switched off borrows the other one's map and is never read.  Packed rows hold
+  // two codes per byte and land under the 64-byte swizzle the unpack warps read; prepared rows hold one
+  // code per byte and land under the 128-byte swizzle of an MMA operand tile.
+  const void* w_lo = f8 ? a.W_low_prep : a.W_low;
+  const void* w_hi = f8 ? a.W_high_prep : a.W_high;
+  const uint64_t lo_row = f8 ? (uint64_t)a.K : (uint64_t)a.K / 2, hi_row = f8 ? BCOL : GROUP_BYTES;
+  const uint32_t box = f8 ? BCOL : GROUP_BYTES;
+  const CUtensorMapSwizzle swz = f8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  int rc = make_map(&tm_w, a.do_dense ? w_lo : w_hi, a.do_dense ? lo_row : hi_row,
+                    a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, box, pre::ROWS, swz);
   if (rc) return rc;
-  rc = make_map(&tm_wh, has_sparse ? a.W_high : a.W_low, has_sparse ? 64 : (uint64_t)a.K / 2,
-                has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, GROUP_BYTES, pre::ROWS, CU_TENSOR_MAP_SWIZZLE_64B);
+  rc = make_map(&tm_wh, has_sparse ? w_hi : w_lo, has_sparse ? hi_row : lo_row,
+                has_sparse ? (uint64_t)a.nnz * BROW : (uint64_t)a.N, box, pre::ROWS, swz);
   if (rc) return rc;
 
   pre::Params p;
@@ -353,9 +376,10 @@ int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
   p.sz_vec = (ng % 8 == 0 && aligned(a.scale_u4, 16) && aligned(a.zero_u4, 16)) ? 1 : 0;
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
 
-  const size_t smem = pre::smem_bytes();
+  const size_t smem = pre::smem_bytes(f8);
   void (*kern)(const CUtensorMap, const CUtensorMap, const pre::Params) =
-      dump ? pre::prefill_gemm_kernel<true> : pre::prefill_gemm_kernel<false>;
+      f8 ? (dump ? pre::prefill_gemm_kernel<true, true> : pre::prefill_gemm_kernel<false, true>)
+         : (dump ? pre::prefill_gemm_kernel<true, false> : pre::prefill_gemm_kernel<false, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(prefill): %s", cudaGetErrorString(e));
   e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, p);
@@ -364,9 +388,10 @@ int launch_prefill(const GemmArgs& a, DeviceInfo* dev) {
 }
 
 int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x, int32_t* sum_X,
-                 void* XE, float* sumxf, int T, int K, cudaStream_t stream, int sm_count) {
+                 void* XE, float* sumxf, int T, int K, cudaStream_t stream, int sm_count, int xe_fmt = 0) {
   using namespace w4a4;
   QuantParams q;
+  q.fmt = xe_fmt;
   q.X = static_cast<const __half*>(X);
   q.ldx = ldx;
   q.perm = perm;
@@ -408,6 +433,24 @@ int check_common(int T, int K, int N, int nnz) {
   return W4A4_OK;
 }
 
+// Many tokens take the tcgen05 kernel, few the weight-streaming one.
+bool wants_tensor_path(int T, int K, int N, int flags, int sm_count) {
+  // W4A4_TENSOR_MIN_T moves the switch-over (A/B runs)
+  static const int min_t = getenv("W4A4_TENSOR_MIN_T") ? atoi(getenv("W4A4_TENSOR_MIN_T")) : 0;
+  bool tensor_path;
+  if (min_t > 0) {
+    tensor_path = T >= min_t;
+  } else {
+    // measured cross-over on B200: the tensor kernel needs a grid that fills the SMs
+    const long long tiles = (long long)((N + 127) / 128) * ((T + w4a4::pre::TN - 1) / w4a4::pre::TN);
+    tensor_path = T >= 256 || (T >= 64 && tiles >= sm_count);
+  }
+  tensor_path = tensor_path && w4a4::pre::supported(T, K, N);
+  if (flags & W4A4_FLAG_FORCE_STREAM) tensor_path = false;
+  if ((flags & W4A4_FLAG_FORCE_TENSOR) && w4a4::pre::supported(T, K, N)) tensor_path = true;
+  return tensor_path;
+}
+
 int run_gemm(GemmArgs& a) {
   int rc = check_common(a.T, a.K, a.N, a.nnz);
   if (rc) return rc;
@@ -422,27 +465,12 @@ int run_gemm(GemmArgs& a) {
   DeviceInfo* dev = nullptr;
   rc = current_device(&dev);
   if (rc) return rc;
-  const bool dump = a.acc_dump || a.acc_hi_dump;
-  // few tokens: weights are streamed once and the MMA shape hardly matters; many
-  // tokens: the tcgen05 kernel.  W4A4_TENSOR_MIN_T moves the switch-over (A/B runs).
-  static const int min_t = getenv("W4A4_TENSOR_MIN_T") ? atoi(getenv("W4A4_TENSOR_MIN_T")) : 0;
-  bool tensor_path;
-  if (min_t > 0) {
-    tensor_path = a.T >= min_t;
-  } else {
-    // measured cross-over on B200: the tensor kernel needs a grid that fills the SMs
-    const long long tiles = (long long)((a.N + 127) / 128) * ((a.T + w4a4::pre::TN - 1) / w4a4::pre::TN);
-    tensor_path = a.T >= 256 || (a.T >= 64 && tiles >= dev->sm_count);
-  }
-  tensor_path = tensor_path && w4a4::pre::supported(a.T, a.K, a.N);
-  if (a.flags & W4A4_FLAG_FORCE_STREAM) tensor_path = false;
-  if (a.flags & W4A4_FLAG_FORCE_TENSOR) {
-    if (!w4a4::pre::supported(a.T, a.K, a.N))
-      return fail(W4A4_ERR_UNSUPPORTED, "tensor-core path does not support T=%d K=%d N=%d", a.T, a.K, a.N);
-    tensor_path = true;
-  }
-  (void)dump;
-  if (tensor_path) return launch_prefill(a, dev);
+  if ((a.flags & W4A4_FLAG_FORCE_TENSOR) && !w4a4::pre::supported(a.T, a.K, a.N))
+    return fail(W4A4_ERR_UNSUPPORTED, "tensor-core path does not support T=%d K=%d N=%d", a.T, a.K, a.N);
+  if (!aligned(a.W_low_prep, 16) || !aligned(a.W_high_prep, 16))
+    return fail(W4A4_ERR_ALIGNMENT, "weight pointers must be 16-byte aligned");
+  if (wants_tensor_path(a.T, a.K, a.N, a.flags, dev->sm_count)) return launch_prefill(a, dev);
+  if (a.XE != nullptr && a.xe_fmt != 0) return fail(W4A4_ERR_BAD_ARG, "the streaming path reads s8 expanded codes");
   return launch_decode(a, dev);
 }
 
@@ -538,8 +566,40 @@ int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t
                             const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
                             const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y, int T, int K,
                             int N, int nnz, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  return w4a4_fused_dense_sparse_prepared(W_low, W_high, nullptr, nullptr, hp_row_offsets, hp_col_indices, X_s4, scale_u4,
+                                          zero_u4, sum_X, scale_x, Y, T, K, N, nnz, flags, workspace, workspace_bytes,
+                                          stream);
+}
+
+size_t w4a4_prepared_weights_bytes(size_t packed_bytes) { return 2 * packed_bytes; }
+
+int w4a4_prepare_weights(const void* packed, void* prepared, size_t packed_bytes, void* stream) {
+  CHECK_ARG(packed && prepared, "NULL tensor pointer");
+  CHECK_ARG(packed_bytes % 4 == 0, "packed_bytes (%zu) must be a multiple of 4", packed_bytes);
+  if (!aligned(packed, 4) || !aligned(prepared, 16)) return fail(W4A4_ERR_ALIGNMENT, "prepare_weights pointer alignment");
+  if (packed_bytes == 0) return W4A4_OK;
+  DeviceInfo* dev = nullptr;
+  int rc = current_device(&dev);
+  if (rc) return rc;
+  const long long words = (long long)(packed_bytes / 4);
+  long long blocks = (words + 255) / 256;
+  if (blocks > 16LL * dev->sm_count) blocks = 16LL * dev->sm_count;
+  w4a4::prepare_weights_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(packed), static_cast<uint2*>(prepared), words);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "prepare_weights kernel launch: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
+int w4a4_fused_dense_sparse_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
+                                     const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                     const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
+                                     const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y, int T,
+                                     int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes,
+                                     void* stream) {
   CHECK_ARG(Y && zero_u4 && sum_X && scale_x, "NULL tensor pointer");
   GemmArgs a{};
+  a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.X_s4 = X_s4; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.sum_X = sum_X; a.scale_x = scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
@@ -622,6 +682,17 @@ int w4a4_fused_quant_dense_sparse(const void* X, long long ldx, const int32_t* p
                                   const void* W_high, const int32_t* hp_row_offsets, const int32_t* hp_col_indices,
                                   const void* scale_u4, const void* zero_u4, void* Y, int T, int K, int N, int nnz,
                                   int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  return w4a4_fused_quant_dense_sparse_prepared(X, ldx, perm, W_low, W_high, nullptr, nullptr, hp_row_offsets,
+                                                hp_col_indices, scale_u4, zero_u4, Y, T, K, N, nnz, flags, workspace,
+                                                workspace_bytes, stream);
+}
+
+int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const int32_t* perm, const void* W_low,
+                                           const void* W_high, const void* W_low_prepared,
+                                           const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                           const int32_t* hp_col_indices, const void* scale_u4, const void* zero_u4,
+                                           void* Y, int T, int K, int N, int nnz, int flags, void* workspace,
+                                           size_t workspace_bytes, void* stream) {
   int rc = check_common(T, K, N, nnz);
   if (rc) return rc;
   CHECK_ARG(X && Y && zero_u4, "NULL tensor pointer");
@@ -634,11 +705,18 @@ int w4a4_fused_quant_dense_sparse(const void* X, long long ldx, const int32_t* p
   DeviceInfo* dev = nullptr;
   rc = current_device(&dev);
   if (rc) return rc;
-  rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
-                    T, K, s, dev->sm_count);
-  if (rc) return rc;
   GemmArgs a{};
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
+  a.nnz = nnz; a.do_dense = true; a.sparse_weight = 16.f;
+  // the quantiser writes the codes in the format the GEMM kernel of this call will read
+  if (wants_tensor_path(T, K, N, flags, dev->sm_count)) {
+    a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
+    if (!has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
+  }
+  a.xe_fmt = has_prepared(a) ? 1 : 0;
+  rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
+                    T, K, s, dev->sm_count, a.xe_fmt);
+  if (rc) return rc;
   a.XE = ws + wl.xe; a.sumxf = reinterpret_cast<float*>(ws + wl.sumxf); a.scale_u4 = scale_u4; a.zero_u4 = zero_u4;
   a.scale_x = ws + wl.scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
@@ -650,8 +728,18 @@ int w4a4_fused_quant_dense_sparse(const void* X, long long ldx, const int32_t* p
 int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t* hp_row_offsets,
                            const int32_t* hp_col_indices, const void* X_s4, int32_t* acc, int32_t* acc_hi, int T,
                            int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  return w4a4_dump_accumulators_prepared(W_low, W_high, nullptr, nullptr, hp_row_offsets, hp_col_indices, X_s4, acc,
+                                         acc_hi, T, K, N, nnz, flags, workspace, workspace_bytes, stream);
+}
+
+int w4a4_dump_accumulators_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
+                                    const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                    const int32_t* hp_col_indices, const void* X_s4, int32_t* acc, int32_t* acc_hi,
+                                    int T, int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes,
+                                    void* stream) {
   CHECK_ARG(acc || acc_hi, "both outputs are NULL");
   GemmArgs a{};
+  a.W_low_prep = acc ? W_low_prepared : nullptr; a.W_high_prep = (acc_hi && nnz > 0) ? W_high_prepared : nullptr;
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.X_s4 = X_s4; a.acc_dump = acc; a.acc_hi_dump = acc_hi;
   a.T = T; a.K = K; a.N = N; a.nnz = acc_hi ? nnz : 0; a.flags = flags;

@@ -208,12 +208,39 @@ def _prep_fused(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indic
             sum_X.contiguous().to(torch.int32), scale_x.contiguous().to(torch.float16), T, d_in, d_out)
 
 
+def prepare_weights_cuda(packed: torch.Tensor) -> torch.Tensor:
+    """A packed weight array (``W_low_packed`` or ``W_high_blocks_packed``) widened once to one
+    byte per code for the many-token tensor-core kernel: same leading shape, last dimension
+    doubled, dtype uint8 (e4m3 encodings; see include/w4a4_b200.h).  Pass the results as
+    ``prepared=(low, high)`` to the fused operators.  No counterpart in the reference."""
+    assert packed.is_cuda and packed.dtype == torch.int8
+    src = packed.contiguous()
+    out = torch.empty(src.shape[:-1] + (src.shape[-1] * 2,), dtype=torch.uint8, device=src.device)
+    if src.numel():
+        with torch.cuda.device(src.device):
+            _lib.check(_L.w4a4_prepare_weights(src.data_ptr(), out.data_ptr(), src.numel(),
+                                               _lib.stream_ptr(src.device)), "prepare_weights")
+    return out
+
+
+def _prepared_ptrs(prepared, W, Wh, nnz):
+    """Device pointers of the (low, high) pair made by :func:`prepare_weights_cuda`, checked against the packed arrays."""
+    if prepared is None:
+        return None, None
+    lo, hi = prepared
+    assert lo.is_cuda and lo.dtype == torch.uint8 and lo.is_contiguous() and lo.numel() == 2 * W.numel()
+    if nnz:
+        assert hi is not None and hi.dtype == torch.uint8 and hi.is_contiguous() and hi.numel() == 2 * Wh.numel()
+    return lo.data_ptr(), (hi.data_ptr() if nnz else None)
+
+
 def fused_dense_sparse_cuda_int4(
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
     X_s4, scale_u4, zero_u4, sum_X, scale_x, d_out, d_in,
-    *, token_major: bool = False, force: Optional[str] = None,
+    *, token_major: bool = False, force: Optional[str] = None, prepared=None,
 ) -> torch.Tensor:
-    """Fused dense + 16 x residual GEMM: ``Y_total (d_out, T)`` fp16 (ops.py:471-481)."""
+    """Fused dense + 16 x residual GEMM: ``Y_total (d_out, T)`` fp16 (ops.py:471-481).
+    ``prepared``: the pair from :func:`prepare_weights_cuda` for the many-token kernel."""
     (W, Wh, ro, ci, X, s, z, sm, sx, T, K, N) = _prep_fused(
         W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
         X_s4, scale_u4, zero_u4, sum_X, scale_x, d_out, d_in)
@@ -223,8 +250,9 @@ def fused_dense_sparse_cuda_int4(
     nnz = int(Wh.shape[0])
     with torch.cuda.device(W.device):
         ws = _lib.workspace(W.device, T, K, N, nnz)
-        _lib.check(_L.w4a4_fused_dense_sparse(
-            W.data_ptr(), Wh.data_ptr() if nnz else None, ro.data_ptr(), ci.data_ptr() if nnz else None,
+        plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
+        _lib.check(_L.w4a4_fused_dense_sparse_prepared(
+            W.data_ptr(), Wh.data_ptr() if nnz else None, plo, phi, ro.data_ptr(), ci.data_ptr() if nnz else None,
             X.data_ptr(), s.data_ptr(), z.data_ptr(), sm.data_ptr(), sx.data_ptr(), Y.data_ptr(),
             T, K, N, nnz, _flags(token_major, force), ws.data_ptr(), ws.numel(),
             _lib.stream_ptr(W.device)), "fused_dense_sparse")
@@ -297,10 +325,11 @@ def fused_dense_sparse_e2e_cuda(
     X_fp16, perm,
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
     scale_u4, zero_u4, d_out, d_in,
-    *, token_major: bool = False, force: Optional[str] = None,
+    *, token_major: bool = False, force: Optional[str] = None, prepared=None,
 ) -> torch.Tensor:
     """fp16 activations in, ``Y (d_out, T)`` fp16 out: quantisation and GEMM are
-    chained inside one C-ABI call (ops.py:707-747)."""
+    chained inside one C-ABI call (ops.py:707-747).  ``prepared``: the pair from
+    :func:`prepare_weights_cuda` for the many-token kernel."""
     assert X_fp16.is_cuda and X_fp16.dtype == torch.float16
     assert perm.dtype in (torch.int32, torch.int64)
     assert W_low_packed.is_cuda and W_low_packed.dtype == torch.int8
@@ -324,9 +353,10 @@ def fused_dense_sparse_e2e_cuda(
         return Y
     with torch.cuda.device(dev):
         ws = _lib.workspace(dev, T, d_in, d_out, nnz)
-        _lib.check(_L.w4a4_fused_quant_dense_sparse(
+        plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
+        _lib.check(_L.w4a4_fused_quant_dense_sparse_prepared(
             X2.data_ptr(), X2.stride(0), perm_i32.data_ptr(), W.data_ptr(),
-            Wh.data_ptr() if nnz else None, ro.data_ptr(), ci.data_ptr() if nnz else None,
+            Wh.data_ptr() if nnz else None, plo, phi, ro.data_ptr(), ci.data_ptr() if nnz else None,
             s.data_ptr(), z.data_ptr(), Y.data_ptr(), T, d_in, d_out, nnz,
             _flags(token_major, force), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)),
             "fused_quant_dense_sparse")
@@ -363,7 +393,7 @@ def fused_quant_dense_sparse_cuda_int4(
 
 
 def dump_accumulators(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices, X_s4,
-                      d_out, d_in, *, force: Optional[str] = None):
+                      d_out, d_in, *, force: Optional[str] = None, prepared=None):
     """Parity aid: the exact int32 accumulators of the MMA path, ``acc (ng, d_out,
     T)`` per group and ``acc_hi (nnz, 128, T)`` per residual block."""
     d_out, d_in = int(d_out), int(d_in)
@@ -376,8 +406,9 @@ def dump_accumulators(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col
     X = X_s4.contiguous()
     with torch.cuda.device(dev):
         ws = _lib.workspace(dev, T, d_in, d_out, nnz)
-        _lib.check(_L.w4a4_dump_accumulators(
-            W.data_ptr(), W_high_blocks_packed.contiguous().data_ptr() if nnz else None,
+        plo, phi = _prepared_ptrs(prepared, W, W_high_blocks_packed.contiguous() if nnz else None, nnz)
+        _lib.check(_L.w4a4_dump_accumulators_prepared(
+            W.data_ptr(), W_high_blocks_packed.contiguous().data_ptr() if nnz else None, plo, phi,
             hp_row_offsets.contiguous().to(torch.int32).data_ptr() if nnz else None,
             hp_col_indices.contiguous().to(torch.int32).data_ptr() if nnz else None,
             X.data_ptr(), acc.data_ptr(), acc_hi.data_ptr() if nnz else None, T, d_in, d_out, nnz,
@@ -403,6 +434,7 @@ __all__ = [
     "fused_quant_dense_sparse_cuda_int4",
     "fused_dense_sparse_e2e_cuda",
     "dump_accumulators",
+    "prepare_weights_cuda",
     "reserve_workspace",
     "expand_activations_cuda",
     "fused_dense_sparse_expanded_cuda",

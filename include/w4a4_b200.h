@@ -172,6 +172,21 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
                                            const int32_t* hp_col_indices, const void* scale_u4,
                                            const void* zero_u4, void* Y, int T, int K, int N, int nnz,
                                            int flags, void* workspace, size_t workspace_bytes, void* stream);
+/* The same with activations expanded once for several linears: the expanded codes that go with
+ * prepared weights are e4m3 bytes as well (code_format W4A4_CODES_E4M3; the layout is that of
+ * w4a4_expand_activations, W4A4_CODES_S8 is what that function writes).  With prepared pointers
+ * the call must be one the tensor-core kernel takes (many tokens, or W4A4_FLAG_FORCE_TENSOR):
+ * the streaming kernel reads s8 codes and the call fails with W4A4_ERR_BAD_ARG otherwise. */
+#define W4A4_CODES_S8   0
+#define W4A4_CODES_E4M3 1
+int w4a4_expand_activations_fmt(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
+                                int code_format, void* stream);
+int w4a4_fused_dense_sparse_expanded_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
+                                              const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                              const int32_t* hp_col_indices, const void* XE, const float* sumxf,
+                                              const void* scale_u4, const void* zero_u4, const void* scale_x,
+                                              void* Y, int T, int K, int N, int nnz, int flags, void* workspace,
+                                              size_t workspace_bytes, void* stream);
 int w4a4_dump_accumulators_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
                                     const void* W_high_prepared, const int32_t* hp_row_offsets,
                                     const int32_t* hp_col_indices, const void* X_s4, int32_t* acc,

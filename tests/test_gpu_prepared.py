@@ -87,6 +87,11 @@ def test_prepared_outputs_equal_packed(ops, T, N, K, density):
     assert torch.equal(Ye, Yp)
     Yt = ops.fused_dense_sparse_e2e_cuda(*args, force="tensor", prepared=prep, token_major=True)
     assert torch.equal(Yt.t(), Yp)
+    XE, sumxf = ops.expand_activations_cuda(q[0], q[2], e4m3=True)
+    Yx = ops.fused_dense_sparse_expanded_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
+                                              Wd.hp_col_indices, XE, sumxf, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
+                                              force="tensor", prepared=prep)
+    assert torch.equal(Yx, Yp)
     if T <= 512:
         xs4, sx, sumx = (np_(t) for t in q)
         assert_close_fp16(np_(Yf), oracle_fused(container_np(W), xs4, sumx, sx), "prepared vs oracle")
@@ -112,3 +117,26 @@ def test_prepared_full_size_gate_up(ops):
     assert torch.equal(ops.fused_dense_sparse_e2e_cuda(*args, prepared=prep), ops.fused_dense_sparse_e2e_cuda(*args))
     from zip_kernel_b200 import _lib
     assert _lib.device_error(torch.device("cuda")) == 0
+
+
+def test_expanded_e4m3_codes_are_refused_by_the_streaming_kernel(ops):
+    T, N, K = 8, 256, 512
+    W, X = make_case(T, N, K, 0.1)
+    Wd = W.to(torch.device("cuda"))
+    q = ops.activation_quant_cuda(X.cuda(), Wd.perm)
+    XE, sumxf = ops.expand_activations_cuda(q[0], q[2], e4m3=True)
+    with pytest.raises(ValueError):
+        ops.fused_dense_sparse_expanded_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
+                                             Wd.hp_col_indices, XE, sumxf, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
+                                             prepared=prepare(ops, Wd))
+
+
+def test_prepared_container_forward(ops):
+    from zip_kernel_b200 import v9_linear
+    T, N, K = 384, 640, 1024
+    W, X = make_case(T, N, K, 0.1, perm_seed=2)
+    Wd = W.to(torch.device("cuda"))
+    Y0 = v9_linear.v9_linear_forward(X.cuda(), Wd)
+    v9_linear.prepare_for_prefill(Wd)
+    assert Wd.prepared is not None and Wd.to(torch.device("cuda")).prepared is None
+    assert torch.equal(v9_linear.v9_linear_forward(X.cuda(), Wd), Y0)

@@ -43,6 +43,8 @@ SIGNATURES = {
     "w4a4_prepare_weights": (_INT, [_PTR, _PTR, _SZ, _PTR]),
     "w4a4_fused_dense_sparse_prepared": (_INT, [_PTR] * 12 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_fused_quant_dense_sparse_prepared": (_INT, [_PTR, _LL] + [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_expand_activations_fmt": (_INT, [_PTR] * 4 + [_INT, _INT, _INT, _PTR]),
+    "w4a4_fused_dense_sparse_expanded_prepared": (_INT, [_PTR] * 12 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_dump_accumulators_prepared": (_INT, [_PTR] * 9 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
 }
 

@@ -61,11 +61,17 @@ constexpr int X_BYTES = TN * BCOL;                // 16384
 constexpr int MAX_STAGES = 6;
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
 constexpr int A_COLS = BCOL / 4;                  // 32 TMEM columns hold one widened row of 128 s8
-constexpr int ACC_BUFS = 2;                       // int32 accumulator buffers: the MMAs run this many steps ahead of the fold
-constexpr int A_COL0 = ACC_BUFS * TN;             // after the accumulator buffers
-constexpr int Z_COL0 = A_COL0 + A_BUFS * A_COLS;  // fp32 accumulator of the zero-point term (TN columns)
-constexpr int TMEM_COLS = 512;                    // power of two >= ACC_BUFS * TN + A_BUFS * A_COLS + TN
-static_assert(Z_COL0 + TN <= TMEM_COLS, "tensor memory capacity");
+constexpr int TMEM_COLS = 512;                    // the whole tensor memory of the SM (one CTA per SM)
+// Tensor-memory columns.  Accumulator buffers first (the MMAs run that many steps ahead of the fold), then
+// the widened weight tiles (packed weights only), then the fp32 accumulator of the zero-point term.
+// Prepared weights leave room for a third accumulator buffer.
+template <bool F8>
+struct TmemLayout {
+  static constexpr int ACC_BUFS = F8 ? 3 : 2;
+  static constexpr int A_COL0 = ACC_BUFS * TN;
+  static constexpr int Z_COL0 = A_COL0 + (F8 ? 0 : A_BUFS * A_COLS);
+  static_assert(Z_COL0 + TN <= TMEM_COLS, "tensor memory capacity");
+};
 constexpr int ZT_BYTES = ROWS * 128;              // one tf32 operand tile of the zero-point term: 128 rows x 32 values
 
 #ifndef W4A4_FOLD_WARPS
@@ -100,6 +106,7 @@ struct Params {
   int nd;                   // dense K-steps (ng, or 0 when the dense part is off)
   int sparse_on;
   int sz_vec;
+  int band;                 // token tiles per band of the CTA order (>= 1)
   float sparse_weight;
 };
 
@@ -111,14 +118,14 @@ inline bool supported(int T, int K, int N) { return T >= 1 && K >= 128 && N >= 1
 // same integers, as floats - and neither the unpack warps nor the int -> float conversion have work.
 template <bool F8>
 struct SmemLayout {
-  static constexpr int W_STAGES = F8 ? 4 : 6;               // weight tiles in flight
-  static constexpr int X_STAGES = F8 ? 4 : 6;               // activation tiles in flight = depth of the "ready" / "step done" rings
+  static constexpr int W_STAGES = F8 ? 5 : 6;               // weight tiles in flight
+  static constexpr int X_STAGES = F8 ? 5 : 6;               // activation tiles in flight = depth of the "ready" / "step done" rings
   static constexpr int WP_BYTES = F8 ? ROWS * BCOL : ROWS * GROUP_BYTES;
   static_assert(!F8 || W_STAGES == X_STAGES, "with prepared weights both copies of a step share a ring slot index");
     static constexpr size_t wp = 0;
   static constexpr size_t x = wp + (size_t)W_STAGES * WP_BYTES;
-  static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float2 [SZ_CHUNK][128]
-  static constexpr size_t zb = sz + (size_t)SZ_CHUNK * ROWS * 8;                // tf32 [2][TN tokens][32]: group sums, twice (K-major, swizzled)
+  static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float [SZ_CHUNK][128]: scale (/16 for int8 accumulators)
+  static constexpr size_t zb = sz + (size_t)SZ_CHUNK * ROWS * 4;                // tf32 [2][TN tokens][32]: group sums, twice (K-major, swizzled)
   static constexpr size_t za = zb + (size_t)2 * ZT_BYTES;                       // tf32 [128 rows][32]: high and low half of scale * zero
   static constexpr size_t raw = za + (size_t)ZT_BYTES;                          // 2 x 16 bytes per (row, half): fp16 scales, zeros
   static constexpr size_t sxs = raw + (size_t)2 * ROWS * 32;                    // float  [TN]
@@ -228,11 +235,13 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
                     const Params p) {
   using SmemLayout = pre::SmemLayout<F8>;
   constexpr int W_STAGES = SmemLayout::W_STAGES, X_STAGES = SmemLayout::X_STAGES, WP_BYTES = SmemLayout::WP_BYTES;
+  constexpr int ACC_BUFS = TmemLayout<F8>::ACC_BUFS, A_COL0 = TmemLayout<F8>::A_COL0, Z_COL0 = TmemLayout<F8>::Z_COL0;
+  static_assert(ACC_BUFS < X_STAGES, "the fold warps' arrival for step n + ACC_BUFS must fall into that step's barrier phase");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   unsigned char* wp_ring = sm + SmemLayout::wp;
   unsigned char* x_ring = sm + SmemLayout::x;
-  float2* szs = reinterpret_cast<float2*>(sm + SmemLayout::sz);
+  float* szs = reinterpret_cast<float*>(sm + SmemLayout::sz);
   unsigned char* zb_tiles = sm + SmemLayout::zb;
   unsigned char* za_tile = sm + SmemLayout::za;
   float* sxs = reinterpret_cast<float*>(sm + SmemLayout::sxs);
@@ -253,9 +262,16 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int r = blockIdx.x;                     // block-row
+  // CTAs are dispatched in the order of their linear index.  Bands of `band` token tiles are walked
+  // token tile first, so the CTAs resident at one time cover a compact patch of (block-rows x token
+  // tiles) whose weight and activation tiles stay in L2 while they are shared.
+  const int lin = blockIdx.x + blockIdx.y * gridDim.x;
+  const int per_band = gridDim.x * p.band;
+  const int band_i = lin / per_band, band_rem = lin - band_i * per_band;
+  const int band_h = min(p.band, (int)gridDim.y - band_i * p.band);
+  const int r = band_rem / band_h;              // block-row
   const int row0 = r * ROWS;
-  const int tok0 = blockIdx.y * TN;
+  const int tok0 = (band_i * p.band + band_rem % band_h) * TN;
 
   if (tid == 0) {
     for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
@@ -495,8 +511,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int i = 0; i < 4; ++i) {
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
         // int8 path: the accumulators carry the factor 16 of the widened nibbles
-        sts_f2(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 8, make_float2(s2.x * (F8 ? 1.f : 0.0625f), 0.f));
-        sts_f2(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 8, make_float2(s2.y * (F8 ? 1.f : 0.0625f), 0.f));
+        sts_f1(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 4, s2.x * (F8 ? 1.f : 0.0625f));
+        sts_f1(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 4, s2.y * (F8 ? 1.f : 0.0625f));
         // scale * zero is exact in fp32 (two 11-bit significands); its upper 11 bits and the exact rest are both tf32 values
         const float c0_ = s2.x * z2.x, c1_ = s2.y * z2.y;
         chi[2 * i] = __uint_as_float(__float_as_uint(c0_) & 0xFFFFE000u);
@@ -537,7 +553,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       float f = 0.f;
       int blk = 0;
       if (is_dense) {
-        f = lds_f2(szs_a + ((n % SZ_CHUNK) * ROWS + rl) * 8).x;
+        f = lds_f1(szs_a + ((n % SZ_CHUNK) * ROWS + rl) * 4);
       } else {
         blk = b_lo + n - p.nd;
         if (p.scale_u4 && row < p.N)

@@ -375,6 +375,9 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   p.sparse_on = has_sparse ? 1 : 0;
   p.sz_vec = (ng % 8 == 0 && aligned(a.scale_u4, 16) && aligned(a.zero_u4, 16)) ? 1 : 0;
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
+  // W4A4_PREFILL_BAND overrides the band height of the CTA order (A/B runs)
+  static const int env_band = getenv("W4A4_PREFILL_BAND") ? atoi(getenv("W4A4_PREFILL_BAND")) : 0;
+  p.band = env_band > 0 ? env_band : 16;
 
   const size_t smem = pre::smem_bytes(f8);
   void (*kern)(const CUtensorMap, const CUtensorMap, const pre::Params) =
@@ -615,6 +618,12 @@ size_t w4a4_expanded_sums_bytes(int T, int K) {
 
 int w4a4_expand_activations(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
                             void* stream) {
+  return w4a4_expand_activations_fmt(X_s4, sum_X, XE, sumxf, T, K, W4A4_CODES_S8, stream);
+}
+
+int w4a4_expand_activations_fmt(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
+                                int code_format, void* stream) {
+  CHECK_ARG(code_format == W4A4_CODES_S8 || code_format == W4A4_CODES_E4M3, "unknown code format %d", code_format);
   int rc = check_common(T, K, 1, 0);
   if (rc) return rc;
   CHECK_ARG(X_s4 && XE && (sum_X == nullptr || sumxf != nullptr), "NULL tensor pointer");
@@ -625,6 +634,7 @@ int w4a4_expand_activations(const void* X_s4, const int32_t* sum_X, void* XE, fl
   if (rc) return rc;
   GemmArgs a{};
   a.X_s4 = X_s4; a.sum_X = sum_X; a.T = T; a.K = K; a.stream = static_cast<cudaStream_t>(stream);
+  a.xe_fmt = code_format;
   return launch_expand(a, XE, sumxf, dev);
 }
 
@@ -633,8 +643,24 @@ int w4a4_fused_dense_sparse_expanded(const void* W_low, const void* W_high, cons
                                      const void* scale_u4, const void* zero_u4, const void* scale_x, void* Y, int T,
                                      int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes,
                                      void* stream) {
+  return w4a4_fused_dense_sparse_expanded_prepared(W_low, W_high, nullptr, nullptr, hp_row_offsets, hp_col_indices, XE,
+                                                   sumxf, scale_u4, zero_u4, scale_x, Y, T, K, N, nnz, flags, workspace,
+                                                   workspace_bytes, stream);
+}
+
+int w4a4_fused_dense_sparse_expanded_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
+                                              const void* W_high_prepared, const int32_t* hp_row_offsets,
+                                              const int32_t* hp_col_indices, const void* XE, const float* sumxf,
+                                              const void* scale_u4, const void* zero_u4, const void* scale_x,
+                                              void* Y, int T, int K, int N, int nnz, int flags, void* workspace,
+                                              size_t workspace_bytes, void* stream) {
   CHECK_ARG(Y && zero_u4 && XE && sumxf && scale_x, "NULL tensor pointer");
   GemmArgs a{};
+  a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
+  a.do_dense = true; a.nnz = nnz; a.sparse_weight = 16.f;
+  // prepared weights go with e4m3 expanded codes, and only the tensor-core kernel reads either
+  a.xe_fmt = has_prepared(a) ? W4A4_CODES_E4M3 : W4A4_CODES_S8;
+  if (!has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.XE = XE; a.sumxf = sumxf; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.scale_x = scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;

@@ -259,12 +259,13 @@ def fused_dense_sparse_cuda_int4(
     return Y
 
 
-def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor):
+def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor, *, e4m3: bool = False):
     """Quantised activations in the layout the GEMM kernels read: returns
     ``(XE, sumxf)`` - an opaque int8 buffer of expanded codes (group-major, see
     include/w4a4_b200.h) and ``(ceil(T/16), K/128, 16)`` fp32 group sums.  Build once
     and reuse across the linears that share an input (no counterpart in the
-    reference)."""
+    reference).  ``e4m3=True`` writes the codes as e4m3 bytes, the form that goes
+    with weights from :func:`prepare_weights_cuda`."""
     assert X_s4.is_cuda and X_s4.dtype == torch.int8 and sum_X.dtype == torch.int32
     T, K = int(X_s4.shape[0]), int(X_s4.shape[1]) * 2
     X = X_s4.contiguous()
@@ -272,18 +273,20 @@ def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor):
     XE = torch.empty((int(_L.w4a4_expanded_codes_bytes(T, K)),), dtype=torch.int8, device=X.device)
     sumxf = torch.zeros(((T + 15) // 16, K // BCOL, 16), dtype=torch.float32, device=X.device)
     with torch.cuda.device(X.device):
-        _lib.check(_L.w4a4_expand_activations(X.data_ptr(), sm.data_ptr(), XE.data_ptr(), sumxf.data_ptr(),
-                                              T, K, _lib.stream_ptr(X.device)), "expand_activations")
+        _lib.check(_L.w4a4_expand_activations_fmt(X.data_ptr(), sm.data_ptr(), XE.data_ptr(), sumxf.data_ptr(),
+                                                  T, K, 1 if e4m3 else 0, _lib.stream_ptr(X.device)),
+                   "expand_activations")
     return XE, sumxf
 
 
 def fused_dense_sparse_expanded_cuda(
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
     XE, sumxf, scale_u4, zero_u4, scale_x, d_out, d_in,
-    *, token_major: bool = False, force: Optional[str] = None,
+    *, token_major: bool = False, force: Optional[str] = None, prepared=None,
 ) -> torch.Tensor:
     """:func:`fused_dense_sparse_cuda_int4` on activations already expanded by
-    :func:`expand_activations_cuda`; a single kernel launch."""
+    :func:`expand_activations_cuda`; a single kernel launch.  With ``prepared`` weights
+    ``XE`` must have been expanded with ``e4m3=True``."""
     d_out, d_in = int(d_out), int(d_in)
     T = int(scale_x.shape[0])
     assert XE.is_cuda and XE.dtype == torch.int8 and XE.is_contiguous()
@@ -301,8 +304,9 @@ def fused_dense_sparse_expanded_cuda(
     Y = _out(d_out, T, W.device, token_major)
     with torch.cuda.device(W.device):
         ws = _lib.workspace(W.device, T, d_in, d_out, nnz)
-        _lib.check(_L.w4a4_fused_dense_sparse_expanded(
-            W.data_ptr(), Wh.data_ptr() if nnz else None, ro.data_ptr(), ci.data_ptr() if nnz else None,
+        plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
+        _lib.check(_L.w4a4_fused_dense_sparse_expanded_prepared(
+            W.data_ptr(), Wh.data_ptr() if nnz else None, plo, phi, ro.data_ptr(), ci.data_ptr() if nnz else None,
             XE.data_ptr(), sumxf.data_ptr(), s.data_ptr(), z.data_ptr(), sx.data_ptr(), Y.data_ptr(),
             T, d_in, d_out, nnz, _flags(token_major, force), ws.data_ptr(), ws.numel(),
             _lib.stream_ptr(W.device)), "fused_dense_sparse_expanded")

@@ -19,7 +19,7 @@ Layout facts the kernels rely on:
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, Tuple
+from typing import Dict, Optional, Tuple
 
 import torch
 
@@ -68,6 +68,9 @@ class V9WeightContainer:
     block_shape: Tuple[int, int]
     d_out: int
     d_in: int
+    # optional (W_low, W_high) widened once for the many-token kernel (``prepare_for_prefill``); not part
+    # of the reference's container and never serialised: a copy made by ``to`` starts without it
+    prepared: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
 
     @property
     def n_hp_blocks(self) -> int:

@@ -29,8 +29,19 @@ def _forward(X_fp16: torch.Tensor, W: V9WeightContainer, force=None) -> torch.Te
     X_2d = X_fp16.reshape(-1, d_in)
     Y = ops.fused_dense_sparse_e2e_cuda(
         X_2d, W.perm, W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
-        W.hp_col_indices, W.scale_u4, W.zero_u4, d_out, d_in, token_major=True, force=force)
+        W.hp_col_indices, W.scale_u4, W.zero_u4, d_out, d_in, token_major=True, force=force,
+        prepared=W.prepared)
     return Y.reshape(X_fp16.shape[:-1] + (d_out,))
+
+
+def prepare_for_prefill(W: V9WeightContainer) -> V9WeightContainer:
+    """Widen the container's packed weights once (2 x their bytes, kept next to them) so that
+    many-token calls run the fp8 instantiation of the tensor-core kernel; few-token calls keep
+    streaming the packed arrays.  Outputs are bit-identical either way.  A load-time step with no
+    counterpart in the reference's forward; returns ``W``."""
+    assert W.W_low_packed.is_cuda, "prepare the container after moving it to the GPU"
+    W.prepared = (ops.prepare_weights_cuda(W.W_low_packed), ops.prepare_weights_cuda(W.W_high_blocks_packed))
+    return W
 
 
 def v9_linear_forward(X_fp16: torch.Tensor, W: V9WeightContainer) -> torch.Tensor:

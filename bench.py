@@ -296,6 +296,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="decode")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--prepared", default="auto", choices=["auto", "on", "off"],
+                    help="many-token workloads: also hold the weights widened once to e4m3 bytes "
+                         "(prepare_for_prefill, 2x the packed bytes) so the tensor-core kernel runs its "
+                         "fp8 instantiation; auto = on when every M >= 256")
     args = ap.parse_args()
     items = workload_items(args.workload) if args.workload != "cfg3_sharded" else []
     args.workload_desc = {
@@ -338,6 +342,13 @@ def main():
     w_bytes = sum(k * n // 2 for _, k, n in {(i[2], i[3]): (0, i[2], i[3]) for i in items}.values())
     n_sets = max(2, -(-2 * L2_BYTES // max(w_bytes, 1)) + 1)
     data = build_inputs(items, device, n_sets)
+    many_tokens = min(i[1] for i in items) >= 256
+    if args.prepared == "on" and not many_tokens:
+        raise SystemExit("--prepared on needs a workload whose linears all take the tensor-core kernel (M >= 256)")
+    use_prepared = many_tokens and args.prepared != "off"
+    if use_prepared:
+        for W in {id(W): W for it in data for W in it["W"]}.values():
+            v9_linear.prepare_for_prefill(W)
     for it in data:
         it["X_dev"] = it["X_host"].to(device)
         it["Y_host"] = torch.empty((it["M"], it["N"]), dtype=torch.float16).pin_memory()
@@ -348,7 +359,7 @@ def main():
             W = it["W"][r]
             it["Y"] = ops.fused_dense_sparse_e2e_cuda(
                 it["X_dev"], W.perm, W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
-                W.hp_col_indices, W.scale_u4, W.zero_u4, W.d_out, W.d_in, token_major=True)
+                W.hp_col_indices, W.scale_u4, W.zero_u4, W.d_out, W.d_in, token_major=True, prepared=W.prepared)
 
     def gemm_only_step(r):
         for it in data:
@@ -356,7 +367,8 @@ def main():
             q = it["q"]
             ops.fused_dense_sparse_expanded_cuda(W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
                                                  W.hp_col_indices, it["XE"], it["sumxf"], W.scale_u4,
-                                                 W.zero_u4, q[1], W.d_out, W.d_in, token_major=True)
+                                                 W.zero_u4, q[1], W.d_out, W.d_in, token_major=True,
+                                                 prepared=W.prepared)
 
     def e2e_step(r):
         # public host-staged call: pinned activations in, pinned results out.  The twelve linears of a
@@ -370,7 +382,7 @@ def main():
     # eager warm-up (also sizes every workspace before capture)
     for it in data:
         it["q"] = ops.activation_quant_cuda(it["X_dev"], it["W"][0].perm)
-        it["XE"], it["sumxf"] = ops.expand_activations_cuda(it["q"][0], it["q"][2])
+        it["XE"], it["sumxf"] = ops.expand_activations_cuda(it["q"][0], it["q"][2], e4m3=use_prepared)
     for r in range(n_sets):
         device_step(r)
         gemm_only_step(r)
@@ -453,7 +465,9 @@ def main():
         "data": "synthetic",
         "config": {"workload": args.workload_desc, "linears_per_step": len(data),
                    "l2": f"weights rotate through {n_sets} distinct copies (> 2x L2)",
-                   "step": "CUDA-graph replay of quant+GEMM per linear", "parallelism": f"replicated x{world}"},
+                   "step": "CUDA-graph replay of quant+GEMM per linear", "parallelism": f"replicated x{world}",
+                   "weights": ("packed nibbles + copy widened once to e4m3 bytes (opt-in prepare_for_prefill); "
+                               "MMA kind::f8f6f4, bit-identical outputs") if use_prepared else "packed nibbles"},
         "us_per_linear": ms_dev / args.steps / len(data) * 1e3,
         "e2e": {"value": e2e_val, "unit": "TOPS",
                 "h2d_bytes_per_step": sum(it["X_host"].numel() * 2 for it in data),

@@ -30,7 +30,7 @@ import torch.nn.functional as F
 
 from . import synth
 from .pack_utils import V9WeightContainer
-from .v9_linear import v9_linear_forward
+from .v9_linear import prepare_for_prefill, v9_linear_forward
 
 
 @dataclass
@@ -51,9 +51,14 @@ class StackConfig:
 
 
 class Layer:
-    def __init__(self, cfg: StackConfig, protos, device):
+    def __init__(self, cfg: StackConfig, protos, device, prepared: bool):
         # distinct device copies per layer: a layer never finds its weights in L2 because another layer left them there
         self.qkv, self.o, self.gate_up, self.down = (p.to(device) for p in protos)
+        if prepared:
+            # prompt processing runs the fp8 instantiation of the tensor-core kernel on weights widened once
+            # (2 x the packed bytes on top); decode steps keep streaming the packed arrays
+            for W in (self.qkv, self.o, self.gate_up, self.down):
+                prepare_for_prefill(W)
         self.norm1 = torch.ones(cfg.hidden, dtype=torch.float16, device=device)
         self.norm2 = torch.ones(cfg.hidden, dtype=torch.float16, device=device)
 
@@ -81,7 +86,7 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 class DecoderStack:
     """Weights, KV cache and the two phases (prefill of a prompt batch, one decode step)."""
 
-    def __init__(self, cfg: StackConfig, batch: int, max_len: int, device, seed: int = 0):
+    def __init__(self, cfg: StackConfig, batch: int, max_len: int, device, seed: int = 0, prepared: bool = True):
         self.cfg, self.batch, self.max_len, self.device = cfg, batch, max_len, device
         h, kv = cfg.hidden, cfg.n_kv_heads * cfg.head_dim
         shapes = [(h, h + 2 * kv), (h, h), (h, 2 * cfg.ffn), (cfg.ffn, h)]             # (d_in, d_out)
@@ -92,7 +97,7 @@ class DecoderStack:
             # standard deviation ~0.15 * sqrt(K) for unit inputs; bring every projection to ~0.5 so that
             # the residual stream of a deep random stack stays inside fp16
             W.scale_u4 = (W.scale_u4.float() * (0.5 / (0.15 * math.sqrt(W.d_in)))).to(torch.float16)
-        self.layers = [Layer(cfg, protos, device) for _ in range(cfg.n_layers)]
+        self.layers = [Layer(cfg, protos, device, prepared) for _ in range(cfg.n_layers)]
         g = torch.Generator().manual_seed(seed + 1)
         self.embed = (torch.randn(cfg.vocab, h, generator=g) * 0.02).to(torch.float16).to(device)
         self.lm_head = (torch.randn(cfg.vocab, h, generator=g) * 0.02).to(torch.float16).to(device)
@@ -151,9 +156,10 @@ class DecoderStack:
         return logits.argmax(-1)
 
 
-def run(cfg: StackConfig, batch: int, prefill_len: int, decode_steps: int, device, use_graph: bool = True, seed: int = 0):
+def run(cfg: StackConfig, batch: int, prefill_len: int, decode_steps: int, device, use_graph: bool = True, seed: int = 0,
+        prepared: bool = True):
     max_len = prefill_len + decode_steps
-    stack = DecoderStack(cfg, batch, max_len, device, seed)
+    stack = DecoderStack(cfg, batch, max_len, device, seed, prepared)
     g = torch.Generator().manual_seed(seed + 2)
     prompt = torch.randint(0, cfg.vocab, (batch, prefill_len), generator=g).to(device)
 
@@ -199,7 +205,8 @@ def run(cfg: StackConfig, batch: int, prefill_len: int, decode_steps: int, devic
         "config": {"layers": cfg.n_layers, "hidden": cfg.hidden, "heads": f"{cfg.n_heads}/{cfg.n_kv_heads}", "ffn": cfg.ffn,
                    "vocab": cfg.vocab, "batch": batch, "prefill": prefill_len, "decode_steps": decode_steps,
                    "w4a4_linears_per_layer": "qkv, o, gate_up, down (7 projections)", "residual_density": cfg.density,
-                   "decode_step": "CUDA graph" if use_graph else "eager"},
+                   "decode_step": "CUDA graph" if use_graph else "eager",
+                   "prefill_weights": "prepared e4m3 copy" if prepared else "packed"},
         "last_tokens": [int(t) for t in produced[-1][:4].tolist()],
     }
 
@@ -211,10 +218,12 @@ def main():
     ap.add_argument("--prefill", type=int, default=1024)
     ap.add_argument("--decode", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-prepared", action="store_true", help="prompt processing on the packed weights")
     a = ap.parse_args()
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
-    res = run(StackConfig(n_layers=a.layers), a.batch, a.prefill, a.decode, device, use_graph=not a.no_graph)
+    res = run(StackConfig(n_layers=a.layers), a.batch, a.prefill, a.decode, device, use_graph=not a.no_graph,
+              prepared=not a.no_prepared)
     print(json.dumps(res), flush=True)
 
 

@@ -41,7 +41,8 @@ L2_BYTES = 126 * 1024 * 1024
 NCU_TRAFFIC_BYTES = {
     "decode": 30.49e6,            # profiles/decode_gemm_kernel_dram_traffic.md
     "gate_up_m16": 65.82e6,       # profiles/decode_gemm_kernel_gate_up_m16.md
-    "prefill_gate_up": 303.6e6,   # profiles/prefill_gemm_kernel_gate_up_m2048.md
+    "prefill_gate_up": 225.9e6,   # profiles/prefill_gemm_kernel_gate_up_m2048.md (prepared weights)
+    "prefill_gate_up/packed": 153.2e6,
 }
 
 
@@ -140,14 +141,15 @@ def build_inputs(items, device, n_sets):
     return out
 
 
-def alg_bytes_gemm(it):
-    """Bytes one GEMM launch must move: weights, scales/zeros, residual blocks and
-    index, expanded activation codes (one byte each) with their scales and group
-    sums, output."""
+def alg_bytes_gemm(it, prepared=False):
+    """Bytes one GEMM launch must move: weights (half a byte per code packed, one byte
+    prepared), scales/zeros, residual blocks and index, expanded activation codes (one
+    byte each) with their scales and group sums, output."""
     M, K, N = it["M"], it["K"], it["N"]
     nnz = it["W"][0].n_hp_blocks
     ng, nbr = K // 128, (N + 127) // 128
-    b_w = K * N // 2 + 4 * N * ng + 8192 * nnz + 4 * (nbr + 1) + 4 * nnz
+    wb = 2 if prepared else 1
+    b_w = wb * K * N // 2 + 4 * N * ng + wb * 8192 * nnz + 4 * (nbr + 1) + 4 * nnz
     return b_w + (M * K + 2 * M + 4 * M * ng) + 2 * M * N
 
 
@@ -443,7 +445,7 @@ def main():
     dev_err = _lib.device_error(device)
 
     ops_step = sum(2 * it["M"] * it["K"] * it["N"] for it in data)
-    bytes_gemm = sum(alg_bytes_gemm(it) for it in data)
+    bytes_gemm = sum(alg_bytes_gemm(it, use_prepared) for it in data)
     gemm_s = ms_gemm / 1e3 / args.steps
     tensor_bound = min(it["M"] for it in data) >= 256
     if tensor_bound:
@@ -476,7 +478,8 @@ def main():
         "gpu_launches": args.steps * len(data) * 2,
         "roofline": {"bound": "tensor" if tensor_bound else "hbm", "achieved": achieved, "peak": peak,
                      "unit": "TOP/s" if tensor_bound else "GB/s",
-                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload), "peak_kind": peak_kind,
+                     "frac": achieved / peak, "traffic": NCU_TRAFFIC_BYTES.get(args.workload if (use_prepared or not many_tokens)
+                                                                else args.workload + "/packed"), "peak_kind": peak_kind,
                      "kernel": "prefill_gemm_kernel" if tensor_bound else "decode_gemm_kernel",
                      "us_per_launch": gemm_s / len(data) * 1e6,
                      "bytes_per_launch": bytes_gemm / len(data)},

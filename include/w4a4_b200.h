@@ -52,6 +52,7 @@ enum {
 #define W4A4_FLAG_OUT_TOKEN_MAJOR 0x1  /* write Y as (T, N) instead of (N, T)          */
 #define W4A4_FLAG_FORCE_STREAM    0x2  /* force the weight-streaming split-K kernel     */
 #define W4A4_FLAG_FORCE_TENSOR    0x4  /* force the tcgen05 tensor-core kernel          */
+#define W4A4_FLAG_CODES_E4M3      0x8  /* *_expanded entry points: XE holds e4m3 codes (w4a4_expand_activations_fmt) */
 
 int w4a4_abi_version(void);
 const char* w4a4_status_string(int status);
@@ -148,9 +149,8 @@ int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t*
  * where the reference has its adapter backend/weight_loader.py:111
  * pack_v9_weights_for_cutlass; no counterpart in its bindings):
  * w4a4_prepare_weights turns a packed array (W_low, or W_high) into one byte per
- * code - the e4m3 encoding of the code, exact for -8..7, each packed 32-bit word
- * becoming its four even-indexed codes followed by its four odd-indexed ones, row
- * shape kept - of w4a4_prepared_weights_bytes(packed_bytes) = 2 x packed_bytes
+ * code - the e4m3 encoding of the code, exact for -8..7, codes in their natural
+ * order, row shape kept - of w4a4_prepared_weights_bytes(packed_bytes) = 2 x packed_bytes
  * bytes.  The *_prepared entry points take the packed arrays AND the prepared ones:
  * calls that go to the tensor-core kernel then run e4m3 x e4m3 MMAs with fp32
  * accumulation on the prepared bytes (the products and sums are small integers,
@@ -172,11 +172,17 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
                                            const int32_t* hp_col_indices, const void* scale_u4,
                                            const void* zero_u4, void* Y, int T, int K, int N, int nnz,
                                            int flags, void* workspace, size_t workspace_bytes, void* stream);
-/* The same with activations expanded once for several linears: the expanded codes that go with
- * prepared weights are e4m3 bytes as well (code_format W4A4_CODES_E4M3; the layout is that of
- * w4a4_expand_activations, W4A4_CODES_S8 is what that function writes).  With prepared pointers
- * the call must be one the tensor-core kernel takes (many tokens, or W4A4_FLAG_FORCE_TENSOR):
- * the streaming kernel reads s8 codes and the call fails with W4A4_ERR_BAD_ARG otherwise. */
+/* The same with activations expanded once for several linears.  The tensor-core kernel runs fp8 MMAs on
+ * e4m3 codes - on prepared weights, and also on packed weights, whose nibbles it then turns into e4m3
+ * on the SM (slower than its integer MMAs on s8 codes, which stay the default for packed weights; same
+ * output bits).  w4a4_expand_activations_fmt with
+ * W4A4_CODES_E4M3 writes the e4m3 form (same group-major, chunk-swizzled layout; inside a packed word
+ * the codes keep their natural order instead of the even-then-odd order of the s8 form;
+ * W4A4_CODES_S8 is what w4a4_expand_activations writes).  Pass such a buffer to
+ * w4a4_fused_dense_sparse_expanded_prepared with W4A4_FLAG_CODES_E4M3 (prepared pointers may be
+ * NULL; non-NULL ones imply the flag).  The call must be one the tensor-core kernel takes (many tokens,
+ * or W4A4_FLAG_FORCE_TENSOR): the streaming kernel reads s8 codes and the call fails with
+ * W4A4_ERR_BAD_ARG otherwise. */
 #define W4A4_CODES_S8   0
 #define W4A4_CODES_E4M3 1
 int w4a4_expand_activations_fmt(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,

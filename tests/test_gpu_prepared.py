@@ -1,6 +1,7 @@
-"""Prepared weights: the many-token kernel on weights widened once to one e4m3 byte per
-code (tcgen05 kind::f8f6f4, fp32 accumulation) must give the packed path's accumulators
-and outputs bit for bit - the products and sums are small integers, exact in fp32."""
+"""The many-token kernel's three instantiations - integer MMAs on s8 codes, fp8 MMAs
+(tcgen05 kind::f8f6f4, fp32 accumulation) on packed weights turned into e4m3 on the SM, and fp8
+MMAs on weights prepared once as e4m3 bytes - must give the same accumulators and the same
+output bits: the products and sums are small integers, exact in fp32."""
 
 import numpy as np
 import pytest
@@ -21,13 +22,13 @@ def e4m3_of_codes(codes):
 
 
 def prepared_reference(packed):
-    """One byte per code; every packed 32-bit word (8 codes) becomes its even-indexed codes, then its odd-indexed ones."""
-    b = np.ascontiguousarray(packed).view(np.uint8).reshape(-1, 4)
+    """One e4m3 byte per code, codes in their natural order (byte b of the packed array holds codes 2b, 2b + 1)."""
+    b = np.ascontiguousarray(packed).view(np.uint8)
     lo = (b & 0xF).astype(np.int8)
     hi = (b >> 4).astype(np.int8)
     lo = np.where(lo >= 8, lo - 16, lo)
     hi = np.where(hi >= 8, hi - 16, hi)
-    out = np.concatenate([e4m3_of_codes(lo), e4m3_of_codes(hi)], axis=1)            # (words, 8)
+    out = np.stack([e4m3_of_codes(lo), e4m3_of_codes(hi)], axis=-1)                 # (..., bytes, 2)
     return out.reshape(packed.shape[:-1] + (packed.shape[-1] * 2,))
 
 
@@ -78,9 +79,14 @@ def test_prepared_outputs_equal_packed(ops, T, N, K, density):
     prep = prepare(ops, Wd)
     Xd = X.cuda()
     q = ops.activation_quant_cuda(Xd, Wd.perm)
-    Yp = fused(ops, Wd, q, force="tensor")
-    Yf = fused(ops, Wd, q, force="tensor", prepared=prep)
+    Yp = fused(ops, Wd, q, force="tensor")                       # packed weights, integer MMAs
+    Yf = fused(ops, Wd, q, force="tensor", prepared=prep)        # prepared weights, fp8 MMAs
     assert torch.equal(Yf, Yp)
+    XE8, sumxf8 = ops.expand_activations_cuda(q[0], q[2])        # the same through caller-expanded s8 codes
+    Yi = ops.fused_dense_sparse_expanded_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
+                                              Wd.hp_col_indices, XE8, sumxf8, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
+                                              force="tensor")
+    assert torch.equal(Yi, Yp)
     args = (Xd, Wd.perm, Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices,
             Wd.scale_u4, Wd.zero_u4, N, K)
     Ye = ops.fused_dense_sparse_e2e_cuda(*args, force="tensor", prepared=prep)
@@ -92,6 +98,10 @@ def test_prepared_outputs_equal_packed(ops, T, N, K, density):
                                               Wd.hp_col_indices, XE, sumxf, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
                                               force="tensor", prepared=prep)
     assert torch.equal(Yx, Yp)
+    Yx2 = ops.fused_dense_sparse_expanded_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
+                                               Wd.hp_col_indices, XE, sumxf, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
+                                               force="tensor", e4m3=True)   # packed weights, fp8 MMAs
+    assert torch.equal(Yx2, Yp)
     if T <= 512:
         xs4, sx, sumx = (np_(t) for t in q)
         assert_close_fp16(np_(Yf), oracle_fused(container_np(W), xs4, sumx, sx), "prepared vs oracle")

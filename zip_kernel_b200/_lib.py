@@ -51,6 +51,7 @@ SIGNATURES = {
 FLAG_OUT_TOKEN_MAJOR = 0x1
 FLAG_FORCE_STREAM = 0x2
 FLAG_FORCE_TENSOR = 0x4
+FLAG_CODES_E4M3 = 0x8
 
 _lib = None
 

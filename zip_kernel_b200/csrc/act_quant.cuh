@@ -42,15 +42,19 @@ struct QuantParams {
   int vec_ok;             // 1 when every row start is 16-byte aligned
   int C;                  // CTAs (cluster size) per token; divides K/128
   int stage_row;          // 1: perm given and the dynamic shared memory holds the whole raw row behind the slice
-  int fmt;                // bytes of XE: 0 = s8 codes, 1 = e4m3 encodings of the codes (fp8 tensor-core path)
+  int fmt;                // bytes of XE: 0 = s8 codes (even/odd order), 1 = e4m3 encodings in natural order (see expand_word)
 };
 
-// One packed word (8 codes) -> 8 bytes: its four even-indexed codes, then its four odd-indexed ones;
-// fmt 0: sign-extended s8, fmt 1: e4m3.
+// One packed word (8 codes) -> 8 bytes.  fmt 0: sign-extended s8, its four even-indexed codes, then its
+// four odd-indexed ones (the order the s8 widening of the weights produces).  fmt 1: e4m3 encodings in the
+// codes' natural order (the order of the weights' table look-up and of prepared weights).
 __device__ __forceinline__ uint2 expand_word(uint32_t w, int fmt = 0) {
-  uint2 r = make_uint2(nib_lo_s8(w), nib_hi_s8(w));
-  if (fmt == 1) r = make_uint2(s8x4_to_e4m3x4(r.x), s8x4_to_e4m3x4(r.y));
-  return r;
+  if (fmt == 1) {
+    uint2 r;
+    nib8_to_e4m3(w, r.x, r.y);
+    return r;
+  }
+  return make_uint2(nib_lo_s8(w), nib_hi_s8(w));
 }
 
 // Expanded activation layout ("XE") read by both GEMM kernels: one byte per code,
@@ -268,8 +272,8 @@ __global__ void __launch_bounds__(256) expand_activations_kernel(const ExpandPar
 }
 
 // Weights prepared for the fp8 tensor-core path: every packed word of nibbles (dense rows or residual
-// blocks alike) becomes its 8 codes as e4m3 bytes in the same even-then-odd order as the activations,
-// so a row of K codes is K bytes and the row-major shape is kept.
+// blocks alike) becomes its 8 codes as e4m3 bytes in their natural order, so a row of K codes is K bytes
+// and the row-major shape is kept.
 __global__ void __launch_bounds__(256) prepare_weights_kernel(const uint32_t* packed, uint2* out, long long words) {
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride)

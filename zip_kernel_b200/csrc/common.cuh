@@ -220,18 +220,29 @@ __device__ __forceinline__ uint32_t sext4_bytes(uint32_t x) {
 }
 __device__ __forceinline__ uint32_t nib_lo_s8(uint32_t w) { return sext4_bytes(w & 0x0F0F0F0Fu); }
 __device__ __forceinline__ uint32_t nib_hi_s8(uint32_t w) { return sext4_bytes((w >> 4) & 0x0F0F0F0Fu); }
-// Four s8 values in [-8, 7] -> their e4m3 encodings (exact: |v| <= 8 needs at most 3 mantissa bits).
-// Two 8-entry byte tables looked up with prmt (index = value & 7), merged by the sign byte mask.
-__device__ __forceinline__ uint32_t s8x4_to_e4m3x4(uint32_t x) {
-  const uint32_t y = x & 0x07070707u;
-  const uint32_t sel = (y & 0x7u) | ((y >> 4) & 0x70u) | ((y >> 8) & 0x700u) | ((y >> 12) & 0x7000u);
-  uint32_t pos, neg, mask;
-  //            v = 0     1     2     3            4     5     6     7
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(pos) : "r"(0x44403800u), "r"(0x4E4C4A48u), "r"(sel));
-  //            v = -8    -7    -6    -5           -4    -3    -2    -1
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(neg) : "r"(0xCACCCED0u), "r"(0xB8C0C4C8u), "r"(sel));
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(mask) : "r"(x), "r"(0u), "r"(0xBA98u));   // 0xFF where the byte is negative
-  return (pos & ~mask) | (neg & mask);
+// One packed word (8 two's-complement nibbles) -> the e4m3 encodings of its 8 codes in their natural
+// order: `first` = codes 0..3, `second` = codes 4..7.  prmt reads a selector's four low nibbles as
+// byte indices into an 8-byte table - the packed nibbles ARE such indices: a nibble 0..7 picks the table
+// byte, a nibble 8..15 (a negative code) selects "replicate the sign bit of table[nibble & 7]" and gives
+// 0x00 for a table byte below 0x80.  Two look-ups per four codes: non-negative codes in the table of
+// their encodings (negatives read 0x00); with bit 3 of every nibble flipped, negative codes in the table
+// of their COMPLEMENTED encodings (which are below 0x80, so non-negatives read 0x00); a third prmt makes
+// the 0xFF-where-negative mask that undoes the complement.  12 logic / permute operations per 8 codes.
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+  uint32_t r;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+  return r;
+}
+__device__ __forceinline__ void nib8_to_e4m3(uint32_t w, uint32_t& first, uint32_t& second) {
+  //            code = 0     1     2     3            4     5     6     7
+  constexpr uint32_t POS_LO = 0x44403800u, POS_HI = 0x4E4C4A48u;
+  //          ~e4m3 of -8    -7    -6    -5           -4    -3    -2    -1      (e4m3: D0 CE CC CA  C8 C4 C0 B8)
+  constexpr uint32_t NEGC_LO = 0x3533312Fu, NEGC_HI = 0x473F3B37u;
+  const uint32_t t = w ^ 0x88888888u, b = w << 4;
+  // sign bits of codes 0..3 are bits 3, 7, 11, 15 of w = the top bits of b.byte0, w.byte0, b.byte1, w.byte1
+  const uint32_t m0 = prmt_b32(w, b, 0x9D8Cu), m1 = prmt_b32(w, b, 0xBFAEu);
+  first = prmt_b32(POS_LO, POS_HI, w) ^ prmt_b32(NEGC_LO, NEGC_HI, t) ^ m0;
+  second = prmt_b32(POS_LO, POS_HI, w >> 16) ^ prmt_b32(NEGC_LO, NEGC_HI, t >> 16) ^ m1;
 }
 
 // ---------------------------------------------------------------- legacy int8 MMA (decode path)

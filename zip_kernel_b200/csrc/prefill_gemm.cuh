@@ -65,11 +65,11 @@ constexpr int TMEM_COLS = 512;                    // the whole tensor memory of 
 // Tensor-memory columns.  Accumulator buffers first (the MMAs run that many steps ahead of the fold), then
 // the widened weight tiles (packed weights only), then the fp32 accumulator of the zero-point term.
 // Prepared weights leave room for a third accumulator buffer.
-template <bool F8>
+template <bool PREP>
 struct TmemLayout {
-  static constexpr int ACC_BUFS = F8 ? 3 : 2;
+  static constexpr int ACC_BUFS = PREP ? 3 : 2;
   static constexpr int A_COL0 = ACC_BUFS * TN;
-  static constexpr int Z_COL0 = A_COL0 + (F8 ? 0 : A_BUFS * A_COLS);
+  static constexpr int Z_COL0 = A_COL0 + (PREP ? 0 : A_BUFS * A_COLS);
   static_assert(Z_COL0 + TN <= TMEM_COLS, "tensor memory capacity");
 };
 constexpr int ZT_BYTES = ROWS * 128;              // one tf32 operand tile of the zero-point term: 128 rows x 32 values
@@ -112,16 +112,19 @@ struct Params {
 
 inline bool supported(int T, int K, int N) { return T >= 1 && K >= 128 && N >= 1; }
 
-// Geometry of the two instantiations.  F8 = false: packed nibbles are copied in (8 KB per step) and
-// widened on the SM.  F8 = true: the caller supplies weights prepared as e4m3 bytes (16 KB per step, the
-// A operand as it is), activations are e4m3 too, the MMA is kind::f8f6f4 with fp32 accumulators - the
-// same integers, as floats - and neither the unpack warps nor the int -> float conversion have work.
-template <bool F8>
+// Three instantiations.  <F8 = false, PREP = false>: packed nibbles are copied in (8 KB per step), widened to
+// s8 on the SM, integer MMAs (kind::i8) - for activation codes the caller expanded as s8.  <F8 = true, PREP =
+// false>: the same packed copies, but the unpack warps turn every nibble into its e4m3 encoding (exact for
+// -8..7) with byte-permute table look-ups, the activation codes are e4m3 bytes too and the MMA is
+// kind::f8f6f4 with fp32 accumulators - the same integers, as floats - so the fold needs no int -> float
+// conversion.  <F8 = true, PREP = true>: the caller supplies weights prepared once as e4m3 bytes (16 KB per
+// step, the A operand as it lands): no unpack work either.
+template <bool PREP>
 struct SmemLayout {
-  static constexpr int W_STAGES = F8 ? 5 : 6;               // weight tiles in flight
-  static constexpr int X_STAGES = F8 ? 5 : 6;               // activation tiles in flight = depth of the "ready" / "step done" rings
-  static constexpr int WP_BYTES = F8 ? ROWS * BCOL : ROWS * GROUP_BYTES;
-  static_assert(!F8 || W_STAGES == X_STAGES, "with prepared weights both copies of a step share a ring slot index");
+  static constexpr int W_STAGES = PREP ? 5 : 6;               // weight tiles in flight
+  static constexpr int X_STAGES = PREP ? 5 : 6;               // activation tiles in flight = depth of the "ready" / "step done" rings
+  static constexpr int WP_BYTES = PREP ? ROWS * BCOL : ROWS * GROUP_BYTES;
+  static_assert(!PREP || W_STAGES == X_STAGES, "with prepared weights both copies of a step share a ring slot index");
     static constexpr size_t wp = 0;
   static constexpr size_t x = wp + (size_t)W_STAGES * WP_BYTES;
   static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float [SZ_CHUNK][128]: scale (/16 for int8 accumulators)
@@ -164,6 +167,14 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC_F8), "r"(accumulate)
+      : "memory");
+}
+// the same with the A operand in tensor memory (row = lane, four e4m3 bytes per 32-bit column)
+__device__ __forceinline__ void umma_f8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(IDESC_F8), "r"(accumulate)
       : "memory");
 }
 // kind::tf32, tf32 x tf32 -> f32, both operands K-major, M = 128, N = TN (K = 8 per instruction)
@@ -229,13 +240,14 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   return d;
 }
 
-template <bool DUMP, bool F8>
+template <bool DUMP, bool F8, bool PREP>
 __global__ void __launch_bounds__(THREADS, 1)
 prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wh,
                     const Params p) {
-  using SmemLayout = pre::SmemLayout<F8>;
+  static_assert(F8 || !PREP, "prepared weights are e4m3 bytes");
+  using SmemLayout = pre::SmemLayout<PREP>;
   constexpr int W_STAGES = SmemLayout::W_STAGES, X_STAGES = SmemLayout::X_STAGES, WP_BYTES = SmemLayout::WP_BYTES;
-  constexpr int ACC_BUFS = TmemLayout<F8>::ACC_BUFS, A_COL0 = TmemLayout<F8>::A_COL0, Z_COL0 = TmemLayout<F8>::Z_COL0;
+  constexpr int ACC_BUFS = TmemLayout<PREP>::ACC_BUFS, A_COL0 = TmemLayout<PREP>::A_COL0, Z_COL0 = TmemLayout<PREP>::Z_COL0;
   static_assert(ACC_BUFS < X_STAGES, "the fold warps' arrival for step n + ACC_BUFS must fall into that step's barrier phase");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -276,7 +288,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   if (tid == 0) {
     for (int i = 0; i < W_STAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], N_UNPACK_WARPS); }
     // arrivals per step: the activation copy, then either the four unpack warps or the weight copy, then the fold warps
-    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&ready[i], (F8 ? 2 : 1 + N_UNPACK_WARPS) + N_FOLD_WARPS); mbar_init(&done[i], 1); }
+    for (int i = 0; i < X_STAGES; ++i) { mbar_init(&ready[i], (PREP ? 2 : 1 + N_UNPACK_WARPS) + N_FOLD_WARPS); mbar_init(&done[i], 1); }
     mbar_init(z_full, N_FOLD_WARPS);
     mbar_init(z_done, 1);
     mbar_fence_init();
@@ -306,9 +318,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       const int n_pre = min(W_STAGES, n_steps);
       auto issue_w = [&](int n, int st) {
         // prepared weights are the A operand as it is: the copy reports to the step's readiness barrier
-        uint64_t* bar = F8 ? &ready[st] : &w_full[st];
+        uint64_t* bar = PREP ? &ready[st] : &w_full[st];
         mbar_arrive_expect_tx(bar, WP_BYTES);
-        if (n < p.nd) tma_load_2d(wp_ring + st * WP_BYTES, &tm_w, n * (F8 ? BCOL : GROUP_BYTES), row0, bar);
+        if (n < p.nd) tma_load_2d(wp_ring + st * WP_BYTES, &tm_w, n * (PREP ? BCOL : GROUP_BYTES), row0, bar);
         else          tma_load_2d(wp_ring + st * WP_BYTES, &tm_wh, 0, (b_lo + n - p.nd) * BROW, bar);
       };
       for (int n = 0; n < n_pre; ++n) issue_w(n, n);
@@ -318,7 +330,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int n = 0; n < n_steps && ok; ++n) {
         if (n >= n_pre) {
           // packed tiles are released by the unpack warps, prepared tiles by the completion of the MMAs that read them
-          ok = F8 ? mbar_wait_relaxed(&done[ws], ((n - W_STAGES) / W_STAGES) & 1, SITE_PRE_WEMPTY)
+          ok = PREP ? mbar_wait_relaxed(&done[ws], ((n - W_STAGES) / W_STAGES) & 1, SITE_PRE_WEMPTY)
                   : mbar_wait_relaxed(&w_empty[ws], wph, SITE_PRE_WEMPTY);
           if (!ok) break;
           issue_w(n, ws);
@@ -372,14 +384,19 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         tc_fence_after();
         const uint64_t bdesc = bdesc0 + (uint64_t)(xs * (X_BYTES >> 4));
         const uint32_t d = d0 + buf * TN, a = a0 + ab * A_COLS;
-        if (F8) {
+        if (PREP) {
           const uint64_t adesc = adesc0 + (uint64_t)(xs * (WP_BYTES >> 4));
           umma_f8(d, adesc, bdesc, 0);                 // K = 32 each: 32 bytes of A and of B
           umma_f8(d, adesc + 2, bdesc + 2, 1);
           umma_f8(d, adesc + 4, bdesc + 4, 1);
           umma_f8(d, adesc + 6, bdesc + 6, 1);
+        } else if (F8) {
+          umma_f8_ta(d, a, bdesc, 0);                  // K = 32 each: 8 columns of A, 32 bytes of B
+          umma_f8_ta(d, a + 8, bdesc + 2, 1);
+          umma_f8_ta(d, a + 16, bdesc + 4, 1);
+          umma_f8_ta(d, a + 24, bdesc + 6, 1);
         } else {
-          umma_i8_ta(d, a, bdesc, 0);                  // K = 32 each: 8 columns of A, 32 bytes of B
+          umma_i8_ta(d, a, bdesc, 0);
           umma_i8_ta(d, a + 8, bdesc + 2, 1);
           umma_i8_ta(d, a + 16, bdesc + 4, 1);
           umma_i8_ta(d, a + 24, bdesc + 6, 1);
@@ -400,7 +417,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     bool ok = true;
     int ws = 0;
     uint32_t wph = 0;
-    for (int n = 0; n < (F8 ? 0 : n_steps); ++n) {       // prepared weights need no widening
+    for (int n = 0; n < (PREP ? 0 : n_steps); ++n) {     // prepared weights need no widening
       const int buf = n % A_BUFS;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&w_full[ws], wph, SITE_PRE_WFULL));
       // the A buffer was last read by the MMAs of step n - 2
@@ -419,8 +436,12 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const uint32_t q[4] = {w[c].x, w[c].y, w[c].z, w[c].w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            v[(c * 4 + e) * 2] = nib_lo_x16(q[e]);
-            v[(c * 4 + e) * 2 + 1] = nib_hi_x16(q[e]);
+            if (F8) {
+              nib8_to_e4m3(q[e], v[(c * 4 + e) * 2], v[(c * 4 + e) * 2 + 1]);      // codes in their natural order
+            } else {
+              v[(c * 4 + e) * 2] = nib_lo_x16(q[e]);                                  // even codes, then odd ones
+              v[(c * 4 + e) * 2 + 1] = nib_hi_x16(q[e]);
+            }
           }
         }
         tmem_st32(a_lane + buf * A_COLS, v);

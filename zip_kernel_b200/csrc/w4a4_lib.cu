@@ -309,11 +309,18 @@ bool has_prepared(const GemmArgs& a) {
 int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   using namespace w4a4;
   GemmArgs a = a_in;
-  const bool f8 = has_prepared(a);
+  const bool prep = has_prepared(a);
+  // Prepared weights exist only as e4m3 and take fp8 MMAs.  Packed weights take integer MMAs on s8 codes:
+  // turning nibbles into e4m3 on the SM (12 permute / logic operations per 8 codes) is slower than widening
+  // them to s8 (3 per 8 codes) plus the int -> float conversion in the fold (measured: gate_up M=8192 3027
+  // against 2430 us).  That instantiation runs when the caller hands in e4m3 codes without prepared weights,
+  // or with W4A4_PREFILL_F8=1 (A/B runs).
+  static const bool env_f8 = getenv("W4A4_PREFILL_F8") && atoi(getenv("W4A4_PREFILL_F8")) != 0;
+  const bool f8 = a.XE != nullptr ? a.xe_fmt == 1 : (prep || env_f8);
   const bool dump = a.acc_dump || a.acc_hi_dump;
   const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
-  if (a.XE != nullptr && (a.xe_fmt == 1) != f8)
-    return fail(W4A4_ERR_BAD_ARG, "expanded activations and weights are in different formats");
+  if (prep && !f8)
+    return fail(W4A4_ERR_BAD_ARG, "prepared weights need activation codes expanded as e4m3 (W4A4_FLAG_CODES_E4M3)");
   a.xe_fmt = f8 ? 1 : 0;
   if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
   const int ng = a.K / BCOL;
@@ -339,11 +346,11 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   // the operand that is switched off borrows the other one's map and is never read.  Packed rows hold
   // two codes per byte and land under the 64-byte swizzle the unpack warps read; prepared rows hold one
   // code per byte and land under the 128-byte swizzle of an MMA operand tile.
-  const void* w_lo = f8 ? a.W_low_prep : a.W_low;
-  const void* w_hi = f8 ? a.W_high_prep : a.W_high;
-  const uint64_t lo_row = f8 ? (uint64_t)a.K : (uint64_t)a.K / 2, hi_row = f8 ? BCOL : GROUP_BYTES;
-  const uint32_t box = f8 ? BCOL : GROUP_BYTES;
-  const CUtensorMapSwizzle swz = f8 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  const void* w_lo = prep ? a.W_low_prep : a.W_low;
+  const void* w_hi = prep ? a.W_high_prep : a.W_high;
+  const uint64_t lo_row = prep ? (uint64_t)a.K : (uint64_t)a.K / 2, hi_row = prep ? BCOL : GROUP_BYTES;
+  const uint32_t box = prep ? BCOL : GROUP_BYTES;
+  const CUtensorMapSwizzle swz = prep ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   int rc = make_map(&tm_w, a.do_dense ? w_lo : w_hi, a.do_dense ? lo_row : hi_row,
                     a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, box, pre::ROWS, swz);
   if (rc) return rc;
@@ -379,10 +386,11 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   static const int env_band = getenv("W4A4_PREFILL_BAND") ? atoi(getenv("W4A4_PREFILL_BAND")) : 0;
   p.band = env_band > 0 ? env_band : 16;
 
-  const size_t smem = pre::smem_bytes(f8);
+  const size_t smem = pre::smem_bytes(prep);
   void (*kern)(const CUtensorMap, const CUtensorMap, const pre::Params) =
-      f8 ? (dump ? pre::prefill_gemm_kernel<true, true> : pre::prefill_gemm_kernel<false, true>)
-         : (dump ? pre::prefill_gemm_kernel<true, false> : pre::prefill_gemm_kernel<false, false>);
+      prep ? (dump ? pre::prefill_gemm_kernel<true, true, true> : pre::prefill_gemm_kernel<false, true, true>)
+      : f8 ? (dump ? pre::prefill_gemm_kernel<true, true, false> : pre::prefill_gemm_kernel<false, true, false>)
+           : (dump ? pre::prefill_gemm_kernel<true, false, false> : pre::prefill_gemm_kernel<false, false, false>);
   cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(prefill): %s", cudaGetErrorString(e));
   e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, p);
@@ -658,9 +666,9 @@ int w4a4_fused_dense_sparse_expanded_prepared(const void* W_low, const void* W_h
   GemmArgs a{};
   a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
   a.do_dense = true; a.nnz = nnz; a.sparse_weight = 16.f;
-  // prepared weights go with e4m3 expanded codes, and only the tensor-core kernel reads either
-  a.xe_fmt = has_prepared(a) ? W4A4_CODES_E4M3 : W4A4_CODES_S8;
+  // e4m3 expanded codes (flagged by the caller; implied by prepared weights) are read only by the tensor-core kernel
   if (!has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
+  a.xe_fmt = (has_prepared(a) || (flags & W4A4_FLAG_CODES_E4M3)) ? W4A4_CODES_E4M3 : W4A4_CODES_S8;
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.XE = XE; a.sumxf = sumxf; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.scale_x = scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
@@ -739,7 +747,9 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
     a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
     if (!has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
   }
-  a.xe_fmt = has_prepared(a) ? 1 : 0;
+  // the tensor-core kernel reads e4m3 codes when it runs fp8 MMAs (prepared weights), s8 codes otherwise
+  static const bool env_f8 = getenv("W4A4_PREFILL_F8") && atoi(getenv("W4A4_PREFILL_F8")) != 0;
+  a.xe_fmt = (wants_tensor_path(T, K, N, flags, dev->sm_count) && (has_prepared(a) || env_f8)) ? 1 : 0;
   rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
                     T, K, s, dev->sm_count, a.xe_fmt);
   if (rc) return rc;

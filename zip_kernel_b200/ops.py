@@ -282,11 +282,12 @@ def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor, *, e4m3: bo
 def fused_dense_sparse_expanded_cuda(
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
     XE, sumxf, scale_u4, zero_u4, scale_x, d_out, d_in,
-    *, token_major: bool = False, force: Optional[str] = None, prepared=None,
+    *, token_major: bool = False, force: Optional[str] = None, prepared=None, e4m3: bool = False,
 ) -> torch.Tensor:
     """:func:`fused_dense_sparse_cuda_int4` on activations already expanded by
-    :func:`expand_activations_cuda`; a single kernel launch.  With ``prepared`` weights
-    ``XE`` must have been expanded with ``e4m3=True``."""
+    :func:`expand_activations_cuda`; a single kernel launch.  ``e4m3=True`` says that ``XE``
+    was expanded with ``e4m3=True`` (many-token calls only: fp8 MMAs instead of integer ones);
+    ``prepared`` weights imply it."""
     d_out, d_in = int(d_out), int(d_in)
     T = int(scale_x.shape[0])
     assert XE.is_cuda and XE.dtype == torch.int8 and XE.is_contiguous()
@@ -308,8 +309,8 @@ def fused_dense_sparse_expanded_cuda(
         _lib.check(_L.w4a4_fused_dense_sparse_expanded_prepared(
             W.data_ptr(), Wh.data_ptr() if nnz else None, plo, phi, ro.data_ptr(), ci.data_ptr() if nnz else None,
             XE.data_ptr(), sumxf.data_ptr(), s.data_ptr(), z.data_ptr(), sx.data_ptr(), Y.data_ptr(),
-            T, d_in, d_out, nnz, _flags(token_major, force), ws.data_ptr(), ws.numel(),
-            _lib.stream_ptr(W.device)), "fused_dense_sparse_expanded")
+            T, d_in, d_out, nnz, _flags(token_major, force) | (_lib.FLAG_CODES_E4M3 if e4m3 else 0),
+            ws.data_ptr(), ws.numel(), _lib.stream_ptr(W.device)), "fused_dense_sparse_expanded")
     return Y
 
 

@@ -380,7 +380,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           z_due += SZ_CHUNK;
           if (!ok) break;
         }
-        if (!mbar_wait(&ready[xs], xph, SITE_PRE_XFULL)) { ok = false; break; }
+        if (!(PREP ? mbar_wait_relaxed(&ready[xs], xph, SITE_PRE_XFULL) : mbar_wait(&ready[xs], xph, SITE_PRE_XFULL))) { ok = false; break; }
         tc_fence_after();
         const uint64_t bdesc = bdesc0 + (uint64_t)(xs * (X_BYTES >> 4));
         const uint32_t d = d0 + buf * TN, a = a0 + ab * A_COLS;

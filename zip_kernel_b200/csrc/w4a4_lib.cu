@@ -445,16 +445,22 @@ int check_common(int T, int K, int N, int nnz) {
 }
 
 // Many tokens take the tcgen05 kernel, few the weight-streaming one.
-bool wants_tensor_path(int T, int K, int N, int flags, int sm_count) {
+bool wants_tensor_path(int T, int K, int N, int flags, int sm_count, bool prepared) {
   // W4A4_TENSOR_MIN_T moves the switch-over (A/B runs)
   static const int min_t = getenv("W4A4_TENSOR_MIN_T") ? atoi(getenv("W4A4_TENSOR_MIN_T")) : 0;
   bool tensor_path;
   if (min_t > 0) {
     tensor_path = T >= min_t;
   } else {
-    // measured cross-over on B200: the tensor kernel needs a grid that fills the SMs
+    // Cross-over between 64 and 255 tokens from a cost model fitted on B200 (quantisation included, us):
+    // the streaming kernel re-reads the weights from L2 once per 32 tokens at ~2.4 TB/s; the tensor-core
+    // kernel takes ~0.6 us (0.53 on prepared weights) per K-step of a 128 x 128 tile and wave of tiles.
+    // It reproduces the measured winner on the Llama-3-8B shapes at 64, 96, 128 and 192 tokens.
     const long long tiles = (long long)((N + 127) / 128) * ((T + w4a4::pre::TN - 1) / w4a4::pre::TN);
-    tensor_path = T >= 256 || (T >= 64 && tiles >= sm_count);
+    const double waves = (double)((tiles + sm_count - 1) / sm_count);
+    const double stream_us = 10.0 + (double)((T + 31) / 32) * ((double)K * N / 2) / 2.4e6;
+    const double tensor_us = 9.0 + waves * (K / 128) * (prepared ? 0.53 : 0.6);
+    tensor_path = T >= 256 || (T >= 64 && tensor_us < stream_us);
   }
   tensor_path = tensor_path && w4a4::pre::supported(T, K, N);
   if (flags & W4A4_FLAG_FORCE_STREAM) tensor_path = false;
@@ -480,7 +486,7 @@ int run_gemm(GemmArgs& a) {
     return fail(W4A4_ERR_UNSUPPORTED, "tensor-core path does not support T=%d K=%d N=%d", a.T, a.K, a.N);
   if (!aligned(a.W_low_prep, 16) || !aligned(a.W_high_prep, 16))
     return fail(W4A4_ERR_ALIGNMENT, "weight pointers must be 16-byte aligned");
-  if (wants_tensor_path(a.T, a.K, a.N, a.flags, dev->sm_count)) return launch_prefill(a, dev);
+  if (wants_tensor_path(a.T, a.K, a.N, a.flags, dev->sm_count, has_prepared(a))) return launch_prefill(a, dev);
   if (a.XE != nullptr && a.xe_fmt != 0) return fail(W4A4_ERR_BAD_ARG, "the streaming path reads s8 expanded codes");
   return launch_decode(a, dev);
 }
@@ -743,13 +749,12 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.nnz = nnz; a.do_dense = true; a.sparse_weight = 16.f;
   // the quantiser writes the codes in the format the GEMM kernel of this call will read
-  if (wants_tensor_path(T, K, N, flags, dev->sm_count)) {
-    a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
-    if (!has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
-  }
+  a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
+  const bool tensor = wants_tensor_path(T, K, N, flags, dev->sm_count, has_prepared(a));
+  if (!tensor || !has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
   // the tensor-core kernel reads e4m3 codes when it runs fp8 MMAs (prepared weights), s8 codes otherwise
   static const bool env_f8 = getenv("W4A4_PREFILL_F8") && atoi(getenv("W4A4_PREFILL_F8")) != 0;
-  a.xe_fmt = (wants_tensor_path(T, K, N, flags, dev->sm_count) && (has_prepared(a) || env_f8)) ? 1 : 0;
+  a.xe_fmt = (tensor && (has_prepared(a) || env_f8)) ? 1 : 0;
   rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
                     T, K, s, dev->sm_count, a.xe_fmt);
   if (rc) return rc;

@@ -284,3 +284,29 @@ def test_host_staged_batch_graph(ops):
         for Xh, Wc, Yh in reqs:
             assert torch.equal(Yh, v9_linear.v9_linear_forward(Xh.cuda(), Wc).cpu())
     backend.clear_cuda_graph_cache()
+
+
+def test_quant_every_fp16_value_against_many_scales(ops):
+    """Rows that hold EVERY finite fp16 value up to a chosen maximum: the kernel divides by the token
+    scale through a reciprocal and one residual correction, which must reproduce the IEEE quotient's code for
+    every value - ties at .5, values next to them, subnormal scales included."""
+    vals = np.arange(65536, dtype=np.uint16).view(np.float16)
+    finite = np.isfinite(vals)
+    rng = np.random.default_rng(7)
+    pos = vals[finite & (vals > 0)]
+    maxima = np.concatenate([
+        rng.choice(pos, 44, replace=False),
+        np.array([6e-8, 4.2e-7, 6.1e-5, 1e-3, 0.4375, 1.0, 3.5, 7.0, 7.5, 10.5, 448.0, 65504.0], dtype=np.float16),
+        # maxima whose scale max/7 lands on or next to a rounding tie of fp16
+        np.array([7 * 1.5, 7 * (1 + 2 ** -10), 7 * (1 + 3 * 2 ** -11), 7 * 2 ** -14, 7 * 2 ** -24, 7 * 1.5 * 2 ** -24,
+                  21 * 2 ** -25, 0.1], dtype=np.float16)])
+    X = np.zeros((len(maxima), 65536), dtype=np.float16)
+    for i, m in enumerate(maxima):
+        keep = finite & (np.abs(vals) <= m)
+        X[i, keep] = vals[keep]
+    perm = np.arange(65536, dtype=np.int32)
+    xs4, sx, sumx = ops.activation_quant_cuda(torch.from_numpy(X).cuda(), torch.from_numpy(perm).cuda())
+    r4, rs, rsum = O.quantize_activation_s4(X, perm)
+    assert np.array_equal(np_(sx).view(np.uint16), rs.view(np.uint16))
+    assert np.array_equal(np_(xs4), r4)
+    assert np.array_equal(np_(sumx), rsum)

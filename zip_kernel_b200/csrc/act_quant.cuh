@@ -71,14 +71,26 @@ __device__ __forceinline__ size_t xe_offset(int t, int c, int t_pad) {
   return ((size_t)g * t_pad + t) * 128 + ((((w >> 1) ^ (t & 7)) << 4) | ((w & 1) << 3));
 }
 
+// max(m, |v[0..7]|): the maximum is taken in half precision (exact), one conversion pair at the end;
+// like fmaxf, __hmax2 returns the other operand when one is NaN
 __device__ __forceinline__ float half_abs_max8(const uint4& v, float m) {
   const __half2* h = reinterpret_cast<const __half2*>(&v);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    float2 f = __half22float2(__habs2(h[i]));
-    m = fmaxf(m, fmaxf(f.x, f.y));
-  }
-  return m;
+  const __half2 mm = __hmax2(__hmax2(__habs2(h[0]), __habs2(h[1])), __hmax2(__habs2(h[2]), __habs2(h[3])));
+  const float2 f = __half22float2(mm);
+  return fmaxf(m, fmaxf(f.x, f.y));
+}
+
+// The code of x for the token scale s: clamp(rint(x / s), -8, 7) with the IEEE quotient.  The divisor is
+// the same for a whole token, so the division is a product with r = RN(1 / s) followed by one residual
+// correction (q0 = x r; e = x - s q0, exact in an FMA; q = q0 + e r).  For every x and s that are fp16
+// values - all this kernel sees - that equals div.rn(x, s) bit for bit wherever |x / s| < 16 and gives the
+// same code everywhere: checked exhaustively on the GPU over all 31 743 positive fp16 scales x all finite
+// fp16 values.  Three instructions instead of the ten-odd of a full division.
+__device__ __forceinline__ int quant_code(float x, float s, float r) {
+  const float q0 = __fmul_rn(x, r);
+  const float q = fmaf(fmaf(-s, q0, x), r, q0);
+  const int c = __float2int_rn(q);                          // round to nearest even, like rint
+  return max(min(c, 7), -8);
 }
 
 // Quantises slice `rank` (of p.C) of token t with a CTA of NTHREADS threads.  Every
@@ -185,6 +197,7 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
   const float s = __half2float(scale16);
   const bool zero_row = !(s > 0.f);
   const float s_safe = zero_row ? 1.0f : s;
+  const float r_safe = __frcp_rn(s_safe);
   if (tid == 0 && rank == 0) p.scale_x[t] = scale16;
 
   uint32_t* out = p.X_s4 ? reinterpret_cast<uint32_t*>(p.X_s4 + (long long)t * (p.K >> 1)) : nullptr;
@@ -204,14 +217,13 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
       const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float2 f = __half22float2(h[i]);
-        float q0 = fminf(fmaxf(rintf(__fdiv_rn(f.x, s_safe)), -8.f), 7.f);
-        float q1 = fminf(fmaxf(rintf(__fdiv_rn(f.y, s_safe)), -8.f), 7.f);
-        int i0 = zero_row ? 0 : (int)q0;
-        int i1 = zero_row ? 0 : (int)q1;
+        const float2 f = __half22float2(h[i]);
+        // a row whose scale rounds to zero holds only values far below 0.5: divided by 1 they give code 0
+        const int i0 = quant_code(f.x, s_safe, r_safe), i1 = quant_code(f.y, s_safe, r_safe);
         sum += i0 + i1;
-        word |= (uint32_t)(i0 & 0xF) << (8 * i);
-        word |= (uint32_t)(i1 & 0xF) << (8 * i + 4);
+        // the low four bits of each code into their nibble (constant positions after unrolling)
+        asm("bfi.b32 %0, %1, %0, %2, 4;" : "+r"(word) : "r"(i0), "r"(8 * i));
+        asm("bfi.b32 %0, %1, %0, %2, 4;" : "+r"(word) : "r"(i1), "r"(8 * i + 4));
       }
       if (out) out[c] = word;
       if (p.XE) *reinterpret_cast<uint2*>(p.XE + xe_offset(t, c, p.t_pad)) = expand_word(word, p.fmt);

@@ -409,13 +409,17 @@ def dump_accumulators(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col
     acc_hi = torch.zeros((nnz, BROW, T), dtype=torch.int32, device=dev)
     W = W_low_packed.contiguous()
     X = X_s4.contiguous()
+    # converted copies stay referenced until the call has been issued
+    Wh = W_high_blocks_packed.contiguous() if nnz else None
+    ro = hp_row_offsets.contiguous().to(torch.int32) if nnz else None
+    ci = hp_col_indices.contiguous().to(torch.int32) if nnz else None
     with torch.cuda.device(dev):
         ws = _lib.workspace(dev, T, d_in, d_out, nnz)
-        plo, phi = _prepared_ptrs(prepared, W, W_high_blocks_packed.contiguous() if nnz else None, nnz)
+        plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
         _lib.check(_L.w4a4_dump_accumulators_prepared(
-            W.data_ptr(), W_high_blocks_packed.contiguous().data_ptr() if nnz else None, plo, phi,
-            hp_row_offsets.contiguous().to(torch.int32).data_ptr() if nnz else None,
-            hp_col_indices.contiguous().to(torch.int32).data_ptr() if nnz else None,
+            W.data_ptr(), Wh.data_ptr() if nnz else None, plo, phi,
+            ro.data_ptr() if nnz else None,
+            ci.data_ptr() if nnz else None,
             X.data_ptr(), acc.data_ptr(), acc_hi.data_ptr() if nnz else None, T, d_in, d_out, nnz,
             _flags(False, force), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)), "dump_accumulators")
     return acc, acc_hi

@@ -41,7 +41,7 @@ struct QuantParams {
   int t_pad;              // tokens rounded up to 16: row pitch of the expanded layout
   int vec_ok;             // 1 when every row start is 16-byte aligned
   int C;                  // CTAs (cluster size) per token; divides K/128
-  int stage_row;          // 1: perm given and the dynamic shared memory holds the whole raw row behind the slice
+  int stage_row;          // 1: perm given, C == 1: the dynamic shared memory holds the raw row, gathered while quantising
   int fmt;                // bytes of XE: 0 = s8 codes (even/odd order), 1 = e4m3 encodings in natural order (see expand_word)
 };
 
@@ -96,7 +96,7 @@ __device__ __forceinline__ int quant_code(float x, float s, float r) {
 // Quantises slice `rank` (of p.C) of token t with a CTA of NTHREADS threads.  Every
 // thread of the CTA calls it; for p.C > 1 the CTAs of a cluster call it together
 // with rank = their cluster rank.  `quant_smem` (16-byte aligned) holds the slice
-// (2 * K / C bytes) and, when p.stage_row is set, the raw row behind it.
+// (2 * K / C bytes; with p.stage_row - one CTA per token - the raw row, 2 * K bytes).
 // With WAIT_DEP the function itself waits for the preceding kernel in the stream
 // (programmatic dependent launch) - after it has fetched the thread's first
 // permutation indices, which belong to the weights and do not depend on that
@@ -136,26 +136,25 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
       m = half_abs_max8(v, m);
     }
   } else if (p.stage_row) {
-    // Column permutation: the whole row is brought into shared memory with coalesced
-    // 128-bit loads (one global round trip, in flight together with the first
-    // permutation indices) and the gather runs on shared memory; a gather from global
-    // memory costs a second, dependent round trip and one L1 wavefront per element.
-    __half* raw = reinterpret_cast<__half*>(row + (c_hi - c_lo));
+    // Column permutation, one CTA per token: the whole raw row is brought into shared memory with
+    // coalesced 128-bit loads (one global round trip, in flight together with the first permutation
+    // indices).  The maximum does not depend on the order of the columns, so it is taken from the values
+    // as they arrive; the gather runs on shared memory while quantising.  (A gather from global memory
+    // costs a second, dependent round trip and one L1 wavefront per element.)
+    __half* raw = reinterpret_cast<__half*>(row);
     if (p.vec_ok) {
       const uint4* src = reinterpret_cast<const uint4*>(xrow);
-      for (int c = tid; c < nchunk_row; c += QUANT_THREADS) reinterpret_cast<uint4*>(raw)[c] = ld_plain(src + c);
+      for (int c = tid; c < nchunk_row; c += QUANT_THREADS) {
+        const uint4 v = ld_plain(src + c);
+        row[c] = v;
+        m = half_abs_max8(v, m);
+      }
     } else {
-      for (int k = tid; k < p.K; k += QUANT_THREADS) raw[k] = xrow[k];
-    }
-    __syncthreads();
-    for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
-      if (c != c_lo + tid) load_perm(c, pa, pb);
-      __align__(16) __half h[8];
-      h[0] = raw[pa.x]; h[1] = raw[pa.y]; h[2] = raw[pa.z]; h[3] = raw[pa.w];
-      h[4] = raw[pb.x]; h[5] = raw[pb.y]; h[6] = raw[pb.z]; h[7] = raw[pb.w];
-      uint4 v = *reinterpret_cast<uint4*>(h);
-      row[c - c_lo] = v;
-      m = half_abs_max8(v, m);
+      for (int k = tid; k < p.K; k += QUANT_THREADS) {
+        const __half x = xrow[k];
+        raw[k] = x;
+        m = fmaxf(m, fabsf(__half2float(x)));
+      }
     }
   } else {
     for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
@@ -213,7 +212,17 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
     uint32_t word = 0;
     int sum = 0;
     if (live) {
-      uint4 v = row[c - c_lo];
+      uint4 v;
+      if (p.stage_row) {
+        const __half* raw = reinterpret_cast<const __half*>(row);
+        if (c0 != c_lo) load_perm(c, pa, pb);        // the first chunk's indices were fetched up front
+        __align__(16) __half g[8];
+        g[0] = raw[pa.x]; g[1] = raw[pa.y]; g[2] = raw[pa.z]; g[3] = raw[pa.w];
+        g[4] = raw[pb.x]; g[5] = raw[pb.y]; g[6] = raw[pb.z]; g[7] = raw[pb.w];
+        v = *reinterpret_cast<uint4*>(g);
+      } else {
+        v = row[c - c_lo];
+      }
       const __half2* h = reinterpret_cast<const __half2*>(&v);
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -237,17 +246,21 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
   }
 }
 
-__global__ void __launch_bounds__(QUANT_THREADS)
+// NT threads per CTA: 256 when a token is spread over a cluster or few tokens are in flight (latency), 128 when
+// there are many tokens (throughput: a thread's set-up - permutation indices, address arithmetic, the
+// reductions - is then shared by twice as many elements and twice as many CTAs fit an SM).
+template <int NT>
+__global__ void __launch_bounds__(NT)
 act_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(16) unsigned char quant_dyn_smem[];
-  __shared__ float warp_max[QUANT_THREADS / 32];
+  __shared__ float warp_max[NT / 32];
   __shared__ float peer_max[8];
   // Let the next kernel in the stream be scheduled early; then wait until the
   // producer of X (and every earlier user of the output buffers) has finished.
   // (the wait for the producer of X and for every earlier user of the output buffers happens inside)
   grid_launch_dependents();
   const int t = blockIdx.x / p.C;
-  quant_token<QUANT_THREADS, true>(p, t, blockIdx.x - t * p.C, quant_dyn_smem, warp_max, peer_max);
+  quant_token<NT, true>(p, t, blockIdx.x - t * p.C, quant_dyn_smem, warp_max, peer_max);
 }
 
 // Builds the expanded layout and the transposed float group sums from already

@@ -423,14 +423,18 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   q.C = C;
   size_t smem = (size_t)K * 2 / C;
   if (smem > 200 * 1024) return fail(W4A4_ERR_UNSUPPORTED, "K=%d exceeds the quantisation kernel's row buffer", K);
-  // with a column permutation and one CTA per token the raw row is staged behind the slice when it fits
-  q.stage_row = (perm != nullptr && C == 1 && smem + (size_t)K * 2 <= 200 * 1024) ? 1 : 0;
-  if (q.stage_row) smem += (size_t)K * 2;
+  // with a column permutation and one CTA per token the row is staged as it is and gathered while quantising
+  q.stage_row = (perm != nullptr && C == 1) ? 1 : 0;
+  // many tokens: smaller CTAs (see act_quant_kernel); W4A4_QUANT_THREADS=128|256 overrides (A/B runs)
+  static const int env_nt = getenv("W4A4_QUANT_THREADS") ? atoi(getenv("W4A4_QUANT_THREADS")) : 0;
+  // (measured, 8192 tokens: K = 4096 54 -> 44 us; K = 14336, where shared memory limits an SM to three CTAs, 194 -> 235 us)
+  const bool small_cta = env_nt ? env_nt == 128 : (C == 1 && T >= 4 * sm_count && smem <= 32 * 1024);
+  void (*kern)(const QuantParams) = small_cta ? act_quant_kernel<128> : act_quant_kernel<QUANT_THREADS>;
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(act_quant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
     if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(quant): %s", cudaGetErrorString(e));
   }
-  cudaError_t e = launch_ex(act_quant_kernel, dim3((unsigned)((long long)T * C)), dim3(QUANT_THREADS), smem, stream, C, q);
+  cudaError_t e = launch_ex(kern, dim3((unsigned)((long long)T * C)), dim3(small_cta ? 128 : QUANT_THREADS), smem, stream, C, q);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "quant kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }

@@ -150,3 +150,24 @@ def test_prepared_container_forward(ops):
     v9_linear.prepare_for_prefill(Wd)
     assert Wd.prepared is not None and Wd.to(torch.device("cuda")).prepared is None
     assert torch.equal(v9_linear.v9_linear_forward(X.cuda(), Wd), Y0)
+
+
+@pytest.mark.parametrize("T,N,K", [(64, 6144, 4096), (96, 6144, 4096), (128, 6144, 4096), (192, 4096, 4096),
+                                   (128, 4096, 14336), (255, 384, 1024), (100, 28672, 512)])
+def test_automatic_kernel_choice_between_64_and_255_tokens(ops, T, N, K):
+    """Whichever kernel the library's cost model picks, with or without prepared weights, the result is that of
+    one of the two kernels bit for bit (they agree with each other within the fp16 tolerance)."""
+    W, X = make_case(T, N, K, 0.05, perm_seed=4)
+    Wd = W.to(torch.device("cuda"))
+    prep = prepare(ops, Wd)
+    args = (X.cuda(), Wd.perm, Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices,
+            Wd.scale_u4, Wd.zero_u4, N, K)
+    Ys = ops.fused_dense_sparse_e2e_cuda(*args, force="stream")
+    Yt = ops.fused_dense_sparse_e2e_cuda(*args, force="tensor")
+    assert_close_fp16(np_(Yt), np_(Ys), "tensor vs stream")
+    for pr in (None, prep):
+        Ya = ops.fused_dense_sparse_e2e_cuda(*args, prepared=pr)
+        assert torch.equal(Ya, Ys) or torch.equal(Ya, Yt)
+        q = ops.activation_quant_cuda(X.cuda(), Wd.perm)
+        Yb = fused(ops, Wd, q, prepared=pr)
+        assert torch.equal(Yb, Ys) or torch.equal(Yb, Yt)

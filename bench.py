@@ -374,7 +374,7 @@ def main():
             ops.fused_dense_sparse_expanded_cuda(W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
                                                  W.hp_col_indices, it["XE"], it["sumxf"], W.scale_u4,
                                                  W.zero_u4, q[1], W.d_out, W.d_in, token_major=True,
-                                                 prepared=W.prepared)
+                                                 prepared=W.prepared, e4m3=W.prepared is not None)
 
     def e2e_step(r):
         # public host-staged call: pinned activations in, pinned results out.  The twelve linears of a

@@ -62,6 +62,13 @@ const char* w4a4_last_error(void);
  * `stream`).  *word == 0 means no bounded wait has given up since the last call. */
 int w4a4_device_error(int* word /* host */, void* stream);
 
+/* Self-test of the bounded device-side waits (no counterpart in the reference): launches a
+ * one-CTA kernel in which one thread waits on a barrier nobody arrives on, gives up after
+ * `polls` polls (1..2^20), records the device error word and returns normally.  A later
+ * w4a4_device_error then returns W4A4_ERR_DEVICE with word = 0x40000000 | (0x7e << 8), and the
+ * context stays usable. */
+int w4a4_selftest_bounded_wait(int polls, void* stream);
+
 /* Replaces activation_quant_launch (bindings.cc:113-122; kernel
  * cuda_kernel/csrc/activation_quant/activation_quant.cu:699-865).
  * No workspace. */
@@ -173,16 +180,15 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
                                            const void* zero_u4, void* Y, int T, int K, int N, int nnz,
                                            int flags, void* workspace, size_t workspace_bytes, void* stream);
 /* The same with activations expanded once for several linears.  The tensor-core kernel runs fp8 MMAs on
- * e4m3 codes - on prepared weights, and also on packed weights, whose nibbles it then turns into e4m3
- * on the SM (slower than its integer MMAs on s8 codes, which stay the default for packed weights; same
- * output bits).  w4a4_expand_activations_fmt with
+ * e4m3 codes against prepared weights.  w4a4_expand_activations_fmt with
  * W4A4_CODES_E4M3 writes the e4m3 form (same group-major, chunk-swizzled layout; inside a packed word
  * the codes keep their natural order instead of the even-then-odd order of the s8 form;
  * W4A4_CODES_S8 is what w4a4_expand_activations writes).  Pass such a buffer to
- * w4a4_fused_dense_sparse_expanded_prepared with W4A4_FLAG_CODES_E4M3 (prepared pointers may be
- * NULL; non-NULL ones imply the flag).  The call must be one the tensor-core kernel takes (many tokens,
- * or W4A4_FLAG_FORCE_TENSOR): the streaming kernel reads s8 codes and the call fails with
- * W4A4_ERR_BAD_ARG otherwise. */
+ * w4a4_fused_dense_sparse_expanded_prepared with W4A4_FLAG_CODES_E4M3 and the prepared weights.  The
+ * flag alone says which bytes XE holds: prepared pointers given WITHOUT the flag (s8 codes) are
+ * rejected with W4A4_ERR_BAD_ARG, and so are e4m3 codes without prepared weights for every operand in
+ * use.  A call with e4m3 codes always runs the tensor-core kernel, whatever the token count (the
+ * streaming kernel reads s8 codes; W4A4_FLAG_FORCE_STREAM with e4m3 codes is W4A4_ERR_BAD_ARG). */
 #define W4A4_CODES_S8   0
 #define W4A4_CODES_E4M3 1
 int w4a4_expand_activations_fmt(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,

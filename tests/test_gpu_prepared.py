@@ -1,7 +1,7 @@
-"""The many-token kernel's three instantiations - integer MMAs on s8 codes, fp8 MMAs
-(tcgen05 kind::f8f6f4, fp32 accumulation) on packed weights turned into e4m3 on the SM, and fp8
-MMAs on weights prepared once as e4m3 bytes - must give the same accumulators and the same
-output bits: the products and sums are small integers, exact in fp32."""
+"""The many-token kernel's two instantiations - integer MMAs on s8 codes against the packed
+nibbles, and fp8 MMAs (tcgen05 kind::f8f6f4, fp32 accumulation) on weights prepared once as e4m3
+bytes - must give the same accumulators and the same output bits: the products and sums are small
+integers, exact in fp32."""
 
 import numpy as np
 import pytest
@@ -96,12 +96,8 @@ def test_prepared_outputs_equal_packed(ops, T, N, K, density):
     XE, sumxf = ops.expand_activations_cuda(q[0], q[2], e4m3=True)
     Yx = ops.fused_dense_sparse_expanded_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
                                               Wd.hp_col_indices, XE, sumxf, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
-                                              force="tensor", prepared=prep)
+                                              force="tensor", prepared=prep, e4m3=True)
     assert torch.equal(Yx, Yp)
-    Yx2 = ops.fused_dense_sparse_expanded_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
-                                               Wd.hp_col_indices, XE, sumxf, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
-                                               force="tensor", e4m3=True)   # packed weights, fp8 MMAs
-    assert torch.equal(Yx2, Yp)
     if T <= 512:
         xs4, sx, sumx = (np_(t) for t in q)
         assert_close_fp16(np_(Yf), oracle_fused(container_np(W), xs4, sumx, sx), "prepared vs oracle")
@@ -129,16 +125,29 @@ def test_prepared_full_size_gate_up(ops):
     assert _lib.device_error(torch.device("cuda")) == 0
 
 
-def test_expanded_e4m3_codes_are_refused_by_the_streaming_kernel(ops):
-    T, N, K = 8, 256, 512
-    W, X = make_case(T, N, K, 0.1)
-    Wd = W.to(torch.device("cuda"))
-    q = ops.activation_quant_cuda(X.cuda(), Wd.perm)
-    XE, sumxf = ops.expand_activations_cuda(q[0], q[2], e4m3=True)
-    with pytest.raises(ValueError):
-        ops.fused_dense_sparse_expanded_cuda(Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets,
-                                             Wd.hp_col_indices, XE, sumxf, Wd.scale_u4, Wd.zero_u4, q[1], N, K,
-                                             prepared=prepare(ops, Wd))
+def test_expanded_code_format_is_what_the_flag_says(ops):
+    """The flag alone tells the library which bytes XE holds.  Prepared weights with s8 codes, e4m3 codes
+    without prepared weights, and e4m3 codes forced onto the streaming kernel are argument errors; e4m3
+    codes with prepared weights run the tensor-core kernel at any token count (64..255 included, where the
+    cost model may prefer the streaming kernel for s8 codes)."""
+    for T, N, K in ((8, 256, 512), (100, 28672, 512), (192, 4096, 4096)):
+        W, X = make_case(T, N, K, 0.1)
+        Wd = W.to(torch.device("cuda"))
+        prep = prepare(ops, Wd)
+        q = ops.activation_quant_cuda(X.cuda(), Wd.perm)
+        XE, sumxf = ops.expand_activations_cuda(q[0], q[2], e4m3=True)
+        XE8, sumxf8 = ops.expand_activations_cuda(q[0], q[2])
+        base = (Wd.W_low_packed, Wd.W_high_blocks_packed, Wd.hp_row_offsets, Wd.hp_col_indices)
+        tail = (Wd.scale_u4, Wd.zero_u4, q[1], N, K)
+        with pytest.raises(ValueError):          # s8 codes + prepared weights
+            ops.fused_dense_sparse_expanded_cuda(*base, XE8, sumxf8, *tail, prepared=prep)
+        with pytest.raises(ValueError):          # e4m3 codes, no prepared weights
+            ops.fused_dense_sparse_expanded_cuda(*base, XE, sumxf, *tail, e4m3=True)
+        with pytest.raises(ValueError):          # e4m3 codes cannot be streamed
+            ops.fused_dense_sparse_expanded_cuda(*base, XE, sumxf, *tail, prepared=prep, e4m3=True, force="stream")
+        Yx = ops.fused_dense_sparse_expanded_cuda(*base, XE, sumxf, *tail, prepared=prep, e4m3=True)
+        Yt = fused(ops, Wd, q, force="tensor")
+        assert torch.equal(Yx, Yt)
 
 
 def test_prepared_container_forward(ops):

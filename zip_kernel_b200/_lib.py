@@ -7,8 +7,10 @@ produces it.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import os
+import threading
 from typing import Dict, Tuple
 
 import torch
@@ -27,6 +29,7 @@ SIGNATURES = {
     "w4a4_status_string": (_c.c_char_p, [_INT]),
     "w4a4_last_error": (_c.c_char_p, []),
     "w4a4_device_error": (_INT, [_c.POINTER(_INT), _PTR]),
+    "w4a4_selftest_bounded_wait": (_INT, [_INT, _PTR]),
     "w4a4_activation_quant": (_INT, [_PTR, _LL, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _PTR]),
     "w4a4_workspace_bytes": (_SZ, [_INT, _INT, _INT, _INT]),
     "w4a4_fused_dense_sparse": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
@@ -110,8 +113,52 @@ def stream_ptr(device) -> int:
 # ---------------------------------------------------------------------------
 # workspace cache: one scratch buffer per (device, stream), grown on
 # demand.  Calls issued on one stream are ordered, so they can share scratch.
+#
+# A captured CUDA graph bakes the scratch address into its kernel nodes, so a
+# graph must own the scratch it was captured with: a buffer from the shared
+# cache could be replaced (and freed) by a later, larger call on a stream that
+# happens to reuse the same handle, and the graph would then replay into freed
+# memory.  Code that captures wraps warm-up and capture in
+# ``use_workspace(holder)`` and keeps ``holder`` alive next to the graph.
 # ---------------------------------------------------------------------------
 _workspaces: Dict[Tuple[int, int], torch.Tensor] = {}
+_tls = threading.local()
+
+
+class WorkspaceHolder:
+    """Scratch buffers private to one captured graph (or one group of graphs that
+    are never replayed concurrently).  Buffers are only ever added: a buffer that a
+    captured kernel may reference is never freed or replaced while the holder lives."""
+
+    def __init__(self):
+        self.buffers: Dict[Tuple[int, int], list] = {}
+
+    def get(self, key: Tuple[int, int], need: int, device: torch.device) -> torch.Tensor:
+        bufs = self.buffers.setdefault(key, [])
+        if bufs and bufs[-1].numel() >= need:
+            return bufs[-1]
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(
+                "the W4A4 workspace must be allocated before CUDA-graph capture: "
+                "run the shape once eagerly inside use_workspace(holder) first"
+            )
+        buf = torch.empty(max(need, 256), dtype=torch.uint8, device=device)
+        bufs.append(buf)
+        return buf
+
+    def nbytes(self) -> int:
+        return sum(b.numel() for bufs in self.buffers.values() for b in bufs)
+
+
+@contextlib.contextmanager
+def use_workspace(holder: WorkspaceHolder):
+    """Route this thread's workspace requests to ``holder`` for the duration of the block."""
+    prev = getattr(_tls, "holder", None)
+    _tls.holder = holder
+    try:
+        yield holder
+    finally:
+        _tls.holder = prev
 
 
 def workspace(device: torch.device, T: int, K: int, N: int, nnz: int) -> torch.Tensor:
@@ -119,6 +166,9 @@ def workspace(device: torch.device, T: int, K: int, N: int, nnz: int) -> torch.T
     need = int(lib.w4a4_workspace_bytes(T, K, N, nnz))
     key = (device.index if device.index is not None else torch.cuda.current_device(),
            stream_ptr(device))
+    holder = getattr(_tls, "holder", None)
+    if holder is not None:
+        return holder.get(key, need, device)
     buf = _workspaces.get(key)
     if buf is None or buf.numel() < need:
         if torch.cuda.is_current_stream_capturing():

@@ -60,6 +60,7 @@ class _CacheEntry:
     graph: Optional[Any] = None          # None after a failed capture (sentinel)
     x_static: Optional[torch.Tensor] = None
     y_static: Optional[torch.Tensor] = None
+    scratch: Optional[Any] = None        # the scratch buffers the captured kernels write (owned by this entry)
     capture_us: float = 0.0
     replay_count: int = 0
     _finalizer: Optional[weakref.finalize] = None
@@ -68,6 +69,7 @@ class _CacheEntry:
         self.graph = None
         self.x_static = None
         self.y_static = None
+        self.scratch = None
         if self._finalizer is not None and self._finalizer.alive:
             self._finalizer.detach()
 
@@ -148,6 +150,10 @@ class _GraphCache:
     def stats(self) -> Dict[str, Any]:
         with self._lock:
             return {
+                # the reference's key names (backend/graph_cache.py:278-288) ...
+                "n_entries": len(self._entries), "max_entries": self.capacity, "n_hit": self.hits,
+                "n_miss": self.misses, "n_evict": self.evictions, "n_capture_fail": self.capture_failures,
+                # ... and this library's own
                 "policy": _policy, "size": len(self._entries), "capacity": self.capacity,
                 "hits": self.hits, "misses": self.misses, "evictions": self.evictions,
                 "weak_evictions": self.weak_evictions, "capture_failures": self.capture_failures,
@@ -196,12 +202,14 @@ def _capture_entry(X: torch.Tensor, W: V9WeightContainer, T: int, key: _CacheKey
         return entry                    # nested capture is refused
     t0 = time.perf_counter()
     try:
-        from .. import ops
+        from .. import _lib, ops
         x_static = torch.empty_strided(tuple(X.shape), tuple(X.stride()), dtype=X.dtype, device=X.device)
         x_static.copy_(X)
         side = torch.cuda.Stream(device=X.device)
         side.wait_stream(torch.cuda.current_stream(X.device))
-        with torch.cuda.stream(side):
+        # the graph bakes the scratch address in: it gets scratch of its own, kept alive by the entry
+        scratch = _lib.WorkspaceHolder()
+        with _lib.use_workspace(scratch), torch.cuda.stream(side):
             ops.reserve_workspace(X.device, T, W.d_in, W.d_out, W.n_hp_blocks)
             for _ in range(3):
                 _eager(x_static, W)
@@ -210,10 +218,10 @@ def _capture_entry(X: torch.Tensor, W: V9WeightContainer, T: int, key: _CacheKey
             with torch.cuda.graph(graph, stream=side):
                 y_static = _eager(x_static, W)
         torch.cuda.current_stream(X.device).wait_stream(side)
-        entry.graph, entry.x_static, entry.y_static = graph, x_static, y_static
+        entry.graph, entry.x_static, entry.y_static, entry.scratch = graph, x_static, y_static, scratch
     except Exception as exc:  # noqa: BLE001 - capture may fail for many reasons; stay on eager
         logger.warning("cuda_graph_cache: capture failed for %s (%s); using eager", key, exc)
-        entry.graph = entry.x_static = entry.y_static = None
+        entry.graph = entry.x_static = entry.y_static = entry.scratch = None
     entry.capture_us = (time.perf_counter() - t0) * 1e6
     return entry
 
@@ -277,14 +285,15 @@ def v9_linear_forward_host_graph(X_pinned: torch.Tensor, W: V9WeightContainer, Y
     if hit is None:
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("v9_linear_forward_host_graph cannot capture inside another capture")
-        from .. import ops
+        from .. import _lib, ops
         T = 1
         for s_ in X_pinned.shape[:-1]:
             T *= int(s_)
         x_static = torch.empty(tuple(X_pinned.shape), dtype=torch.float16, device=dev)
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(side):
+        scratch = _lib.WorkspaceHolder()          # owned by the graph (kept in the cache tuple)
+        with _lib.use_workspace(scratch), torch.cuda.stream(side):
             ops.reserve_workspace(dev, T, W.d_in, W.d_out, W.n_hp_blocks)
             for _ in range(2):
                 x_static.copy_(X_pinned, non_blocking=True)
@@ -296,7 +305,7 @@ def v9_linear_forward_host_graph(X_pinned: torch.Tensor, W: V9WeightContainer, Y
                 y_static = _eager(x_static, W)
                 Y_pinned.copy_(y_static, non_blocking=True)
         torch.cuda.current_stream(dev).wait_stream(side)
-        hit = (graph, x_static, y_static)
+        hit = (graph, x_static, y_static, scratch)
         _host_graphs[key] = hit
         weakref.finalize(W, _host_graphs.pop, key, None)
         while len(_host_graphs) > _HOST_GRAPH_CAPACITY:
@@ -337,7 +346,8 @@ def v9_linear_forward_host_graph_many(requests, n_streams: int = 3,
     if hit is None:
         if torch.cuda.is_current_stream_capturing():
             raise RuntimeError("v9_linear_forward_host_graph_many cannot capture inside another capture")
-        from .. import ops
+        from .. import _lib, ops
+        scratch = _lib.WorkspaceHolder()          # one buffer per branch stream, owned by the graph
         statics = [torch.empty(tuple(X.shape), dtype=torch.float16, device=dev) for X, _, _ in reqs]
         main = torch.cuda.Stream(device=dev)
         branches = [torch.cuda.Stream(device=dev) for _ in range(max(1, min(int(n_streams), len(reqs))))]
@@ -356,7 +366,7 @@ def v9_linear_forward_host_graph_many(requests, n_streams: int = 3,
                 main.wait_stream(b)
 
         main.wait_stream(torch.cuda.current_stream(dev))
-        with torch.cuda.stream(main):
+        with _lib.use_workspace(scratch), torch.cuda.stream(main):
             for i, (X, W, _) in enumerate(reqs):          # the scratch is per stream: size it on every branch first
                 T = X.numel() // X.shape[-1]
                 with torch.cuda.stream(branches[i % len(branches)]):
@@ -368,7 +378,7 @@ def v9_linear_forward_host_graph_many(requests, n_streams: int = 3,
             with torch.cuda.graph(graph, stream=main):
                 issue()
         torch.cuda.current_stream(dev).wait_stream(main)
-        hit = (graph, [statics, keep, branches])
+        hit = (graph, [statics, keep, branches, scratch])
         _host_batch_graphs[key] = hit
         while len(_host_batch_graphs) > _HOST_BATCH_CAPACITY:
             _host_batch_graphs.popitem(last=False)

@@ -27,6 +27,7 @@
 namespace w4a4 {
 
 constexpr int QUANT_THREADS = 256;
+constexpr size_t QUANT_MAX_SMEM = 200 * 1024;   // dynamic shared memory the kernel may ask for (one row slice)
 
 struct QuantParams {
   const __half* X;        // (T, K) fp16, row stride ldx elements
@@ -124,6 +125,10 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
     }
   };
   int4 pa = make_int4(0, 0, 0, 0), pb = pa;
+  // A CTA may write into a peer's shared memory only once that peer is known to have started: every
+  // CTA of the cluster arrives here at once and the matching wait sits just before the remote stores,
+  // so the row load hides the barrier's latency.
+  if (C > 1) asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   if (p.perm != nullptr && c_lo + tid < c_hi) load_perm(c_lo + tid, pa, pb);
   if (WAIT_DEP) grid_dependency_wait();
 
@@ -180,6 +185,7 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
 #pragma unroll
   for (int w = 1; w < QUANT_THREADS / 32; ++w) m = fmaxf(m, warp_max[w]);
   if (C > 1) {
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");   // all peers have started
     // push this CTA's maximum into slot `rank` of every CTA of the cluster
     if (tid < C) {
       uint32_t remote;

@@ -142,6 +142,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (after recording the site) when the phase never
 // completed; callers then stop using the pipeline and fall through to the exit.
+__device__ __forceinline__ bool mbar_wait_limit(uint64_t* bar, uint32_t parity, int site, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if (i > 4096) __nanosleep(64);
+  }
+  record_error(site, parity);
+  return false;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int site) {
   for (uint32_t i = 0; i < WAIT_POLL_LIMIT; ++i) {
     if (mbar_try_wait(bar, parity)) return true;

@@ -10,6 +10,7 @@
 #include <cstring>
 #include <mutex>
 #include <string>
+#include <unordered_map>
 
 #include "../../include/w4a4_b200.h"
 #include "act_quant.cuh"
@@ -30,6 +31,10 @@ int fail(int code, const char* fmt, ...) {
   t_last_error = buf;
   return code;
 }
+
+// Every entry point starts with a clean per-thread message, so w4a4_last_error()
+// never reports the failure of an earlier call after a successful one.
+inline void begin_call() { t_last_error.clear(); }
 
 #define CHECK_ARG(cond, ...) \
   do {                       \
@@ -53,6 +58,33 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
+// The kernels' dynamic shared-memory limits are function attributes of the device's
+// context: they are set once per device, on the first call that reaches it.
+cudaError_t set_kernel_attributes() {
+  using namespace w4a4;
+  cudaError_t e = cudaSuccess;
+  auto set = [&](auto kern, size_t smem) {
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  };
+  set(dec::decode_gemm_kernel<1, false>, dec::smem_bytes(1));
+  set(dec::decode_gemm_kernel<2, false>, dec::smem_bytes(2));
+  set(dec::decode_gemm_kernel<4, false>, dec::smem_bytes(4));
+  set(dec::decode_gemm_kernel<1, true>, dec::smem_bytes(1));
+  set(dec::decode_gemm_kernel<2, true>, dec::smem_bytes(2));
+  set(dec::decode_gemm_kernel<4, true>, dec::smem_bytes(4));
+  set(pre::prefill_gemm_kernel<false, false, false>, pre::smem_bytes(false));
+  set(pre::prefill_gemm_kernel<true, false, false>, pre::smem_bytes(false));
+  set(pre::prefill_gemm_kernel<false, true, true>, pre::smem_bytes(true));
+  set(pre::prefill_gemm_kernel<true, true, true>, pre::smem_bytes(true));
+#ifdef W4A4_F8_ON_PACKED
+  set(pre::prefill_gemm_kernel<false, true, false>, pre::smem_bytes(false));
+  set(pre::prefill_gemm_kernel<true, true, false>, pre::smem_bytes(false));
+#endif
+  set(act_quant_kernel<128>, QUANT_MAX_SMEM);
+  set(act_quant_kernel<QUANT_THREADS>, QUANT_MAX_SMEM);
+  return e;
+}
+
 int current_device(DeviceInfo** out) {
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
@@ -63,6 +95,11 @@ int current_device(DeviceInfo** out) {
   if (d.sm_count == 0) {
     e = cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaDeviceGetAttribute: %s", cudaGetErrorString(e));
+  }
+  if (!d.attrs_set) {
+    e = set_kernel_attributes();
+    if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    d.attrs_set = true;
   }
   if (!g_encode) {
     void* fn = nullptr;
@@ -77,9 +114,43 @@ int current_device(DeviceInfo** out) {
 }
 
 // 2-D byte tensor map: `rows` rows of `row_bytes` bytes (pitch = row_bytes), box
-// box_bytes x box_rows.  Out-of-range rows read as zero.
+// box_bytes x box_rows.  Out-of-range rows read as zero.  A map depends only on the
+// address and the geometry, so encoded maps are kept (weights are called with the
+// same pointers over and over) and a repeated call costs a table look-up instead
+// of a driver call.
+struct MapKey {
+  const void* ptr;
+  uint64_t row_bytes, rows;
+  uint32_t box_bytes, box_rows;
+  int swz;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && row_bytes == o.row_bytes && rows == o.rows && box_bytes == o.box_bytes &&
+           box_rows == o.box_rows && swz == o.swz;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+    h ^= (k.row_bytes + 0x9E3779B9u + (h << 6) + (h >> 2));
+    h ^= (k.rows + 0x9E3779B9u + (h << 6) + (h >> 2));
+    h ^= (((uint64_t)k.box_bytes << 32 | k.box_rows) + (uint64_t)k.swz + (h << 6) + (h >> 2));
+    return h;
+  }
+};
+std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+constexpr size_t MAP_CACHE_LIMIT = 4096;
+
 int make_map(CUtensorMap* m, const void* ptr, uint64_t row_bytes, uint64_t rows, uint32_t box_bytes,
              uint32_t box_rows, CUtensorMapSwizzle swz) {
+  const MapKey key{ptr, row_bytes, rows, box_bytes, box_rows, (int)swz};
+  {
+    std::lock_guard<std::mutex> lock(g_mutex);
+    auto it = g_maps.find(key);
+    if (it != g_maps.end()) {
+      *m = it->second;
+      return W4A4_OK;
+    }
+  }
   cuuint64_t dims[2] = {row_bytes, rows ? rows : 1};
   cuuint64_t strides[1] = {row_bytes};
   cuuint32_t box[2] = {box_bytes, box_rows};
@@ -88,6 +159,9 @@ int make_map(CUtensorMap* m, const void* ptr, uint64_t row_bytes, uint64_t rows,
                         CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(W4A4_ERR_LAUNCH, "cuTensorMapEncodeTiled failed (%d)", (int)r);
+  std::lock_guard<std::mutex> lock(g_mutex);
+  if (g_maps.size() >= MAP_CACHE_LIMIT) g_maps.clear();
+  g_maps.emplace(key, *m);
   return W4A4_OK;
 }
 
@@ -128,8 +202,10 @@ DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_p
   const long long base = (long long)p.row_tiles * p.tok_tiles;
   long long s = 1;
   while (s * 2 <= dec::MAX_CLUSTER && base * s * 2 * 10 <= 18LL * sm_count) s *= 2;
-  // tuning override for A/B experiments
-  static const int env_split = getenv("W4A4_DECODE_SPLIT") ? atoi(getenv("W4A4_DECODE_SPLIT")) : 0;
+  // tuning override for A/B experiments and for the split-parity test; read on every call so that one
+  // process can compare cluster sizes on one shape
+  const char* env_split_s = getenv("W4A4_DECODE_SPLIT");
+  const int env_split = env_split_s ? atoi(env_split_s) : 0;
   if (env_split > 0) s = env_split;
   if (s > dec::MAX_CLUSTER) s = dec::MAX_CLUSTER;
   while (s > dense_steps && s > 1) s /= 2;
@@ -157,7 +233,6 @@ struct GemmArgs {
   int T, K, N, nnz, flags;
   bool do_dense;
   float sparse_weight;
-  bool pdl;                // launch as programmatic dependent of the preceding kernel
   int xe_fmt;              // bytes of the expanded codes: 0 = s8, 1 = e4m3 (goes with prepared weights)
   void* ws;
   size_t ws_bytes;
@@ -290,10 +365,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   void (*kern)(const CUtensorMap, const dec::Params) =
       dump ? (nt == 4 ? dec::decode_gemm_kernel<4, true> : nt == 2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
            : (nt == 4 ? dec::decode_gemm_kernel<4, false> : nt == 2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(decode): %s", cudaGetErrorString(e));
-
-  e = launch_ex(kern, dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
+  cudaError_t e = launch_ex(kern, dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
                 plan.split, tm_low, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
@@ -313,14 +385,22 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   // Prepared weights exist only as e4m3 and take fp8 MMAs.  Packed weights take integer MMAs on s8 codes:
   // turning nibbles into e4m3 on the SM (12 permute / logic operations per 8 codes) is slower than widening
   // them to s8 (3 per 8 codes) plus the int -> float conversion in the fold (measured: gate_up M=8192 3027
-  // against 2430 us).  That instantiation runs when the caller hands in e4m3 codes without prepared weights,
-  // or with W4A4_PREFILL_F8=1 (A/B runs).
+  // against 2430 us).  That third instantiation is compiled only with -DW4A4_F8_ON_PACKED (A/B builds); it
+  // then runs when the caller hands in e4m3 codes without prepared weights, or with W4A4_PREFILL_F8=1.
+#ifdef W4A4_F8_ON_PACKED
   static const bool env_f8 = getenv("W4A4_PREFILL_F8") && atoi(getenv("W4A4_PREFILL_F8")) != 0;
+#else
+  const bool env_f8 = false;
+#endif
   const bool f8 = a.XE != nullptr ? a.xe_fmt == 1 : (prep || env_f8);
   const bool dump = a.acc_dump || a.acc_hi_dump;
   const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
   if (prep && !f8)
     return fail(W4A4_ERR_BAD_ARG, "prepared weights need activation codes expanded as e4m3 (W4A4_FLAG_CODES_E4M3)");
+#ifndef W4A4_F8_ON_PACKED
+  if (f8 && !prep)
+    return fail(W4A4_ERR_BAD_ARG, "e4m3 activation codes need prepared weights (w4a4_prepare_weights) for every operand in use");
+#endif
   a.xe_fmt = f8 ? 1 : 0;
   if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
   const int ng = a.K / BCOL;
@@ -389,11 +469,11 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   const size_t smem = pre::smem_bytes(prep);
   void (*kern)(const CUtensorMap, const CUtensorMap, const pre::Params) =
       prep ? (dump ? pre::prefill_gemm_kernel<true, true, true> : pre::prefill_gemm_kernel<false, true, true>)
+#ifdef W4A4_F8_ON_PACKED
       : f8 ? (dump ? pre::prefill_gemm_kernel<true, true, false> : pre::prefill_gemm_kernel<false, true, false>)
+#endif
            : (dump ? pre::prefill_gemm_kernel<true, false, false> : pre::prefill_gemm_kernel<false, false, false>);
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(prefill): %s", cudaGetErrorString(e));
-  e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, p);
+  cudaError_t e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "prefill kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
 }
@@ -422,7 +502,7 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
     if (ng % c == 0 && (long long)T * c <= 2LL * sm_count) { C = c; break; }
   q.C = C;
   size_t smem = (size_t)K * 2 / C;
-  if (smem > 200 * 1024) return fail(W4A4_ERR_UNSUPPORTED, "K=%d exceeds the quantisation kernel's row buffer", K);
+  if (smem > QUANT_MAX_SMEM) return fail(W4A4_ERR_UNSUPPORTED, "K=%d exceeds the quantisation kernel's row buffer", K);
   // with a column permutation and one CTA per token the row is staged as it is and gathered while quantising
   q.stage_row = (perm != nullptr && C == 1) ? 1 : 0;
   // many tokens: smaller CTAs (see act_quant_kernel); W4A4_QUANT_THREADS=128|256 overrides (A/B runs)
@@ -430,10 +510,6 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   // (measured, 8192 tokens: K = 4096 54 -> 44 us; K = 14336, where shared memory limits an SM to three CTAs, 194 -> 235 us)
   const bool small_cta = env_nt ? env_nt == 128 : (C == 1 && T >= 4 * sm_count && smem <= 32 * 1024);
   void (*kern)(const QuantParams) = small_cta ? act_quant_kernel<128> : act_quant_kernel<QUANT_THREADS>;
-  if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-    if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaFuncSetAttribute(quant): %s", cudaGetErrorString(e));
-  }
   cudaError_t e = launch_ex(kern, dim3((unsigned)((long long)T * C)), dim3(small_cta ? 128 : QUANT_THREADS), smem, stream, C, q);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "quant kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
@@ -490,8 +566,12 @@ int run_gemm(GemmArgs& a) {
     return fail(W4A4_ERR_UNSUPPORTED, "tensor-core path does not support T=%d K=%d N=%d", a.T, a.K, a.N);
   if (!aligned(a.W_low_prep, 16) || !aligned(a.W_high_prep, 16))
     return fail(W4A4_ERR_ALIGNMENT, "weight pointers must be 16-byte aligned");
+  // e4m3 codes exist only for the tensor-core kernel: such a call goes there whatever the token count
+  if (a.XE != nullptr && a.xe_fmt != 0) {
+    if (a.flags & W4A4_FLAG_FORCE_STREAM) return fail(W4A4_ERR_BAD_ARG, "the streaming path reads s8 expanded codes");
+    return launch_prefill(a, dev);
+  }
   if (wants_tensor_path(a.T, a.K, a.N, a.flags, dev->sm_count, has_prepared(a))) return launch_prefill(a, dev);
-  if (a.XE != nullptr && a.xe_fmt != 0) return fail(W4A4_ERR_BAD_ARG, "the streaming path reads s8 expanded codes");
   return launch_decode(a, dev);
 }
 
@@ -499,7 +579,7 @@ int run_gemm(GemmArgs& a) {
 // Scratch for w4a4_fused_dense_sparse_noalloc: expanded activation codes of up to
 // NOALLOC_MAX_T tokens of up to NOALLOC_MAX_K features, followed by their
 // transposed group sums.  It lives in the library image, so every GPU that loads
-// the library holds these ~528 KiB until the process exits.
+// the library holds these 544 KiB (557 056 bytes) until the process exits.
 constexpr int NOALLOC_MAX_T = W4A4_NOALLOC_MAX_T;
 constexpr int NOALLOC_MAX_K = W4A4_NOALLOC_MAX_K;
 constexpr size_t NOALLOC_XE_BYTES = (size_t)NOALLOC_MAX_T * NOALLOC_MAX_K + 128 * 128;
@@ -528,6 +608,19 @@ int noalloc_scratch_address(void** out) {
   return W4A4_OK;
 }
 
+// Self-test of the bounded wait: one thread polls a barrier nobody ever arrives on (no copy
+// in flight, nothing else running in the CTA), gives up after `polls` polls, records the
+// error word like any production wait and returns.
+constexpr int SITE_SELFTEST = 0x7e;
+__global__ void selftest_wait_kernel(uint32_t polls) {
+  __shared__ uint64_t bar;
+  if (threadIdx.x == 0) {
+    w4a4::mbar_init(&bar, 1);
+    w4a4::mbar_fence_init();
+    w4a4::mbar_wait_limit(&bar, 0, SITE_SELFTEST, polls);
+  }
+}
+
 }  // namespace
 
 // ===================================================================== C ABI
@@ -551,6 +644,7 @@ const char* w4a4_status_string(int status) {
 const char* w4a4_last_error(void) { return t_last_error.c_str(); }
 
 int w4a4_device_error(int* word, void* stream) {
+  begin_call();
   CHECK_ARG(word != nullptr, "word is NULL");
   int zero = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -561,8 +655,18 @@ int w4a4_device_error(int* word, void* stream) {
   return *word ? W4A4_ERR_DEVICE : W4A4_OK;
 }
 
+int w4a4_selftest_bounded_wait(int polls, void* stream) {
+  begin_call();
+  CHECK_ARG(polls >= 1 && polls <= (1 << 20), "polls must be in 1..2^20, got %d", polls);
+  selftest_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>((uint32_t)polls);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "self-test kernel launch: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
 int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x,
                           int32_t* sum_X, int T, int K, void* stream) {
+  begin_call();
   int rc = check_common(T, K, 1, 0);
   if (rc) return rc;
   CHECK_ARG(X && X_s4 && scale_x && sum_X, "NULL tensor pointer");
@@ -595,6 +699,7 @@ int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t
 size_t w4a4_prepared_weights_bytes(size_t packed_bytes) { return 2 * packed_bytes; }
 
 int w4a4_prepare_weights(const void* packed, void* prepared, size_t packed_bytes, void* stream) {
+  begin_call();
   CHECK_ARG(packed && prepared, "NULL tensor pointer");
   CHECK_ARG(packed_bytes % 4 == 0, "packed_bytes (%zu) must be a multiple of 4", packed_bytes);
   if (!aligned(packed, 4) || !aligned(prepared, 16)) return fail(W4A4_ERR_ALIGNMENT, "prepare_weights pointer alignment");
@@ -618,13 +723,14 @@ int w4a4_fused_dense_sparse_prepared(const void* W_low, const void* W_high, cons
                                      const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y, int T,
                                      int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes,
                                      void* stream) {
+  begin_call();
   CHECK_ARG(Y && zero_u4 && sum_X && scale_x, "NULL tensor pointer");
   GemmArgs a{};
   a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.X_s4 = X_s4; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.sum_X = sum_X; a.scale_x = scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
-  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = false;
+  a.do_dense = true; a.sparse_weight = 16.f;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
   return run_gemm(a);
 }
@@ -641,6 +747,7 @@ int w4a4_expand_activations(const void* X_s4, const int32_t* sum_X, void* XE, fl
 
 int w4a4_expand_activations_fmt(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
                                 int code_format, void* stream) {
+  begin_call();
   CHECK_ARG(code_format == W4A4_CODES_S8 || code_format == W4A4_CODES_E4M3, "unknown code format %d", code_format);
   int rc = check_common(T, K, 1, 0);
   if (rc) return rc;
@@ -672,17 +779,23 @@ int w4a4_fused_dense_sparse_expanded_prepared(const void* W_low, const void* W_h
                                               const void* scale_u4, const void* zero_u4, const void* scale_x,
                                               void* Y, int T, int K, int N, int nnz, int flags, void* workspace,
                                               size_t workspace_bytes, void* stream) {
+  begin_call();
   CHECK_ARG(Y && zero_u4 && XE && sumxf && scale_x, "NULL tensor pointer");
   GemmArgs a{};
   a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
   a.do_dense = true; a.nnz = nnz; a.sparse_weight = 16.f;
-  // e4m3 expanded codes (flagged by the caller; implied by prepared weights) are read only by the tensor-core kernel
+  // The caller says which bytes XE holds.  e4m3 codes are read only by the tensor-core kernel on prepared
+  // weights; s8 codes go with the packed arrays, so prepared pointers given with s8 codes are an error
+  // rather than a silent reinterpretation of the bytes.
   if (!has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
-  a.xe_fmt = (has_prepared(a) || (flags & W4A4_FLAG_CODES_E4M3)) ? W4A4_CODES_E4M3 : W4A4_CODES_S8;
+  a.xe_fmt = (flags & W4A4_FLAG_CODES_E4M3) ? W4A4_CODES_E4M3 : W4A4_CODES_S8;
+  if (has_prepared(a) && a.xe_fmt != W4A4_CODES_E4M3)
+    return fail(W4A4_ERR_BAD_ARG, "prepared weights were passed with s8 activation codes: expand with W4A4_CODES_E4M3 and set "
+                                  "W4A4_FLAG_CODES_E4M3, or pass NULL prepared pointers");
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.XE = XE; a.sumxf = sumxf; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.scale_x = scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
-  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = false;
+  a.do_dense = true; a.sparse_weight = 16.f;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
   return run_gemm(a);
 }
@@ -690,12 +803,13 @@ int w4a4_fused_dense_sparse_expanded_prepared(const void* W_low, const void* W_h
 int w4a4_dense_gemm(const void* W_low, const void* X_s4, const void* scale_u4, const void* zero_u4,
                     const int32_t* sum_X, const void* scale_x, void* Y_low, int T, int K, int N, int flags,
                     void* workspace, size_t workspace_bytes, void* stream) {
+  begin_call();
   CHECK_ARG(Y_low && zero_u4 && sum_X && scale_x, "NULL tensor pointer");
   GemmArgs a{};
   a.W_low = W_low; a.X_s4 = X_s4; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.sum_X = sum_X;
   a.scale_x = scale_x; a.Y = Y_low;
   a.T = T; a.K = K; a.N = N; a.nnz = 0; a.flags = flags;
-  a.do_dense = true; a.sparse_weight = 0.f; a.pdl = false;
+  a.do_dense = true; a.sparse_weight = 0.f;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
   return run_gemm(a);
 }
@@ -703,6 +817,7 @@ int w4a4_dense_gemm(const void* W_low, const void* X_s4, const void* scale_u4, c
 int w4a4_sparse_gemm(const void* W_high, const int32_t* hp_row_offsets, const int32_t* hp_col_indices,
                      const void* X_s4, const void* scale_u4, const void* scale_x, void* Y_high, int T, int K, int N,
                      int nnz, int flags, void* workspace, size_t workspace_bytes, void* stream) {
+  begin_call();
   CHECK_ARG(Y_high && scale_x, "NULL tensor pointer");
   {
     // block-rows without blocks are never visited by the kernel: they are zero
@@ -717,7 +832,7 @@ int w4a4_sparse_gemm(const void* W_high, const int32_t* hp_row_offsets, const in
   a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.X_s4 = X_s4; a.scale_u4 = scale_u4; a.scale_x = scale_x; a.Y = Y_high;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
-  a.do_dense = false; a.sparse_weight = 1.f; a.pdl = false;
+  a.do_dense = false; a.sparse_weight = 1.f;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
   return run_gemm(a);
 }
@@ -737,6 +852,7 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
                                            const int32_t* hp_col_indices, const void* scale_u4, const void* zero_u4,
                                            void* Y, int T, int K, int N, int nnz, int flags, void* workspace,
                                            size_t workspace_bytes, void* stream) {
+  begin_call();
   int rc = check_common(T, K, N, nnz);
   if (rc) return rc;
   CHECK_ARG(X && Y && zero_u4, "NULL tensor pointer");
@@ -757,7 +873,11 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
   const bool tensor = wants_tensor_path(T, K, N, flags, dev->sm_count, has_prepared(a));
   if (!tensor || !has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
   // the tensor-core kernel reads e4m3 codes when it runs fp8 MMAs (prepared weights), s8 codes otherwise
+#ifdef W4A4_F8_ON_PACKED
   static const bool env_f8 = getenv("W4A4_PREFILL_F8") && atoi(getenv("W4A4_PREFILL_F8")) != 0;
+#else
+  const bool env_f8 = false;
+#endif
   a.xe_fmt = (tensor && (has_prepared(a) || env_f8)) ? 1 : 0;
   rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
                     T, K, s, dev->sm_count, a.xe_fmt);
@@ -765,7 +885,7 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
   a.XE = ws + wl.xe; a.sumxf = reinterpret_cast<float*>(ws + wl.sumxf); a.scale_u4 = scale_u4; a.zero_u4 = zero_u4;
   a.scale_x = ws + wl.scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
-  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = true;
+  a.do_dense = true; a.sparse_weight = 16.f;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = s;
   return run_gemm(a);
 }
@@ -782,13 +902,14 @@ int w4a4_dump_accumulators_prepared(const void* W_low, const void* W_high, const
                                     const int32_t* hp_col_indices, const void* X_s4, int32_t* acc, int32_t* acc_hi,
                                     int T, int K, int N, int nnz, int flags, void* workspace, size_t workspace_bytes,
                                     void* stream) {
+  begin_call();
   CHECK_ARG(acc || acc_hi, "both outputs are NULL");
   GemmArgs a{};
   a.W_low_prep = acc ? W_low_prepared : nullptr; a.W_high_prep = (acc_hi && nnz > 0) ? W_high_prepared : nullptr;
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.X_s4 = X_s4; a.acc_dump = acc; a.acc_hi_dump = acc_hi;
   a.T = T; a.K = K; a.N = N; a.nnz = acc_hi ? nnz : 0; a.flags = flags;
-  a.do_dense = acc != nullptr; a.sparse_weight = 16.f; a.pdl = false;
+  a.do_dense = acc != nullptr; a.sparse_weight = 16.f;
   a.ws = workspace; a.ws_bytes = workspace_bytes; a.stream = static_cast<cudaStream_t>(stream);
   return run_gemm(a);
 }
@@ -797,6 +918,7 @@ int w4a4_fused_dense_sparse_noalloc(const void* W_low, const void* W_high, const
                                     const int32_t* hp_col_indices, const void* X_s4, const void* scale_u4,
                                     const void* zero_u4, const int32_t* sum_X, const void* scale_x, void* Y, int T,
                                     int K, int N, int nnz, int flags, void* stream) {
+  begin_call();
   int rc = check_common(T, K, N, nnz);
   if (rc) return rc;
   CHECK_ARG(Y && X_s4 && zero_u4 && sum_X && scale_x, "NULL tensor pointer");
@@ -806,6 +928,9 @@ int w4a4_fused_dense_sparse_noalloc(const void* W_low, const void* W_high, const
                 "use w4a4_fused_dense_sparse with a caller-provided workspace",
                 T, K, NOALLOC_MAX_T, NOALLOC_MAX_K);
   if (!aligned(X_s4, 4)) return fail(W4A4_ERR_ALIGNMENT, "X_s4 must be 4-byte aligned");
+  // this entry point always runs the weight-streaming kernel on s8 codes it expands itself
+  CHECK_ARG((flags & (W4A4_FLAG_FORCE_TENSOR | W4A4_FLAG_CODES_E4M3)) == 0,
+            "w4a4_fused_dense_sparse_noalloc accepts neither W4A4_FLAG_FORCE_TENSOR nor W4A4_FLAG_CODES_E4M3");
   void* scratch = nullptr;
   rc = noalloc_scratch_address(&scratch);      // first call on a device resolves the address
   if (rc) return rc;
@@ -828,7 +953,7 @@ int w4a4_fused_dense_sparse_noalloc(const void* W_low, const void* W_high, const
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.XE = xe; a.sumxf = sums; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.scale_x = scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags | W4A4_FLAG_FORCE_STREAM;
-  a.do_dense = true; a.sparse_weight = 16.f; a.pdl = true;
+  a.do_dense = true; a.sparse_weight = 16.f;
   a.ws = nullptr; a.ws_bytes = 0; a.stream = s;
   return run_gemm(a);
 }

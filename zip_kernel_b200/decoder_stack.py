@@ -28,7 +28,7 @@ from typing import List
 import torch
 import torch.nn.functional as F
 
-from . import synth
+from . import _lib, synth
 from .pack_utils import V9WeightContainer
 from .v9_linear import prepare_for_prefill, v9_linear_forward
 
@@ -176,9 +176,10 @@ def run(cfg: StackConfig, batch: int, prefill_len: int, decode_steps: int, devic
         out = torch.empty_like(tok)
         produced = [nxt.clone()]
         graph = None
+        scratch = _lib.WorkspaceHolder()      # the captured step writes scratch of its own, alive as long as the graph
         if use_graph:
             side = torch.cuda.Stream()
-            with torch.cuda.stream(side):
+            with _lib.use_workspace(scratch), torch.cuda.stream(side):
                 stack.decode_step(tok, pos, max_len)           # warm-up on the capture stream (scratch is per stream)
                 torch.cuda.synchronize()
                 graph = torch.cuda.CUDAGraph()

@@ -18,6 +18,7 @@ from typing import Optional, Tuple
 import torch
 
 from . import _lib
+from .nvtx_shim import traced
 from .pack_utils import BCOL, BROW
 
 _L = _lib.load()
@@ -33,6 +34,7 @@ def reserve_workspace(device, T: int, d_in: int, d_out: int, n_hp_blocks: int = 
 # activation_quant   (reference: cuda_kernel/ops.py:223-260)
 # ---------------------------------------------------------------------------
 
+@traced("cuda.activation_quant")
 def activation_quant_cuda(
     X_fp16: torch.Tensor,
     perm: torch.Tensor,
@@ -54,7 +56,9 @@ def activation_quant_cuda(
         raise ValueError(f"bcol must be {BCOL}, got {bcol}")
     if D % bcol != 0:
         raise ValueError(f"d_in ({D}) must be divisible by bcol ({bcol})")
-    X_2d = X_fp16.reshape(T, D).contiguous()
+    X_2d = X_fp16.reshape(T, D)
+    if X_2d.stride(-1) != 1 or (T > 1 and X_2d.stride(0) < D):
+        X_2d = X_2d.contiguous()          # row-strided inputs (a column slice of a wider tensor) go to the kernel as they are
     perm_i32 = perm.to(device=X_2d.device, dtype=torch.int32).contiguous()
     dev = X_2d.device
     X_s4 = torch.empty((T, D // 2), dtype=torch.int8, device=dev)
@@ -64,7 +68,7 @@ def activation_quant_cuda(
         return X_s4, scale_x, sum_X
     with torch.cuda.device(dev):
         _lib.check(_L.w4a4_activation_quant(
-            X_2d.data_ptr(), X_2d.stride(0), perm_i32.data_ptr(), X_s4.data_ptr(),
+            X_2d.data_ptr(), X_2d.stride(0) if T > 1 else D, perm_i32.data_ptr(), X_s4.data_ptr(),
             scale_x.data_ptr(), sum_X.data_ptr(), int(T), int(D), _lib.stream_ptr(dev),
         ), "activation_quant")
     return X_s4, scale_x, sum_X
@@ -108,6 +112,7 @@ def _out(d_out: int, T: int, device, token_major: bool) -> torch.Tensor:
     return torch.empty(shape, dtype=torch.float16, device=device)
 
 
+@traced("cuda.dense_gemm")
 def dense_gemm_cuda_int4(W_low_packed, X_s4, scale_u4, zero_u4, sum_X, scale_x,
                          *, token_major: bool = False, force: Optional[str] = None) -> torch.Tensor:
     """Dense u4 x s4 GEMM: ``Y_low (d_out, T)`` fp16 (ops.py:314-320)."""
@@ -136,6 +141,7 @@ def dense_gemm_cuda_int8(*args, **kwargs):
     )
 
 
+@traced("cuda.sparse_gemm")
 def sparse_gemm_cuda_int4(W_high_blocks_packed, hp_row_offsets, hp_col_indices,
                           X_s4, scale_u4, scale_x, d_out, d_in,
                           *, token_major: bool = False, force: Optional[str] = None) -> torch.Tensor:
@@ -234,6 +240,7 @@ def _prepared_ptrs(prepared, W, Wh, nnz):
     return lo.data_ptr(), (hi.data_ptr() if nnz else None)
 
 
+@traced("cuda.fused_dense_sparse")
 def fused_dense_sparse_cuda_int4(
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
     X_s4, scale_u4, zero_u4, sum_X, scale_x, d_out, d_in,
@@ -286,8 +293,9 @@ def fused_dense_sparse_expanded_cuda(
 ) -> torch.Tensor:
     """:func:`fused_dense_sparse_cuda_int4` on activations already expanded by
     :func:`expand_activations_cuda`; a single kernel launch.  ``e4m3=True`` says that ``XE``
-    was expanded with ``e4m3=True`` (many-token calls only: fp8 MMAs instead of integer ones);
-    ``prepared`` weights imply it."""
+    was expanded with ``e4m3=True``; such codes go with ``prepared`` weights and always run the
+    tensor-core kernel.  ``prepared`` weights with s8 codes (``e4m3=False``) raise ``ValueError``:
+    the bytes of ``XE`` are never reinterpreted silently."""
     d_out, d_in = int(d_out), int(d_in)
     T = int(scale_x.shape[0])
     assert XE.is_cuda and XE.dtype == torch.int8 and XE.is_contiguous()
@@ -326,6 +334,7 @@ def fused_dense_sparse_cuda_int8(*args, **kwargs):
     )
 
 
+@traced("cuda.fused_dense_sparse_e2e")
 def fused_dense_sparse_e2e_cuda(
     X_fp16, perm,
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
@@ -381,6 +390,7 @@ def fused_quant_gemv_cuda(
                                        hp_row_offsets, hp_col_indices, scale_u4, zero_u4, d_out, d_in)
 
 
+@traced("cuda.fused_quant_dense_sparse")
 def fused_quant_dense_sparse_cuda_int4(
     X_fp16, perm,
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,

@@ -75,6 +75,25 @@ int w4a4_selftest_bounded_wait(int polls, void* stream);
 int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4,
                           void* scale_x, int32_t* sum_X, int T, int K, void* stream);
 
+/* Quantisation fused with the element-wise step that precedes it in a decoder layer, so that the
+ * intermediate fp16 activations never travel through memory and a linear costs two launches (this
+ * one and the GEMM on the expanded codes).  They remove the seam the reference leaves between its
+ * PyTorch glue and activation_quant (triton_kernel/v9_linear.py:106-170 on the output side; on the
+ * input side the reference has no fused form).  Outputs as w4a4_activation_quant (X_s4 + sum_X,
+ * may both be NULL) and/or the expanded layout (XE + sumxf, may both be NULL; code_format as
+ * w4a4_expand_activations_fmt; sizes from w4a4_expanded_codes_bytes / _sums_bytes; sumxf must be
+ * zero-initialised when T is not a multiple of 16); scale_x always.
+ *
+ * w4a4_rmsnorm_quant quantises  y[t,k] = fp16( fp16( x[t,k] * r[t] ) * w[k] ),
+ *   r[t] = 1 / sqrt( fp32( sum_k x[t,k]^2 / K ) + eps )   (sum exact, IEEE sqrt and division).
+ * w4a4_silu_mul_quant reads rows [gate (K) | up (K)] (ldgu >= 2K) and quantises
+ *   y[t,k] = fp16( fp16( silu(gate[t,k]) ) * up[t,k] ),  silu(g) = g / (1 + exp(-g)). */
+int w4a4_rmsnorm_quant(const void* X, long long ldx, const void* norm_weight, float eps, const int32_t* perm,
+                       void* X_s4, void* scale_x, int32_t* sum_X, void* XE, float* sumxf, int code_format, int T,
+                       int K, void* stream);
+int w4a4_silu_mul_quant(const void* GU, long long ldgu, const int32_t* perm, void* X_s4, void* scale_x,
+                        int32_t* sum_X, void* XE, float* sumxf, int code_format, int T, int K, void* stream);
+
 /* Scratch bytes the GEMM entry points below need for (T, K, N, nnz); the same
  * size serves all of them.  The scratch holds the activations in the layout the
  * kernels read (expanded codes, transposed group sums, and the per-token scales

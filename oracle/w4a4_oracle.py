@@ -372,6 +372,31 @@ def v9_linear_fakequant(X_fp16, W: dict):
 # the timed CPU baseline: the reference's own CPU path, multi-threaded
 # ---------------------------------------------------------------------------
 
+def rmsnorm_fp16(X_fp16: np.ndarray, weight_fp16: np.ndarray, eps: float) -> np.ndarray:
+    """fp16 RMSNorm as a decoder layer applies it before a quantised linear:
+    ``y = fp16(fp16(x * r) * w)`` with ``r = 1 / sqrt(fp32(mean(x^2)) + eps)`` in fp32 (the PyTorch
+    composition ``(x.float() * rsqrt(x.float().pow(2).mean(-1) + eps)).half() * w`` with the mean taken
+    exactly and IEEE square root / division).  The reference has no fused form of this step; this is
+    the definition the fused RMSNorm + quantisation kernel is checked against, bit for bit."""
+    X = np.asarray(X_fp16, dtype=np.float16)
+    x64 = X.astype(np.float64)
+    ms = ((x64 * x64).sum(axis=-1) / X.shape[-1]).astype(np.float32)
+    r = (np.float32(1.0) / np.sqrt(ms + np.float32(eps), dtype=np.float32)).astype(np.float32)
+    xn = (X.astype(np.float32) * r[..., None]).astype(np.float16)
+    return (xn.astype(np.float32) * np.asarray(weight_fp16, dtype=np.float16).astype(np.float32)).astype(np.float16)
+
+
+def silu_mul_fp16(gate_fp16: np.ndarray, up_fp16: np.ndarray) -> np.ndarray:
+    """The gated activation ahead of the down projection, ``fp16(fp16(silu(gate)) * up)`` with
+    ``silu(g) = g / (1 + exp(-g))`` evaluated in double precision and rounded to fp32, then fp16 (the
+    PyTorch composition ``F.silu(gate) * up`` on fp16 tensors, made independent of the accuracy of a
+    single-precision exponential)."""
+    g = np.asarray(gate_fp16, dtype=np.float16).astype(np.float64)
+    with np.errstate(over="ignore"):
+        s = (g / (1.0 + np.exp(-g))).astype(np.float32).astype(np.float16)
+    return (s.astype(np.float32) * np.asarray(up_fp16, dtype=np.float16).astype(np.float32)).astype(np.float16)
+
+
 def cpu_reference_path(X_fp16_t, perm_t, Wt: dict):
     """The reference's CPU route for one linear, on torch CPU tensors with all
     host threads: ``quantize_activation_s4_reference`` followed by

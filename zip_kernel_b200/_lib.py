@@ -31,6 +31,8 @@ SIGNATURES = {
     "w4a4_device_error": (_INT, [_c.POINTER(_INT), _PTR]),
     "w4a4_selftest_bounded_wait": (_INT, [_INT, _PTR]),
     "w4a4_activation_quant": (_INT, [_PTR, _LL, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _PTR]),
+    "w4a4_rmsnorm_quant": (_INT, [_PTR, _LL, _PTR, _c.c_float] + [_PTR] * 6 + [_INT, _INT, _INT, _PTR]),
+    "w4a4_silu_mul_quant": (_INT, [_PTR, _LL] + [_PTR] * 6 + [_INT, _INT, _INT, _PTR]),
     "w4a4_workspace_bytes": (_SZ, [_INT, _INT, _INT, _INT]),
     "w4a4_fused_dense_sparse": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_expanded_codes_bytes": (_SZ, [_INT, _INT]),

@@ -44,7 +44,58 @@ struct QuantParams {
   int C;                  // CTAs (cluster size) per token; divides K/128
   int stage_row;          // 1: perm given, C == 1: the dynamic shared memory holds the raw row, gathered while quantising
   int fmt;                // bytes of XE: 0 = s8 codes (even/odd order), 1 = e4m3 encodings in natural order (see expand_word)
+  // Fused prologues (SRC template parameter of the kernel): the value that is quantised is a function of the input row.
+  const __half* norm_w;   // SRC_RMSNORM: (K) fp16 weight of the normalisation
+  float eps;              // SRC_RMSNORM: added to the mean square
 };
+
+// What the quantiser reads.  SRC_PLAIN: X itself.  SRC_RMSNORM: fp16(fp16(x * r) * w[k]) with
+// r = 1 / sqrt(mean(x^2) + eps) - the fp16 RMSNorm of a decoder layer, so that normalisation and
+// quantisation are one launch and the normalised activations never travel through memory.
+// SRC_SILU_MUL: the row holds [gate (K) | up (K)] (row stride ldx >= 2K) and the value is
+// fp16(fp16(silu(gate)) * up) - the gated activation that feeds the down projection.
+enum : int { SRC_PLAIN = 0, SRC_RMSNORM = 1, SRC_SILU_MUL = 2 };
+
+// silu(x) = x / (1 + exp(-x)), rounded once to fp32 and then to fp16.  Evaluated in double precision so that
+// the result does not depend on the accuracy of a single-precision exponential: a CPU restatement with
+// a correctly rounded exp gives the same fp16 bits (the two can only differ when the double result lies
+// within 2^-40 of an fp16 rounding boundary).
+__device__ __forceinline__ __half silu_fp16(__half g) {
+  const double x = (double)__half2float(g);
+  return __float2half_rn((float)(x / (1.0 + exp(-x))));
+}
+// fp16 product of two fp16 values: exact in fp32 (two 11-bit significands), one rounding
+__device__ __forceinline__ __half mul_fp16(__half a, __half b) {
+  return __float2half_rn(__half2float(a) * __half2float(b));
+}
+template <int SRC>
+__device__ __forceinline__ __half transform1(const QuantParams& p, const __half* xrow, int k, float rinv) {
+  const __half x = xrow[k];
+  if (SRC == SRC_RMSNORM) return mul_fp16(__float2half_rn(__half2float(x) * rinv), p.norm_w[k]);
+  if (SRC == SRC_SILU_MUL) return mul_fp16(silu_fp16(x), xrow[p.K + k]);
+  return x;
+}
+// the same for the 8 consecutive columns 8c .. 8c + 7 of a 16-byte aligned row
+template <int SRC>
+__device__ __forceinline__ uint4 transform8(const QuantParams& p, const __half* xrow, int c, float rinv) {
+  uint4 v = ld_plain(reinterpret_cast<const uint4*>(xrow) + c);
+  if (SRC == SRC_PLAIN) return v;
+  __half* h = reinterpret_cast<__half*>(&v);
+  if (SRC == SRC_RMSNORM) {
+    const bool wv = (reinterpret_cast<uintptr_t>(p.norm_w) & 15) == 0;
+    uint4 w4 = wv ? ld_plain(reinterpret_cast<const uint4*>(p.norm_w) + c) : make_uint4(0, 0, 0, 0);
+    const __half* w = reinterpret_cast<const __half*>(&w4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = mul_fp16(__float2half_rn(__half2float(h[j]) * rinv), wv ? w[j] : p.norm_w[c * 8 + j]);
+  } else {
+    const bool uv = ((reinterpret_cast<uintptr_t>(xrow + p.K)) & 15) == 0;
+    uint4 u4 = uv ? ld_plain(reinterpret_cast<const uint4*>(xrow + p.K) + c) : make_uint4(0, 0, 0, 0);
+    const __half* u = reinterpret_cast<const __half*>(&u4);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) h[j] = mul_fp16(silu_fp16(h[j]), uv ? u[j] : xrow[p.K + c * 8 + j]);
+  }
+  return v;
+}
 
 // One packed word (8 codes) -> 8 bytes.  fmt 0: sign-extended s8, its four even-indexed codes, then its
 // four odd-indexed ones (the order the s8 widening of the weights produces).  fmt 1: e4m3 encodings in the
@@ -102,7 +153,7 @@ __device__ __forceinline__ int quant_code(float x, float s, float r) {
 // (programmatic dependent launch) - after it has fetched the thread's first
 // permutation indices, which belong to the weights and do not depend on that
 // kernel: the dependent part of the load phase is then one global round trip.
-template <int NTHREADS, bool WAIT_DEP>
+template <int NTHREADS, bool WAIT_DEP, int SRC = SRC_PLAIN>
 __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int rank, unsigned char* quant_smem,
                                             float* warp_max, float* peer_max) {
   constexpr int QUANT_THREADS = NTHREADS;
@@ -132,11 +183,45 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
   if (p.perm != nullptr && c_lo + tid < c_hi) load_perm(c_lo + tid, pa, pb);
   if (WAIT_DEP) grid_dependency_wait();
 
+  float rinv = 1.f;
+  if (SRC == SRC_RMSNORM) {
+    // Mean square of the WHOLE row (every CTA of a token's cluster reads it: a few KB from L2), summed in
+    // double precision - the squares of fp16 values are exact there and the sum's rounding error is far
+    // below the fp32 rounding that follows - then r = 1 / sqrt(fp32(mean) + eps) with IEEE operations.
+    __shared__ double warp_ss[NTHREADS / 32];
+    double ss = 0.0;
+    if (p.vec_ok) {
+      const uint4* src = reinterpret_cast<const uint4*>(xrow);
+      for (int c = tid; c < nchunk_row; c += QUANT_THREADS) {
+        const uint4 v = ld_plain(src + c);
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(h[i]);
+          ss += (double)(f.x * f.x) + (double)(f.y * f.y);
+        }
+      }
+    } else {
+      for (int k = tid; k < p.K; k += QUANT_THREADS) {
+        const float f = __half2float(xrow[k]);
+        ss += (double)(f * f);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((tid & 31) == 0) warp_ss[tid >> 5] = ss;
+    __syncthreads();
+    ss = 0.0;
+#pragma unroll
+    for (int w = 0; w < NTHREADS / 32; ++w) ss += warp_ss[w];
+    const float ms = (float)(ss / (double)p.K);
+    rinv = __frcp_rn(__fsqrt_rn(__fadd_rn(ms, p.eps)));
+  }
+
   float m = 0.f;
   if (p.perm == nullptr && p.vec_ok) {
-    const uint4* src = reinterpret_cast<const uint4*>(xrow);
     for (int c = c_lo + tid; c < c_hi; c += QUANT_THREADS) {
-      uint4 v = ld_plain(src + c);
+      uint4 v = transform8<SRC>(p, xrow, c, rinv);
       row[c - c_lo] = v;
       m = half_abs_max8(v, m);
     }
@@ -148,15 +233,14 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
     // costs a second, dependent round trip and one L1 wavefront per element.)
     __half* raw = reinterpret_cast<__half*>(row);
     if (p.vec_ok) {
-      const uint4* src = reinterpret_cast<const uint4*>(xrow);
       for (int c = tid; c < nchunk_row; c += QUANT_THREADS) {
-        const uint4 v = ld_plain(src + c);
+        const uint4 v = transform8<SRC>(p, xrow, c, rinv);
         row[c] = v;
         m = half_abs_max8(v, m);
       }
     } else {
       for (int k = tid; k < p.K; k += QUANT_THREADS) {
-        const __half x = xrow[k];
+        const __half x = transform1<SRC>(p, xrow, k, rinv);
         raw[k] = x;
         m = fmaxf(m, fabsf(__half2float(x)));
       }
@@ -166,11 +250,12 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
       __align__(16) __half h[8];
       if (p.perm) {
         if (c != c_lo + tid) load_perm(c, pa, pb);
-        h[0] = xrow[pa.x]; h[1] = xrow[pa.y]; h[2] = xrow[pa.z]; h[3] = xrow[pa.w];
-        h[4] = xrow[pb.x]; h[5] = xrow[pb.y]; h[6] = xrow[pb.z]; h[7] = xrow[pb.w];
+        const int idx[8] = {pa.x, pa.y, pa.z, pa.w, pb.x, pb.y, pb.z, pb.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) h[j] = transform1<SRC>(p, xrow, idx[j], rinv);
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) h[j] = xrow[c * 8 + j];
+        for (int j = 0; j < 8; ++j) h[j] = transform1<SRC>(p, xrow, c * 8 + j, rinv);
       }
       uint4 v = *reinterpret_cast<uint4*>(h);
       row[c - c_lo] = v;
@@ -255,7 +340,7 @@ __device__ __forceinline__ void quant_token(const QuantParams& p, int t, int ran
 // NT threads per CTA: 256 when a token is spread over a cluster or few tokens are in flight (latency), 128 when
 // there are many tokens (throughput: a thread's set-up - permutation indices, address arithmetic, the
 // reductions - is then shared by twice as many elements and twice as many CTAs fit an SM).
-template <int NT>
+template <int NT, int SRC = SRC_PLAIN>
 __global__ void __launch_bounds__(NT)
 act_quant_kernel(const QuantParams p) {
   extern __shared__ __align__(16) unsigned char quant_dyn_smem[];
@@ -266,7 +351,7 @@ act_quant_kernel(const QuantParams p) {
   // (the wait for the producer of X and for every earlier user of the output buffers happens inside)
   grid_launch_dependents();
   const int t = blockIdx.x / p.C;
-  quant_token<NT, true>(p, t, blockIdx.x - t * p.C, quant_dyn_smem, warp_max, peer_max);
+  quant_token<NT, true, SRC>(p, t, blockIdx.x - t * p.C, quant_dyn_smem, warp_max, peer_max);
 }
 
 // Builds the expanded layout and the transposed float group sums from already

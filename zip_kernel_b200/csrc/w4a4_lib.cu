@@ -82,6 +82,10 @@ cudaError_t set_kernel_attributes() {
 #endif
   set(act_quant_kernel<128>, QUANT_MAX_SMEM);
   set(act_quant_kernel<QUANT_THREADS>, QUANT_MAX_SMEM);
+  set(act_quant_kernel<128, SRC_RMSNORM>, QUANT_MAX_SMEM);
+  set(act_quant_kernel<QUANT_THREADS, SRC_RMSNORM>, QUANT_MAX_SMEM);
+  set(act_quant_kernel<128, SRC_SILU_MUL>, QUANT_MAX_SMEM);
+  set(act_quant_kernel<QUANT_THREADS, SRC_SILU_MUL>, QUANT_MAX_SMEM);
   return e;
 }
 
@@ -479,10 +483,13 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
 }
 
 int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, void* scale_x, int32_t* sum_X,
-                 void* XE, float* sumxf, int T, int K, cudaStream_t stream, int sm_count, int xe_fmt = 0) {
+                 void* XE, float* sumxf, int T, int K, cudaStream_t stream, int sm_count, int xe_fmt = 0,
+                 int src = w4a4::SRC_PLAIN, const void* norm_w = nullptr, float eps = 0.f) {
   using namespace w4a4;
   QuantParams q;
   q.fmt = xe_fmt;
+  q.norm_w = static_cast<const __half*>(norm_w);
+  q.eps = eps;
   q.X = static_cast<const __half*>(X);
   q.ldx = ldx;
   q.perm = perm;
@@ -509,7 +516,10 @@ int launch_quant(const void* X, long long ldx, const int32_t* perm, void* X_s4, 
   static const int env_nt = getenv("W4A4_QUANT_THREADS") ? atoi(getenv("W4A4_QUANT_THREADS")) : 0;
   // (measured, 8192 tokens: K = 4096 54 -> 44 us; K = 14336, where shared memory limits an SM to three CTAs, 194 -> 235 us)
   const bool small_cta = env_nt ? env_nt == 128 : (C == 1 && T >= 4 * sm_count && smem <= 32 * 1024);
-  void (*kern)(const QuantParams) = small_cta ? act_quant_kernel<128> : act_quant_kernel<QUANT_THREADS>;
+  void (*kern)(const QuantParams) =
+      src == SRC_RMSNORM    ? (small_cta ? act_quant_kernel<128, SRC_RMSNORM> : act_quant_kernel<QUANT_THREADS, SRC_RMSNORM>)
+      : src == SRC_SILU_MUL ? (small_cta ? act_quant_kernel<128, SRC_SILU_MUL> : act_quant_kernel<QUANT_THREADS, SRC_SILU_MUL>)
+                            : (small_cta ? act_quant_kernel<128> : act_quant_kernel<QUANT_THREADS>);
   cudaError_t e = launch_ex(kern, dim3((unsigned)((long long)T * C)), dim3(small_cta ? 128 : QUANT_THREADS), smem, stream, C, q);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "quant kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
@@ -678,6 +688,46 @@ int w4a4_activation_quant(const void* X, long long ldx, const int32_t* perm, voi
   if (rc) return rc;
   return launch_quant(X, ldx, perm, X_s4, scale_x, sum_X, nullptr, nullptr, T, K, static_cast<cudaStream_t>(stream),
                       dev->sm_count);
+}
+
+namespace {
+int fused_prologue_quant(int src, const void* X, long long ldx, long long min_ld, const void* norm_w, float eps,
+                         const int32_t* perm, void* X_s4, void* scale_x, int32_t* sum_X, void* XE, float* sumxf,
+                         int code_format, int T, int K, void* stream) {
+  int rc = check_common(T, K, 1, 0);
+  if (rc) return rc;
+  CHECK_ARG(code_format == W4A4_CODES_S8 || code_format == W4A4_CODES_E4M3, "unknown code format %d", code_format);
+  CHECK_ARG(X && scale_x, "NULL tensor pointer");
+  CHECK_ARG((X_s4 != nullptr) == (sum_X != nullptr), "X_s4 and sum_X go together");
+  CHECK_ARG((XE != nullptr) == (sumxf != nullptr), "XE and sumxf go together");
+  CHECK_ARG(X_s4 || XE, "no output requested: pass X_s4 + sum_X, XE + sumxf, or both");
+  CHECK_ARG(ldx >= min_ld, "row stride (%lld) must be >= %lld", ldx, min_ld);
+  if (!aligned(X, 2) || !aligned(X_s4, 4) || !aligned(sum_X, 4) || !aligned(scale_x, 2) || !aligned(XE, 16) ||
+      !aligned(sumxf, 16) || !aligned(norm_w, 2))
+    return fail(W4A4_ERR_ALIGNMENT, "pointer alignment");
+  DeviceInfo* dev = nullptr;
+  rc = current_device(&dev);
+  if (rc) return rc;
+  return launch_quant(X, ldx, perm, X_s4, scale_x, sum_X, XE, sumxf, T, K, static_cast<cudaStream_t>(stream),
+                      dev->sm_count, code_format, src, norm_w, eps);
+}
+}  // namespace
+
+int w4a4_rmsnorm_quant(const void* X, long long ldx, const void* norm_weight, float eps, const int32_t* perm,
+                       void* X_s4, void* scale_x, int32_t* sum_X, void* XE, float* sumxf, int code_format, int T,
+                       int K, void* stream) {
+  begin_call();
+  CHECK_ARG(norm_weight != nullptr, "norm_weight is NULL");
+  CHECK_ARG(eps >= 0.f, "eps must be >= 0");
+  return fused_prologue_quant(w4a4::SRC_RMSNORM, X, ldx, K, norm_weight, eps, perm, X_s4, scale_x, sum_X, XE, sumxf,
+                              code_format, T, K, stream);
+}
+
+int w4a4_silu_mul_quant(const void* GU, long long ldgu, const int32_t* perm, void* X_s4, void* scale_x,
+                        int32_t* sum_X, void* XE, float* sumxf, int code_format, int T, int K, void* stream) {
+  begin_call();
+  return fused_prologue_quant(w4a4::SRC_SILU_MUL, GU, ldgu, 2LL * K, nullptr, 0.f, perm, X_s4, scale_x, sum_X, XE,
+                              sumxf, code_format, T, K, stream);
 }
 
 size_t w4a4_workspace_bytes(int T, int K, int N, int nnz) {

@@ -30,7 +30,8 @@ import torch.nn.functional as F
 
 from . import _lib, synth
 from .pack_utils import V9WeightContainer
-from .v9_linear import prepare_for_prefill, v9_linear_forward
+from .v9_linear import (prepare_for_prefill, v9_linear_forward, v9_linear_forward_rmsnorm,
+                        v9_linear_forward_silu_mul)
 
 
 @dataclass
@@ -86,8 +87,12 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
 class DecoderStack:
     """Weights, KV cache and the two phases (prefill of a prompt batch, one decode step)."""
 
-    def __init__(self, cfg: StackConfig, batch: int, max_len: int, device, seed: int = 0, prepared: bool = True):
+    def __init__(self, cfg: StackConfig, batch: int, max_len: int, device, seed: int = 0, prepared: bool = True,
+                 fused_seams: bool = True):
         self.cfg, self.batch, self.max_len, self.device = cfg, batch, max_len, device
+        # fused_seams: RMSNorm and SiLU * mul run inside the quantisation launch of the linear they feed
+        # (v9_linear_forward_rmsnorm / _silu_mul) instead of as separate PyTorch kernels
+        self.fused_seams = fused_seams
         h, kv = cfg.hidden, cfg.n_kv_heads * cfg.head_dim
         shapes = [(h, h + 2 * kv), (h, h), (h, 2 * cfg.ffn), (cfg.ffn, h)]             # (d_in, d_out)
         protos: List[V9WeightContainer] = [
@@ -111,7 +116,10 @@ class DecoderStack:
         cfg, L = self.cfg, self.layers[li]
         B = x.shape[0]
         hd, nh, nkv = cfg.head_dim, cfg.n_heads, cfg.n_kv_heads
-        qkv = v9_linear_forward(rms_norm(x, L.norm1, cfg.rms_eps), L.qkv)
+        if self.fused_seams:
+            qkv = v9_linear_forward_rmsnorm(x, L.norm1, cfg.rms_eps, L.qkv)
+        else:
+            qkv = v9_linear_forward(rms_norm(x, L.norm1, cfg.rms_eps), L.qkv)
         q, k, v = qkv.split([nh * hd, nkv * hd, nkv * hd], dim=-1)
         q = q.view(B, S, nh, hd)
         k = k.view(B, S, nkv, hd)
@@ -134,6 +142,9 @@ class DecoderStack:
             mask = (torch.arange(attend_len, device=x.device) <= pos).view(1, 1, 1, attend_len)
             att = F.scaled_dot_product_attention(q.transpose(1, 2), keys, vals, attn_mask=mask, enable_gqa=True)
         x = x + v9_linear_forward(att.transpose(1, 2).reshape(B, S, nh * hd), L.o)
+        if self.fused_seams:
+            gu = v9_linear_forward_rmsnorm(x, L.norm2, cfg.rms_eps, L.gate_up)
+            return x + v9_linear_forward_silu_mul(gu, L.down)
         gu = v9_linear_forward(rms_norm(x, L.norm2, cfg.rms_eps), L.gate_up)
         gate, up = gu.split(cfg.ffn, dim=-1)
         return x + v9_linear_forward(F.silu(gate) * up, L.down)
@@ -157,9 +168,9 @@ class DecoderStack:
 
 
 def run(cfg: StackConfig, batch: int, prefill_len: int, decode_steps: int, device, use_graph: bool = True, seed: int = 0,
-        prepared: bool = True):
+        prepared: bool = True, fused_seams: bool = True):
     max_len = prefill_len + decode_steps
-    stack = DecoderStack(cfg, batch, max_len, device, seed, prepared)
+    stack = DecoderStack(cfg, batch, max_len, device, seed, prepared, fused_seams)
     g = torch.Generator().manual_seed(seed + 2)
     prompt = torch.randint(0, cfg.vocab, (batch, prefill_len), generator=g).to(device)
 
@@ -207,7 +218,8 @@ def run(cfg: StackConfig, batch: int, prefill_len: int, decode_steps: int, devic
                    "vocab": cfg.vocab, "batch": batch, "prefill": prefill_len, "decode_steps": decode_steps,
                    "w4a4_linears_per_layer": "qkv, o, gate_up, down (7 projections)", "residual_density": cfg.density,
                    "decode_step": "CUDA graph" if use_graph else "eager",
-                   "prefill_weights": "prepared e4m3 copy" if prepared else "packed"},
+                   "prefill_weights": "prepared e4m3 copy" if prepared else "packed",
+                   "seams": "RMSNorm and SiLU*mul fused into the quantisation launches" if fused_seams else "PyTorch RMSNorm / SiLU*mul"},
         "last_tokens": [int(t) for t in produced[-1][:4].tolist()],
     }
 
@@ -220,11 +232,12 @@ def main():
     ap.add_argument("--decode", type=int, default=128)
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-prepared", action="store_true", help="prompt processing on the packed weights")
+    ap.add_argument("--no-fused-seams", action="store_true", help="RMSNorm and SiLU*mul as separate PyTorch kernels")
     a = ap.parse_args()
     device = torch.device("cuda", 0)
     torch.cuda.set_device(device)
     res = run(StackConfig(n_layers=a.layers), a.batch, a.prefill, a.decode, device, use_graph=not a.no_graph,
-              prepared=not a.no_prepared)
+              prepared=not a.no_prepared, fused_seams=not a.no_fused_seams)
     print(json.dumps(res), flush=True)
 
 

@@ -75,6 +75,88 @@ def activation_quant_cuda(
 
 
 # ---------------------------------------------------------------------------
+# quantisation fused with the element-wise step in front of it (no counterpart in the
+# reference, whose layers run RMSNorm / SiLU*mul as separate PyTorch launches)
+# ---------------------------------------------------------------------------
+
+def perm_or_none(perm: torch.Tensor, cache_on=None):
+    """``None`` when ``perm`` is the identity (the kernels then read rows with 128-bit loads instead of
+    gathering), else ``perm`` as contiguous int32.  The check synchronises once; pass the object that
+    owns ``perm`` (a weight container) as ``cache_on`` to remember the answer there."""
+    if cache_on is not None and getattr(cache_on, "_perm_arg", None) is not None:
+        tag, val = cache_on._perm_arg
+        if tag == perm.data_ptr():
+            return val
+    p32 = perm.to(torch.int32).contiguous()
+    ident = bool(torch.equal(p32, torch.arange(p32.numel(), dtype=torch.int32, device=p32.device)))
+    val = None if ident else p32
+    if cache_on is not None:
+        cache_on._perm_arg = (perm.data_ptr(), val)
+    return val
+
+
+def _fused_prologue(which: str, X2: torch.Tensor, K: int, perm, norm_weight, eps: float, expanded: bool, e4m3: bool):
+    T = int(X2.shape[0])
+    dev = X2.device
+    scale_x = torch.empty((T,), dtype=torch.float16, device=dev)
+    if expanded:
+        XE = torch.empty((int(_L.w4a4_expanded_codes_bytes(T, K)),), dtype=torch.int8, device=dev)
+        sumxf = torch.zeros(((T + 15) // 16, K // BCOL, 16), dtype=torch.float32, device=dev)
+        outs = (None, scale_x.data_ptr(), None, XE.data_ptr(), sumxf.data_ptr())
+        ret = (XE, sumxf, scale_x)
+    else:
+        X_s4 = torch.empty((T, K // 2), dtype=torch.int8, device=dev)
+        sum_X = torch.empty((T, K // BCOL), dtype=torch.int32, device=dev)
+        outs = (X_s4.data_ptr(), scale_x.data_ptr(), sum_X.data_ptr(), None, None)
+        ret = (X_s4, scale_x, sum_X)
+    if T == 0:
+        return ret
+    pp = None if perm is None else perm.data_ptr()
+    with torch.cuda.device(dev):
+        if which == "rmsnorm":
+            w = norm_weight.to(device=dev, dtype=torch.float16).contiguous()
+            _lib.check(_L.w4a4_rmsnorm_quant(X2.data_ptr(), X2.stride(0) if T > 1 else K, w.data_ptr(), float(eps), pp, *outs,
+                                             1 if e4m3 else 0, T, K, _lib.stream_ptr(dev)), "rmsnorm_quant")
+        else:
+            _lib.check(_L.w4a4_silu_mul_quant(X2.data_ptr(), X2.stride(0) if T > 1 else 2 * K, pp, *outs,
+                                              1 if e4m3 else 0, T, K, _lib.stream_ptr(dev)), "silu_mul_quant")
+    return ret
+
+
+def _rows(X: torch.Tensor, width: int) -> torch.Tensor:
+    X2 = X.reshape(-1, width)
+    if X2.stride(-1) != 1 or (X2.shape[0] > 1 and X2.stride(0) < width):
+        X2 = X2.contiguous()
+    return X2
+
+
+def rmsnorm_quant_cuda(X_fp16, norm_weight, eps, perm, *, expanded: bool = False, e4m3: bool = False):
+    """RMSNorm and activation quantisation in one launch: quantises
+    ``fp16(fp16(x * rsqrt(mean(x^2) + eps)) * norm_weight)``.  Returns ``(X_s4, scale_x, sum_X)`` like
+    :func:`activation_quant_cuda`, or with ``expanded=True`` ``(XE, sumxf, scale_x)`` in the layout
+    :func:`fused_dense_sparse_expanded_cuda` reads.  ``perm``: int32 permutation, or ``None`` for identity."""
+    assert X_fp16.is_cuda and X_fp16.dtype == torch.float16
+    K = int(X_fp16.shape[-1])
+    if K % BCOL != 0:
+        raise ValueError(f"d_in ({K}) must be divisible by {BCOL}")
+    if int(norm_weight.numel()) != K:
+        raise ValueError(f"norm_weight must have {K} entries, got {int(norm_weight.numel())}")
+    return _fused_prologue("rmsnorm", _rows(X_fp16, K), K, perm, norm_weight, eps, expanded, e4m3)
+
+
+def silu_mul_quant_cuda(gate_up_fp16, perm, *, expanded: bool = False, e4m3: bool = False):
+    """``silu(gate) * up`` and activation quantisation in one launch.  ``gate_up_fp16 (..., 2K)`` holds the
+    gate in its first K columns and the up projection in the last K (the output of a fused gate/up
+    linear); the quantised tensor is ``fp16(fp16(silu(gate)) * up)`` of width K.  Returns as
+    :func:`rmsnorm_quant_cuda`."""
+    assert gate_up_fp16.is_cuda and gate_up_fp16.dtype == torch.float16
+    K2 = int(gate_up_fp16.shape[-1])
+    if K2 % (2 * BCOL) != 0:
+        raise ValueError(f"the gate/up width ({K2}) must be a multiple of {2 * BCOL}")
+    return _fused_prologue("silu_mul", _rows(gate_up_fp16, K2), K2 // 2, perm, None, 0.0, expanded, e4m3)
+
+
+# ---------------------------------------------------------------------------
 # argument preparation shared by the GEMM entry points (ops.py:268-298,419-460)
 # ---------------------------------------------------------------------------
 
@@ -457,4 +539,7 @@ __all__ = [
     "reserve_workspace",
     "expand_activations_cuda",
     "fused_dense_sparse_expanded_cuda",
+    "rmsnorm_quant_cuda",
+    "silu_mul_quant_cuda",
+    "perm_or_none",
 ]

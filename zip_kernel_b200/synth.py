@@ -94,6 +94,30 @@ def make_container(N: int, K: int, density: float, seed: int, perm_seed: Optiona
     )
 
 
+def make_container_like(base: V9WeightContainer, density: float, seed: int) -> V9WeightContainer:
+    """A container with ``base``'s dense weights, scales, zeros and permutation and a NEW residual part
+    (Bernoulli(density) mask, uniform s4 blocks) - for sweeps over the residual density, where drawing
+    the dense matrix again for every point would only cost time."""
+    N, K = base.d_out, base.d_in
+    g = torch.Generator(device="cpu").manual_seed(int(seed))
+    ng, nbr = K // BCOL, (N + BROW - 1) // BROW
+    mask = torch.rand(nbr, ng, generator=g) < density
+    coords = mask.nonzero()
+    nnz = int(coords.shape[0])
+    wh = torch.randint(-8, 8, (nnz, BROW, BCOL), generator=g, dtype=torch.int8)
+    if N % BROW != 0 and nnz > 0:
+        wh[coords[:, 0] == nbr - 1, N - (nbr - 1) * BROW:, :] = 0
+    row_offsets = torch.zeros(nbr + 1, dtype=torch.int32)
+    if nnz > 0:
+        row_offsets[1:] = torch.cumsum(torch.bincount(coords[:, 0], minlength=nbr), 0).to(torch.int32)
+    return V9WeightContainer(
+        W_low_packed=base.W_low_packed, scale_u4=base.scale_u4, zero_u4=base.zero_u4, perm=base.perm,
+        W_high_blocks_packed=pack_s4_le(wh) if nnz > 0 else torch.zeros((0, BROW, BCOL // 2), dtype=torch.int8),
+        hp_row_offsets=row_offsets,
+        hp_col_indices=coords[:, 1].to(torch.int32).contiguous() if nnz > 0 else torch.zeros((0,), dtype=torch.int32),
+        block_shape=(BROW, BCOL), d_out=N, d_in=K)
+
+
 def algorithmic_bytes(M: int, K: int, N: int, nnz: int, fused_quant: bool = True) -> int:
     """Bytes one fused linear must move at least once.
 

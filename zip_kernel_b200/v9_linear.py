@@ -34,6 +34,43 @@ def _forward(X_fp16: torch.Tensor, W: V9WeightContainer, force=None) -> torch.Te
     return Y.reshape(X_fp16.shape[:-1] + (d_out,))
 
 
+def _gemm_on_expanded(quantised, W: V9WeightContainer, lead_shape, e4m3: bool) -> torch.Tensor:
+    XE, sumxf, scale_x = quantised
+    Y = ops.fused_dense_sparse_expanded_cuda(
+        W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets, W.hp_col_indices, XE, sumxf, W.scale_u4,
+        W.zero_u4, scale_x, W.d_out, W.d_in, token_major=True, prepared=W.prepared if e4m3 else None, e4m3=e4m3)
+    return Y.reshape(tuple(lead_shape) + (W.d_out,))
+
+
+def _wants_e4m3(W: V9WeightContainer, T: int) -> bool:
+    # prepared weights serve the many-token kernel; below its threshold the packed arrays are streamed
+    return W.prepared is not None and T >= 256
+
+
+def v9_linear_forward_rmsnorm(X_fp16: torch.Tensor, norm_weight: torch.Tensor, eps: float,
+                              W: V9WeightContainer) -> torch.Tensor:
+    """``v9_linear_forward(rms_norm(X) * norm_weight, W)`` in two launches (normalise + quantise, GEMM):
+    the normalised activations are never written out.  Same output bits as the unfused sequence when the
+    RMSNorm is the fp16 one of :func:`oracle.w4a4_oracle.rmsnorm_fp16`."""
+    if X_fp16.shape[-1] != W.d_in:
+        raise ValueError(f"X last dim ({X_fp16.shape[-1]}) must match d_in ({W.d_in})")
+    T = X_fp16.numel() // W.d_in
+    e4m3 = _wants_e4m3(W, T)
+    q = ops.rmsnorm_quant_cuda(X_fp16, norm_weight, eps, ops.perm_or_none(W.perm, W), expanded=True, e4m3=e4m3)
+    return _gemm_on_expanded(q, W, X_fp16.shape[:-1], e4m3)
+
+
+def v9_linear_forward_silu_mul(gate_up_fp16: torch.Tensor, W: V9WeightContainer) -> torch.Tensor:
+    """``v9_linear_forward(silu(gate) * up, W)`` for ``gate_up (..., 2 * d_in)`` (gate first) in two launches:
+    the gated activations are quantised as they are computed, with no fp16 round trip."""
+    if gate_up_fp16.shape[-1] != 2 * W.d_in:
+        raise ValueError(f"gate_up last dim ({gate_up_fp16.shape[-1]}) must be 2 * d_in ({2 * W.d_in})")
+    T = gate_up_fp16.numel() // (2 * W.d_in)
+    e4m3 = _wants_e4m3(W, T)
+    q = ops.silu_mul_quant_cuda(gate_up_fp16, ops.perm_or_none(W.perm, W), expanded=True, e4m3=e4m3)
+    return _gemm_on_expanded(q, W, gate_up_fp16.shape[:-1], e4m3)
+
+
 def prepare_for_prefill(W: V9WeightContainer) -> V9WeightContainer:
     """Widen the container's packed weights once (2 x their bytes, kept next to them) so that
     many-token calls run the fp8 instantiation of the tensor-core kernel; few-token calls keep
@@ -96,6 +133,8 @@ __all__ = [
     "v9_linear_forward",
     "v9_linear_forward_decode",
     "v9_linear_forward_prefill",
+    "v9_linear_forward_rmsnorm",
+    "v9_linear_forward_silu_mul",
     "v9_linear_fakequant",
     "reconstruct_w_fakequant_fp16",
     "DECODE_T_THRESHOLD",

@@ -56,13 +56,44 @@ struct QuantParams {
 // fp16(fp16(silu(gate)) * up) - the gated activation that feeds the down projection.
 enum : int { SRC_PLAIN = 0, SRC_RMSNORM = 1, SRC_SILU_MUL = 2 };
 
-// silu(x) = x / (1 + exp(-x)), rounded once to fp32 and then to fp16.  Evaluated in double precision so that
-// the result does not depend on the accuracy of a single-precision exponential: a CPU restatement with
-// a correctly rounded exp gives the same fp16 bits (the two can only differ when the double result lies
-// within 2^-40 of an fp16 rounding boundary).
+// silu(x) = x / (1 + exp(-x)), rounded once to fp32 and then to fp16 - the value a double-precision
+// evaluation gives, so that a CPU restatement with a correctly rounded exp produces the same fp16 bits.
+// Fast path: single precision (expf is accurate to 2 ulp, the sum and the IEEE quotient add half an ulp
+// each: relative error below 4e-7).  If the fp16 roundings of s (1 - 1e-6) and s (1 + 1e-6) agree, every
+// value in between - the exact one included - rounds to that fp16 and the answer is known.  They differ
+// for about one element in 250; those take the double-precision path below.
+__device__ __forceinline__ double silu_f64(double x) {
+  // exp(-x) = 2^n * exp(r), |r| <= ln2 / 2, Taylor polynomial of degree 11 (truncation below 2^-46)
+  double t = fmin(fmax(-x, -60.0), 60.0);       // beyond +-60 the fp16 result no longer changes
+  const double n = rint(t * 1.4426950408889634);
+  const double r = fma(n, -1.9082149292705877e-10, fma(n, -0.6931471803691238, t));
+  double p = 2.505210838544172e-8;               // 1 / 11!
+  p = fma(p, r, 2.755731922398589e-7);
+  p = fma(p, r, 2.7557319223985893e-6);
+  p = fma(p, r, 2.48015873015873e-5);
+  p = fma(p, r, 1.984126984126984e-4);
+  p = fma(p, r, 1.388888888888889e-3);
+  p = fma(p, r, 8.333333333333333e-3);
+  p = fma(p, r, 4.1666666666666664e-2);
+  p = fma(p, r, 1.6666666666666666e-1);
+  p = fma(p, r, 0.5);
+  p = fma(p, r, 1.0);
+  p = fma(p, r, 1.0);
+  const double e = __longlong_as_double(__double_as_longlong(p) + ((long long)(int)n << 52));   // * 2^n (|n| <= 87)
+  const double d = 1.0 + e;
+  // x / d by Newton's iteration on the reciprocal (d lies in [1, 2^88]: no overflow in single precision)
+  double y = (double)__frcp_rn((float)d);
+  y = fma(y, fma(-d, y, 1.0), y);
+  y = fma(y, fma(-d, y, 1.0), y);
+  const double q = x * y;
+  return fma(fma(-d, q, x), y, q);
+}
 __device__ __forceinline__ __half silu_fp16(__half g) {
-  const double x = (double)__half2float(g);
-  return __float2half_rn((float)(x / (1.0 + exp(-x))));
+  const float x = __half2float(g);
+  const float s = __fdiv_rn(x, 1.f + expf(-x));
+  const __half lo = __float2half_rn(s * 0.999999f), hi = __float2half_rn(s * 1.000001f);
+  if (__half_as_ushort(lo) == __half_as_ushort(hi)) return lo;
+  return __float2half_rn((float)silu_f64((double)x));
 }
 // fp16 product of two fp16 values: exact in fp32 (two 11-bit significands), one rounding
 __device__ __forceinline__ __half mul_fp16(__half a, __half b) {

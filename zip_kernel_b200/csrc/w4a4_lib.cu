@@ -63,8 +63,14 @@ EncodeTiledFn g_encode = nullptr;
 cudaError_t set_kernel_attributes() {
   using namespace w4a4;
   cudaError_t e = cudaSuccess;
+  // W4A4_CARVEOUT=0 leaves the shared-memory carve-out to the driver's heuristic (A/B experiments).  By default
+  // the kernels ask for the largest carve-out: a launch that keeps ONE ~100 KB CTA per SM would otherwise be
+  // given a carve-out that has no room for the next kernel's CTA, and the two could never overlap.
+  const bool carve = !(getenv("W4A4_CARVEOUT") && atoi(getenv("W4A4_CARVEOUT")) == 0);
   auto set = [&](auto kern, size_t smem) {
     if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess && carve)
+      e = cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
   };
   set(dec::decode_gemm_kernel<1, false>, dec::smem_bytes(1));
   set(dec::decode_gemm_kernel<2, false>, dec::smem_bytes(2));
@@ -193,16 +199,24 @@ WsLayout ws_layout(int T, int K) {
 
 // ------------------------------------------------------------------ plans
 struct DecodePlan {
-  int row_tiles, tok_tiles, split;   // split = CTAs (cluster size) per block-row
+  int row_tiles, tok_tiles;
+  int split;      // CTAs (cluster size) per block-row
+  int clusters;   // clusters along x: row_tiles when split > 1, else at most one CTA per SM (each walks several block-rows)
 };
 DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_per_pass) {
   using namespace w4a4;
   DecodePlan p;
   p.row_tiles = (N + dec::ROWS - 1) / dec::ROWS;
   p.tok_tiles = (T + tokens_per_pass - 1) / tokens_per_pass;
-  // Largest power-of-two cluster that keeps the grid within the two CTAs per SM that
-  // fit at once (a grid that needs a second wave costs far more than it gains;
-  // measured on the Llama-3-8B decode shapes with dependent launches enabled).
+  // Largest power-of-two cluster that keeps the grid within the two CTAs per SM that fit at once (a grid
+  // that needs a second wave costs far more than it gains; measured on the Llama-3-8B decode shapes with
+  // dependent launches enabled).  Measured and not adopted: at most ONE CTA per SM (any cluster size up to
+  // 8, persistent CTAs walking several block-rows when there are more block-rows than SMs) so that the
+  // next kernel's CTAs become resident early - a pure-copy kernel gains 3 us per launch that way, this
+  // kernel loses 1-8 us: its time after the dependency resolves (activation fetch, the MMAs of the
+  // prefetched tiles, cluster reduction) is serial and halving the warps per SM doubles it, and 128-byte
+  // wide TMA boxes feed one SM at only ~34 GB/s, so a CTA with two block-rows is bound by its copy engine.
+  const long long budget = sm_count / (p.tok_tiles > 0 ? p.tok_tiles : 1);
   const long long base = (long long)p.row_tiles * p.tok_tiles;
   long long s = 1;
   while (s * 2 <= dec::MAX_CLUSTER && base * s * 2 * 10 <= 18LL * sm_count) s *= 2;
@@ -212,8 +226,15 @@ DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_p
   const int env_split = env_split_s ? atoi(env_split_s) : 0;
   if (env_split > 0) s = env_split;
   if (s > dec::MAX_CLUSTER) s = dec::MAX_CLUSTER;
-  while (s > dense_steps && s > 1) s /= 2;
+  while (s > dense_steps && s > 1) --s;
   p.split = (int)s;
+  // W4A4_DECODE_CTAS=n caps the grid at n persistent CTAs that walk several block-rows each (A/B
+  // experiments; -1 = one per SM); by default every block-row has a CTA (cluster) of its own
+  const char* env_ctas_s = getenv("W4A4_DECODE_CTAS");
+  long long cap = env_ctas_s ? atoll(env_ctas_s) : 0;
+  if (cap < 0) cap = budget > 0 ? budget : 1;
+  if (cap == 0) cap = p.row_tiles;
+  p.clusters = p.split > 1 ? p.row_tiles : (int)(p.row_tiles < cap ? p.row_tiles : cap);
   return p;
 }
 
@@ -313,7 +334,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   if (env_nt == 1 || env_nt == 2 || env_nt == 4) nt = env_nt;
   if (nt == 1 && a.T > 8) nt = 2;
   DecodePlan plan = plan_decode(a.T, a.N, dense_steps > 0 ? dense_steps : 1, dev->sm_count, dec::tokens_per_pass(nt));
-  if ((long long)plan.row_tiles * plan.split > 2147483647LL)
+  if ((long long)plan.clusters * plan.split > 2147483647LL)
     return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d is too large", a.N);
   // expanded activations: given by the caller, or built here from the packed codes
   const void* XE = a.XE;
@@ -369,7 +390,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   void (*kern)(const CUtensorMap, const dec::Params) =
       dump ? (nt == 4 ? dec::decode_gemm_kernel<4, true> : nt == 2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
            : (nt == 4 ? dec::decode_gemm_kernel<4, false> : nt == 2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
-  cudaError_t e = launch_ex(kern, dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
+  cudaError_t e = launch_ex(kern, dim3(plan.clusters * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
                 plan.split, tm_low, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;

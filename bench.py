@@ -27,6 +27,7 @@ Further legs in the same line (`--legs`, default all that apply):
   cfg3     Llama-2-70B linears split column-parallel over the ranks (strong scaling),
            M = 1 and M = 4096, with and without the all-gather of the output
   stack    decoder-stack decode tokens per second (one GPU)
+  legacy   the reference's naive mma.sync kernels recompiled for sm_100a, as a same-GPU anchor (one GPU)
 and, on more than one GPU, `sharded_parity`: the gathered output of a sharded
 layer equals the single-GPU output bit for bit.
 """
@@ -378,6 +379,17 @@ def leg_prefill(timer, device, args):
                         "roofline": {"bound": "tensor", "achieved": tops, "frac_burst": tops / peak_burst,
                                      "frac_sustained": tops / peak_sus}, "reps_per_window": reps}
                     del gg, fg, h1, h2, XE, sumxf
+                if W.n_hp_blocks == 0:
+                    # the W4A16 route the reference takes for such a layer at this length (dequantise once, library
+                    # fp16 GEMM; activations are NOT quantised): reported beside the W4A4 kernels, see DESIGN
+                    W16 = v9_linear.dequant_u4_to_fp16(Wd)
+                    ms_dq, _, _ = timer.time(lambda i: ops.dequant_u4_to_fp16_cuda(Wd.W_low_packed, Wd.scale_u4, Wd.zero_u4), 1, 2, min_window_s=0.05)
+                    ms_mm, _, _ = timer.time(lambda i: torch.nn.functional.linear(X, W16), 1, 3, min_window_s=0.1)
+                    out.setdefault("w4a16_route", {})[f"{name}_M{M}"] = {
+                        "us_library_fp16_gemm": ms_mm * 1e3, "us_dequantise_weights": ms_dq * 1e3,
+                        "tflops_library_fp16_gemm": 2.0 * M * K * N / (ms_mm * 1e-3) / 1e12}
+                    del W16
+                    Wd._fp16_cache = None
                 del X, q
             Wd.prepared = None
             del Wd, prep
@@ -401,7 +413,9 @@ def leg_sharded(timer, rank, world, device, args):
 
     hbm, hk = measured_peak("hbm_gbs", 6650.0)
     bf16, _ = measured_peak("bf16_tflops", 1590.0)
-    shards, nnz_per_rank, res = {}, {}, {"per_linear_us": {}, "allgather_us": {}, "linear_plus_gather_graph_us": {}}
+    shards, nnz_per_rank, res = {}, {}, {"per_linear_us": {}, "allgather_us": {}, "linear_plus_gather_graph_us": {},
+                                         "linear_plus_peer_exchange_us": {}}
+    pg = sharding.PeerGather(2 * 4096 * 57344, device=device) if world > 1 else None
     for name, K, N in LLAMA2_70B:
         W = synth.make_container(N, K, DENSITY, seed=synth.shape_seed(0, K, N))
         sh = sharding.shard_container(W, rank, world) if world > 1 else W
@@ -465,6 +479,15 @@ def leg_sharded(timer, rank, world, device, args):
                         del gl, holder
                     except Exception as exc:   # capture of a collective refused: the eager figures stand
                         res["linear_plus_gather_graph_us"][f"{name}_M{M}"] = f"capture failed: {type(exc).__name__}"
+                # the linear followed by the peer-memory exchange (one more kernel, no collective library call)
+                if M == 1:
+                    gp, kp = capture_graphs(lambda r: pg.gather(linear(r), N, token_major=False), len(sets) + (len(sets) & 1))
+                    ms_p, _, _ = timer.time(lambda i: gp[i % len(gp)].replay(), 1, 3)
+                    del gp, kp
+                else:
+                    # many tokens: token bands; a band's exchange runs on a side stream while the next band's GEMM runs
+                    ms_p = time_banded_exchange(timer, ops, pg, Xs[name], sets, N, device)
+                res["linear_plus_peer_exchange_us"][f"{name}_M{M}"] = ms_p * 1e3
             res["per_linear_us"][f"{name}_M{M}"] = per[name]
         t_lin = sum(per.values()) * 1e-6
         res[f"tops_M{M}"] = ops_total / t_lin / 1e12
@@ -482,11 +505,43 @@ def leg_sharded(timer, rank, world, device, args):
             lg = [res["linear_plus_gather_graph_us"].get(f"{n}_M{M}") for n, _, _ in LLAMA2_70B]
             if M == 1 and all(isinstance(v, float) for v in lg):
                 res["tops_M1_linear_plus_gather_graph"] = ops_total / (sum(lg) * 1e-6) / 1e12
+            lp = [res["linear_plus_peer_exchange_us"][f"{n}_M{M}"] for n, _, _ in LLAMA2_70B]
+            res[f"tops_M{M}_with_peer_exchange"] = ops_total / (sum(lp) * 1e-6) / 1e12
         del Xs
+    if pg is not None:
+        pg.close()
     res["residual_blocks_per_rank"] = nnz_per_rank
     res["weights"] = "packed" if args.prepared == "off" else "packed; M=4096 on the prepared e4m3 copy"
     res["scaling"] = "strong"
     return res
+
+
+def time_banded_exchange(timer, ops, pg, X, sets, N, device, bands=4):
+    """One many-token sharded linear with its output exchanged over peer memory in token bands: band b's
+    GEMM writes (T_b, N_r) token-major, its exchange runs on a side stream while band b + 1 computes."""
+    T = int(X.shape[0])
+    edges = [T * b // bands for b in range(bands + 1)]
+    side = torch.cuda.Stream(device=device)
+
+    def step(i):
+        W = sets[i % len(sets)]
+        main = torch.cuda.current_stream(device)
+        outs = []
+        for b in range(bands):
+            y = fused_call(ops, X[edges[b]:edges[b + 1]], W, token_major=True)           # (T_b, N_r)
+            y.record_stream(side)
+            ev = torch.cuda.Event()
+            ev.record(main)
+            outs.append((y, ev))
+        with torch.cuda.stream(side):
+            for b, (y, ev) in enumerate(outs):
+                side.wait_event(ev)
+                pg.gather_band(y, N, T, edges[b])
+        pg.advance()
+        main.wait_stream(side)
+
+    ms, _, _ = timer.time(step, 1, 3, min_window_s=0.05)
+    return ms
 
 
 def sharded_parity(rank, world, device):
@@ -503,9 +558,50 @@ def sharded_parity(rank, world, device):
         sharding.check_shard_metadata(N, K, sh, rank, world)
         got = sharding.column_parallel_forward(X, sh.to(device), N)
         ok = ok and bool(torch.equal(got, full))
+        pg = sharding.PeerGather(2 * T * N, device=device)       # the library's own exchange over peer memory
+        for _ in range(3):
+            ok = ok and bool(torch.equal(sharding.column_parallel_forward(X, sh.to(device), N, exchange=pg), full))
+        pg.close()
     flag = torch.tensor([1 if ok else 0], device=device)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     return bool(flag.item())
+
+
+def leg_legacy(timer, device):
+    """Same-GPU anchor (reported, not a target): the reference's naive mma.sync s4 kernels (dense GEMM, block-sparse
+    GEMM, element-wise sum), built for sm_100a from the reference tree by baseline/build_naive_reference.py, fed with
+    activations quantised by this library.  None when the extension was not built."""
+    from baseline import build_naive_reference
+    from zip_kernel_b200 import ops, synth
+    mod = build_naive_reference.load()
+    if mod is None:
+        return {"unavailable": "baseline/_ref/naive was not built (needs the reference tree and nvcc at build time)"}
+    out = {"kernels": "reference csrc_naive dense_gemm_naive + sparse_gemm_naive + reduce_sum_naive, recompiled for sm_100a",
+           "configs": {}}
+    for name, M, K, N in (("o_M16", 16, 4096, 4096), ("gate_up_M16", 16, 4096, 28672), ("gate_up_M2048", 2048, 4096, 28672)):
+        W = synth.make_container(N, K, DENSITY, seed=synth.shape_seed(0, K, N)).to(device)
+        X = synth.make_activations(M, K, seed=synth.shape_seed(M, K, N) + 1).to(device)
+        q4, qs, qsum = ops.activation_quant_cuda(X, W.perm)
+        Yl = torch.empty((N, M), dtype=torch.float16, device=device)
+        Yh = torch.zeros((N, M), dtype=torch.float16, device=device)
+        Yt = torch.empty((N, M), dtype=torch.float16, device=device)
+
+        def run(i):
+            mod.dense_gemm(W.W_low_packed, q4, W.scale_u4, W.zero_u4, qsum, qs, Yl)
+            mod.sparse_gemm(W.W_high_blocks_packed, W.hp_row_offsets, W.hp_col_indices, q4, W.scale_u4, qs, Yh, N, K)
+            mod.reduce_sum(Yl, Yh, Yt)
+        ms, _, _ = timer.time(run, 1, 3, min_window_s=0.05)
+        ours = ops.fused_dense_sparse_cuda(W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets, W.hp_col_indices,
+                                           q4, W.scale_u4, W.zero_u4, qsum, qs, N, K)
+        ref = Yl.float() + 16.0 * Yh.float()
+        dev_rel = float((ours.float() - ref).abs().max() / ref.abs().max().clamp(min=1e-6))
+        g, kp = capture_graphs(lambda r: ops.fused_dense_sparse_cuda(W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
+                                                                      W.hp_col_indices, q4, W.scale_u4, W.zero_u4, qsum, qs, N, K), 1)
+        ms_ours, _, _ = timer.time(lambda i: g[0].replay(), 1, 3, min_window_s=0.05)
+        out["configs"][name] = {"us_legacy": ms * 1e3, "tops_legacy": 2.0 * M * K * N / (ms * 1e-3) / 1e12,
+                                "us_this_library_warm_l2": ms_ours * 1e3, "max_rel_deviation_from_this_library": dev_rel}
+        del g, kp, W
+    return out
 
 
 def leg_stack(device):
@@ -538,7 +634,7 @@ def main():
     if args.workload == "cfg3_sharded":       # former name of the sharded leg on its own
         args.workload, args.legs = "decode", "cfg3"
     items = workload_items(args.workload)
-    legs = (["cfg0", "prefill", "cfg3", "stack"] if args.workload == "decode" else []) if args.legs == "auto" \
+    legs = (["cfg0", "prefill", "cfg3", "stack", "legacy"] if args.workload == "decode" else []) if args.legs == "auto" \
         else [l for l in args.legs.split(",") if l and l != "none"]
 
     rank = int(os.environ.get("RANK", "0"))
@@ -692,6 +788,8 @@ def main():
                 out["prefill"] = leg_prefill(timer, device, args)
             elif leg == "cfg3":
                 out["cfg3"] = leg_sharded(timer, rank, world, device, args)
+            elif leg == "legacy" and world == 1:
+                out["legacy_gpu_baseline"] = leg_legacy(timer, device)
             elif leg == "stack" and world == 1:
                 out["stack"] = leg_stack(device)
                 out["decode_tok_s"] = out["stack"]["decode_tok_s"]

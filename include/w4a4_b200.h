@@ -184,6 +184,13 @@ int w4a4_dump_accumulators(const void* W_low, const void* W_high, const int32_t*
  * path's); calls with few tokens stream the packed arrays as before.  NULL
  * prepared pointers (both, or the one of an operand in use) select the packed path.
  * Prepared pointers must be 16-byte aligned. */
+/* Dense fp16 copy of the low-precision weights, out (N, K) row-major = fp16( fp16( fp16(code) - zero ) * scale ): the
+ * dequantisation step of the reference's W4A16 route for long prompts without residual blocks
+ * (triton_kernel/dequant_w4_to_fp16.py:131-172, used by backend/dispatcher.py:228-238; the fp16 GEMM that follows is
+ * a plain library GEMM and is not part of this library). */
+int w4a4_dequant_weights_fp16(const void* W_low, const void* scale_u4, const void* zero_u4, void* out_fp16, int N, int K,
+                              void* stream);
+
 size_t w4a4_prepared_weights_bytes(size_t packed_bytes);
 int w4a4_prepare_weights(const void* packed, void* prepared, size_t packed_bytes, void* stream);
 int w4a4_fused_dense_sparse_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,
@@ -223,6 +230,32 @@ int w4a4_dump_accumulators_prepared(const void* W_low, const void* W_high, const
                                     const int32_t* hp_col_indices, const void* X_s4, int32_t* acc,
                                     int32_t* acc_hi, int T, int K, int N, int nnz, int flags, void* workspace,
                                     size_t workspace_bytes, void* stream);
+
+/* Output exchange of a column-parallel (row-sharded) linear over peer memory, for one process per GPU on one
+ * node.  No counterpart in the reference, which is single-GPU.  Set-up (these four calls allocate or map memory
+ * and are NOT stream-ordered; call them once, outside any capture): every rank allocates a buffer with
+ * w4a4_peer_alloc (zero-filled), exports a 64-byte handle with w4a4_peer_export, the host code passes the
+ * handles between the processes, and every rank maps its peers' buffers with w4a4_peer_open (close with
+ * w4a4_peer_close before the owner frees).
+ *
+ * w4a4_peer_push_wait(src, ...) is the per-step call: one kernel copies this rank's shard (`rows` rows of
+ * `row_bytes` bytes, `src_pitch` apart) into EVERY rank's full-output buffer dst[i] (host array of `world` device
+ * pointers, own buffer included) at byte offset dst_offset with row pitch dst_pitch, using plain 16-byte stores
+ * to peer-mapped memory; raises flags[i][rank] (host array of `world` pointers to each rank's array of `world`
+ * 32-bit flags); and then waits until all `world` flags of THIS rank have arrived, so that when the kernel has
+ * finished the full output is complete in this rank's buffer.  The wait is bounded: after poll_limit polls per
+ * flag the kernel records the device error word (w4a4_device_error) and returns.  `state` is (1 + 2 * world)
+ * zero-initialised 32-bit words of LOCAL device memory that belong to this (buffer set, rank); every rank must
+ * make the same sequence of calls on a buffer set.  Reusing a destination buffer is safe once every rank has
+ * completed a later w4a4_peer_push_wait (alternate between two buffer sets). */
+int w4a4_peer_alloc(size_t bytes, void** ptr /* host */);
+int w4a4_peer_free(void* ptr);
+int w4a4_peer_export(const void* ptr, void* handle /* host, 64 bytes */);
+int w4a4_peer_open(const void* handle /* host, 64 bytes */, void** ptr /* host */);
+int w4a4_peer_close(void* ptr);
+int w4a4_peer_push_wait(const void* src, long long src_pitch, void* const* dst /* host */, void* const* flags /* host */,
+                        long long dst_pitch, long long dst_offset, int rows, int row_bytes, int world, int rank,
+                        void* state, int poll_limit, void* stream);
 
 /* No counterpart in the reference (its launchers allocate split-K partials with
  * torch::empty, fused_dense_sparse_mma_int4.cu:1873-1879).

@@ -372,6 +372,16 @@ def v9_linear_fakequant(X_fp16, W: dict):
 # the timed CPU baseline: the reference's own CPU path, multi-threaded
 # ---------------------------------------------------------------------------
 
+def dequant_u4_to_fp16(W_low_packed: np.ndarray, scale_u4: np.ndarray, zero_u4: np.ndarray) -> np.ndarray:
+    """``(d_out, d_in)`` fp16 weight of the reference's W4A16 route: ``(fp16(code) - zero) * scale`` with both
+    operations rounded to half precision (triton_kernel/dequant_w4_to_fp16.py:97-121)."""
+    codes = unpack_s4_le(np.asarray(W_low_packed)).astype(np.float16)
+    z = np.repeat(np.asarray(zero_u4, dtype=np.float16), BCOL, axis=1)
+    s = np.repeat(np.asarray(scale_u4, dtype=np.float16), BCOL, axis=1)
+    d = (codes.astype(np.float32) - z.astype(np.float32)).astype(np.float16)
+    return (d.astype(np.float32) * s.astype(np.float32)).astype(np.float16)
+
+
 def rmsnorm_fp16(X_fp16: np.ndarray, weight_fp16: np.ndarray, eps: float) -> np.ndarray:
     """fp16 RMSNorm as a decoder layer applies it before a quantised linear:
     ``y = fp16(fp16(x * r) * w)`` with ``r = 1 / sqrt(fp32(mean(x^2)) + eps)`` in fp32 (the PyTorch

@@ -33,6 +33,12 @@ SIGNATURES = {
     "w4a4_activation_quant": (_INT, [_PTR, _LL, _PTR, _PTR, _PTR, _PTR, _INT, _INT, _PTR]),
     "w4a4_rmsnorm_quant": (_INT, [_PTR, _LL, _PTR, _c.c_float] + [_PTR] * 6 + [_INT, _INT, _INT, _PTR]),
     "w4a4_silu_mul_quant": (_INT, [_PTR, _LL] + [_PTR] * 6 + [_INT, _INT, _INT, _PTR]),
+    "w4a4_peer_alloc": (_INT, [_SZ, _c.POINTER(_PTR)]),
+    "w4a4_peer_free": (_INT, [_PTR]),
+    "w4a4_peer_export": (_INT, [_PTR, _PTR]),
+    "w4a4_peer_open": (_INT, [_PTR, _c.POINTER(_PTR)]),
+    "w4a4_peer_close": (_INT, [_PTR]),
+    "w4a4_peer_push_wait": (_INT, [_PTR, _LL, _c.POINTER(_PTR), _c.POINTER(_PTR), _LL, _LL, _INT, _INT, _INT, _INT, _PTR, _INT, _PTR]),
     "w4a4_workspace_bytes": (_SZ, [_INT, _INT, _INT, _INT]),
     "w4a4_fused_dense_sparse": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_expanded_codes_bytes": (_SZ, [_INT, _INT]),
@@ -44,6 +50,7 @@ SIGNATURES = {
     "w4a4_fused_quant_dense_sparse": (_INT, [_PTR, _LL] + [_PTR] * 8 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
     "w4a4_fused_dense_sparse_noalloc": (_INT, [_PTR] * 10 + [_INT] * 5 + [_PTR]),
     "w4a4_dump_accumulators": (_INT, [_PTR] * 7 + [_INT] * 5 + [_PTR, _SZ, _PTR]),
+    "w4a4_dequant_weights_fp16": (_INT, [_PTR] * 4 + [_INT, _INT, _PTR]),
     "w4a4_prepared_weights_bytes": (_SZ, [_SZ]),
     "w4a4_prepare_weights": (_INT, [_PTR, _PTR, _SZ, _PTR]),
     "w4a4_fused_dense_sparse_prepared": (_INT, [_PTR] * 12 + [_INT] * 5 + [_PTR, _SZ, _PTR]),

@@ -427,4 +427,26 @@ __global__ void __launch_bounds__(256) prepare_weights_kernel(const uint32_t* pa
     out[i] = expand_word(ld_plain(packed + i), 1);
 }
 
+// Dense fp16 copy of the low-precision weights for the W4A16 route (many tokens, no residual blocks):
+// out[n, k] = fp16( fp16( fp16(code) - zero[n, g] ) * scale[n, g] ), two roundings in half precision, exactly what the
+// reference's dequantisation kernel computes (triton_kernel/dequant_w4_to_fp16.py:61-128).  One thread per packed word.
+__global__ void __launch_bounds__(256) dequant_weights_kernel(const uint32_t* __restrict__ packed, const __half* __restrict__ scale,
+                                                              const __half* __restrict__ zero, uint4* __restrict__ out, int N, int K) {
+  const long long words = (long long)N * (K >> 3);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const int wpr = K >> 3, ng = K >> 7;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < words; i += stride) {
+    const int n = (int)(i / wpr), c = (int)(i - (long long)n * wpr);
+    const uint32_t w = ld_plain(packed + i);
+    const __half s = scale[(size_t)n * ng + (c >> 4)], z = zero[(size_t)n * ng + (c >> 4)];
+    __align__(16) __half h[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int code = ((int)(w << (28 - 4 * j))) >> 28;           // sign-extended nibble j
+      h[j] = __hmul(__hsub(__int2half_rn(code), z), s);
+    }
+    out[i] = *reinterpret_cast<uint4*>(h);
+  }
+}
+
 }  // namespace w4a4

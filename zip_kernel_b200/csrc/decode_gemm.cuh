@@ -201,16 +201,10 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
   const int lane = tid & 31;
   const int S = p.split;
   const int rank = S > 1 ? (int)cluster_ctarank() : 0;   // == blockIdx.x % S
-  // A cluster (a single CTA when S == 1) walks the block-rows r_first, r_first + r_stride, ...  The grid
-  // is sized so that one launch keeps at most one CTA on an SM: with about half of an SM's shared memory
-  // and registers per CTA, the CTAs of the NEXT kernel in the stream become resident while this kernel
-  // still runs, fill their rings with weights and only then wait for this kernel to finish (programmatic
-  // dependent launch) - the launch gap and the ramp of every kernel hide behind its predecessor.  With
-  // S > 1 a cluster owns exactly one block-row (r_stride == row_tiles).
-  const int r_first = blockIdx.x / S;
-  const int r_stride = gridDim.x / S;
+  const int r = blockIdx.x / S;                            // block-row of this cluster
   const int tt = blockIdx.y;
   const int tok0 = tt * TOK;
+  const int row0 = r * ROWS;
   constexpr int XG_BYTES = NT * 8 * BCOL;     // activation bytes actually copied per group
   // this CTA's share of the dense steps of the block-row: needs no memory access
   const int d_lo = (int)((long long)rank * p.nd / S), d_hi = (int)((long long)(rank + 1) * p.nd / S);
@@ -238,7 +232,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
       // stream, the activation copies do.  Dense step j covers groups 2j, 2j+1.
       // the tokens' codes of one group are one contiguous run in the expanded layout
       auto x_src = [&](int g) { return p.XE + ((size_t)g * p.t_pad + tok0) * BCOL; };
-      auto dense_w = [&](int j, int st, int row0) {
+      auto dense_w = [&](int j, int st) {
         const int n_grp = (2 * j + 1 < p.ng) ? 2 : 1;
         mbar_arrive_expect_tx(&full[st], W_TILE_BYTES + n_grp * XG_BYTES + n_u * n_grp * 64);
         tma_load_2d(stage_buf + st * STAGE_BYTES, &tm_low, 2 * j * GROUP_BYTES, row0, &full[st]);
@@ -256,37 +250,34 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
       // ring fill: weight tiles first, then wait for the activations' producer kernel
       const int n_dense = d_hi - d_lo;
       const int n_pre = min(STAGES, n_dense);
-      for (int n = 0; n < n_pre; ++n) dense_w(d_lo + n, n, r_first * ROWS);
+      for (int n = 0; n < n_pre; ++n) dense_w(d_lo + n, n);
+      // this CTA's share of the residual blocks of the block-row
+      int b_lo = 0, b_hi = 0;
+      if (p.sparse_on) {
+        const int o0 = ld_plain(p.hp_row_offsets + r), o1 = ld_plain(p.hp_row_offsets + r + 1);
+        b_lo = o0 + (int)((long long)rank * (o1 - o0) / S);
+        b_hi = o0 + (int)((long long)(rank + 1) * (o1 - o0) / S);
+      }
       grid_dependency_wait();
       int st = 0, n = 0;
       uint32_t ph = 1;                     // parity the empty barrier is waited on
-      for (int r = r_first; r < p.row_tiles && ok; r += r_stride) {
-        const int row0 = r * ROWS;
-        // this CTA's share of the residual blocks of the block-row
-        int b_lo = 0, b_hi = 0;
-        if (p.sparse_on) {
-          const int o0 = ld_plain(p.hp_row_offsets + r), o1 = ld_plain(p.hp_row_offsets + r + 1);
-          b_lo = o0 + (int)((long long)rank * (o1 - o0) / S);
-          b_hi = o0 + (int)((long long)(rank + 1) * (o1 - o0) / S);
-        }
-        for (int j = d_lo; j < d_hi && ok; ++j, ++n) {
-          if (n >= n_pre) {
-            ok = mbar_wait(&empty[st], ph, SITE_DEC_EMPTY);
-            if (!ok) break;
-            dense_w(j, st, row0);
-          }
-          dense_x(j, st);
-          if (++st == STAGES) { st = 0; ph ^= 1; }
-        }
-        for (int blk = b_lo; blk < b_hi && ok; ++blk, ++n) {
+      for (int j = d_lo; j < d_hi && ok; ++j, ++n) {
+        if (n >= n_pre) {
           ok = mbar_wait(&empty[st], ph, SITE_DEC_EMPTY);
           if (!ok) break;
-          unsigned char* slot = stage_buf + st * STAGE_BYTES;
-          mbar_arrive_expect_tx(&full[st], BLK_BYTES + XG_BYTES);
-          bulk_load_1d(slot, p.W_high + (size_t)blk * BLK_BYTES, BLK_BYTES, &full[st]);
-          bulk_load_1d(slot + W_TILE_BYTES, x_src(ld_plain(p.hp_col_indices + blk)), XG_BYTES, &full[st]);
-          if (++st == STAGES) { st = 0; ph ^= 1; }
+          dense_w(j, st);
         }
+        dense_x(j, st);
+        if (++st == STAGES) { st = 0; ph ^= 1; }
+      }
+      for (int blk = b_lo; blk < b_hi && ok; ++blk, ++n) {
+        ok = mbar_wait(&empty[st], ph, SITE_DEC_EMPTY);
+        if (!ok) break;
+        unsigned char* slot = stage_buf + st * STAGE_BYTES;
+        mbar_arrive_expect_tx(&full[st], BLK_BYTES + XG_BYTES);
+        bulk_load_1d(slot, p.W_high + (size_t)blk * BLK_BYTES, BLK_BYTES, &full[st]);
+        bulk_load_1d(slot + W_TILE_BYTES, x_src(ld_plain(p.hp_col_indices + blk)), XG_BYTES, &full[st]);
+        if (++st == STAGES) { st = 0; ph ^= 1; }
       }
       if (!ok) {
         misc[1] = 1;
@@ -313,22 +304,16 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
     const uint32_t stage_a = smem_u32(stage_buf), sumx_a = smem_u32(sumx_ring), szs_a = smem_u32(szs);
 
     float2 y[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = make_float2(0.f, 0.f);
     bool ok = true;
     int consumed = 0;
-    // the block-row being worked on (the ring's step counter `consumed` runs on across block-rows)
-    int r = r_first, row0 = r_first * ROWS;
     int b_lo = 0, b_hi = 0;
-    auto set_item = [&](int r_new) {
-      r = r_new;
-      row0 = r_new * ROWS;
-      b_lo = b_hi = 0;
-      if (p.sparse_on) {
-        const int o0 = ld_plain(p.hp_row_offsets + r), o1 = ld_plain(p.hp_row_offsets + r + 1);
-        b_lo = o0 + (int)((long long)rank * (o1 - o0) / S);
-        b_hi = o0 + (int)((long long)(rank + 1) * (o1 - o0) / S);
-      }
-    };
-    set_item(r_first);
+    if (p.sparse_on) {
+      const int o0 = ld_plain(p.hp_row_offsets + r), o1 = ld_plain(p.hp_row_offsets + r + 1);
+      b_lo = o0 + (int)((long long)rank * (o1 - o0) / S);
+      b_hi = o0 + (int)((long long)(rank + 1) * (o1 - o0) / S);
+    }
 
     // The dense share is walked in spans that lie inside one aligned window of 16
     // groups (8 steps); the residual blocks form a last span.
@@ -408,9 +393,6 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
       }
     // A wait that gives up clears `ok` for the whole warp; the loops still run to
     // their end (skipping the work) so that every barrier below is reached.
-    for (;;) {     // block-rows of this CTA
-#pragma unroll
-    for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = make_float2(0.f, 0.f);
     while (have) {
       const bool have_next = walk(j_w, did_sparse, nxt);
       asm volatile("bar.sync 1, %0;" ::"n"(CONSUMER_THREADS) : "memory");   // previous span's window is free
@@ -536,6 +518,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
       cur = nxt;
       have = have_next;
     }
+    if (!ok) misc[1] = 1;
 
     // ---------------------------------------------------------- block-row share done
     if (p.Y != nullptr && S == 1) {
@@ -562,21 +545,11 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
         sts_f2(stage_a + (r_b * TOK + nt * 8 + tig * 2) * 4, y[nt][1]);
       }
     }
-    if (r + r_stride >= p.row_tiles) break;
-    // next block-row of this CTA: its first scale window is requested at once
-    set_item(r + r_stride);
-    j_w = d_lo;
-    did_sparse = 0;
-    have = walk(j_w, did_sparse, cur);
-    if (have) fetch_sz(cur);
-    }     // block-rows
-    if (!ok) misc[1] = 1;
   }
 
   if (p.Y != nullptr && S > 1) {
     // Every thread of every CTA of the cluster reaches both barriers: no path
     // above returns early.  CTA k then owns rows [k*128/S, (k+1)*128/S) of the tile.
-    const int row0 = r_first * ROWS;       // a cluster owns exactly one block-row
     __syncwarp();
     constexpr int NCOL = NT * 8;
     static_assert(THREADS % NCOL == 0, "a thread keeps one output column through the reduction loop");

@@ -18,6 +18,7 @@
 #include "decode_gemm.cuh"
 #include "prefill_gemm.cuh"
 #include "prefill_pair_gemm.cuh"
+#include "peer_gather.cuh"
 
 namespace {
 
@@ -204,9 +205,7 @@ WsLayout ws_layout(int T, int K) {
 
 // ------------------------------------------------------------------ plans
 struct DecodePlan {
-  int row_tiles, tok_tiles;
-  int split;      // CTAs (cluster size) per block-row
-  int clusters;   // clusters along x: row_tiles when split > 1, else at most one CTA per SM (each walks several block-rows)
+  int row_tiles, tok_tiles, split;   // split = CTAs (cluster size) per block-row
 };
 DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_per_pass) {
   using namespace w4a4;
@@ -217,11 +216,11 @@ DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_p
   // that needs a second wave costs far more than it gains; measured on the Llama-3-8B decode shapes with
   // dependent launches enabled).  Measured and not adopted: at most ONE CTA per SM (any cluster size up to
   // 8, persistent CTAs walking several block-rows when there are more block-rows than SMs) so that the
-  // next kernel's CTAs become resident early - a pure-copy kernel gains 3 us per launch that way, this
-  // kernel loses 1-8 us: its time after the dependency resolves (activation fetch, the MMAs of the
-  // prefetched tiles, cluster reduction) is serial and halving the warps per SM doubles it, and 128-byte
-  // wide TMA boxes feed one SM at only ~34 GB/s, so a CTA with two block-rows is bound by its copy engine.
-  const long long budget = sm_count / (p.tok_tiles > 0 ? p.tok_tiles : 1);
+  // next kernel's CTAs become resident early - a pure-copy kernel of this footprint gains 3 us per launch
+  // that way (8.4 MB: 6.7 -> 3.1 us), this kernel loses 1-8 us: its time after the dependency resolves
+  // (activation fetch, the MMAs of the prefetched tiles, cluster reduction) is serial and halving the
+  // warps per SM doubles it, 128-byte wide TMA boxes feed one SM at only ~34 GB/s, so a CTA with two
+  // block-rows is bound by its copy engine, and the loop over block-rows itself cost 5 % on every shape.
   const long long base = (long long)p.row_tiles * p.tok_tiles;
   long long s = 1;
   while (s * 2 <= dec::MAX_CLUSTER && base * s * 2 * 10 <= 18LL * sm_count) s *= 2;
@@ -231,15 +230,8 @@ DecodePlan plan_decode(int T, int N, int dense_steps, int sm_count, int tokens_p
   const int env_split = env_split_s ? atoi(env_split_s) : 0;
   if (env_split > 0) s = env_split;
   if (s > dec::MAX_CLUSTER) s = dec::MAX_CLUSTER;
-  while (s > dense_steps && s > 1) --s;
+  while (s > dense_steps && s > 1) s /= 2;
   p.split = (int)s;
-  // W4A4_DECODE_CTAS=n caps the grid at n persistent CTAs that walk several block-rows each (A/B
-  // experiments; -1 = one per SM); by default every block-row has a CTA (cluster) of its own
-  const char* env_ctas_s = getenv("W4A4_DECODE_CTAS");
-  long long cap = env_ctas_s ? atoll(env_ctas_s) : 0;
-  if (cap < 0) cap = budget > 0 ? budget : 1;
-  if (cap == 0) cap = p.row_tiles;
-  p.clusters = p.split > 1 ? p.row_tiles : (int)(p.row_tiles < cap ? p.row_tiles : cap);
   return p;
 }
 
@@ -339,7 +331,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   if (env_nt == 1 || env_nt == 2 || env_nt == 4) nt = env_nt;
   if (nt == 1 && a.T > 8) nt = 2;
   DecodePlan plan = plan_decode(a.T, a.N, dense_steps > 0 ? dense_steps : 1, dev->sm_count, dec::tokens_per_pass(nt));
-  if ((long long)plan.clusters * plan.split > 2147483647LL)
+  if ((long long)plan.row_tiles * plan.split > 2147483647LL)
     return fail(W4A4_ERR_UNSUPPORTED, "d_out=%d is too large", a.N);
   // expanded activations: given by the caller, or built here from the packed codes
   const void* XE = a.XE;
@@ -395,7 +387,7 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   void (*kern)(const CUtensorMap, const dec::Params) =
       dump ? (nt == 4 ? dec::decode_gemm_kernel<4, true> : nt == 2 ? dec::decode_gemm_kernel<2, true> : dec::decode_gemm_kernel<1, true>)
            : (nt == 4 ? dec::decode_gemm_kernel<4, false> : nt == 2 ? dec::decode_gemm_kernel<2, false> : dec::decode_gemm_kernel<1, false>);
-  cudaError_t e = launch_ex(kern, dim3(plan.clusters * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
+  cudaError_t e = launch_ex(kern, dim3(plan.row_tiles * plan.split, plan.tok_tiles, 1), dim3(dec::THREADS), smem, a.stream,
                 plan.split, tm_low, p);
   if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "decode kernel launch: %s", cudaGetErrorString(e));
   return W4A4_OK;
@@ -772,6 +764,91 @@ int w4a4_silu_mul_quant(const void* GU, long long ldgu, const int32_t* perm, voi
                               sumxf, code_format, T, K, stream);
 }
 
+// ------------------------------------------------------------------ output exchange over peer memory
+int w4a4_peer_alloc(size_t bytes, void** ptr) {
+  begin_call();
+  CHECK_ARG(ptr != nullptr && bytes > 0, "bad arguments");
+  void* p = nullptr;
+  cudaError_t e = cudaMalloc(&p, bytes);
+  if (e == cudaSuccess) e = cudaMemset(p, 0, bytes);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "w4a4_peer_alloc(%zu): %s", bytes, cudaGetErrorString(e));
+  *ptr = p;
+  return W4A4_OK;
+}
+
+int w4a4_peer_free(void* ptr) {
+  begin_call();
+  cudaError_t e = cudaFree(ptr);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "w4a4_peer_free: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
+int w4a4_peer_export(const void* ptr, void* handle) {
+  begin_call();
+  CHECK_ARG(ptr && handle, "NULL pointer");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+  cudaIpcMemHandle_t h;
+  cudaError_t e = cudaIpcGetMemHandle(&h, const_cast<void*>(ptr));
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaIpcGetMemHandle: %s", cudaGetErrorString(e));
+  memcpy(handle, &h, 64);
+  return W4A4_OK;
+}
+
+int w4a4_peer_open(const void* handle, void** ptr) {
+  begin_call();
+  CHECK_ARG(ptr && handle, "NULL pointer");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle, 64);
+  void* p = nullptr;
+  cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaIpcOpenMemHandle: %s", cudaGetErrorString(e));
+  *ptr = p;
+  return W4A4_OK;
+}
+
+int w4a4_peer_close(void* ptr) {
+  begin_call();
+  cudaError_t e = cudaIpcCloseMemHandle(ptr);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "cudaIpcCloseMemHandle: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
+int w4a4_peer_push_wait(const void* src, long long src_pitch, void* const* dst, void* const* flags, long long dst_pitch,
+                        long long dst_offset, int rows, int row_bytes, int world, int rank, void* state, int poll_limit,
+                        void* stream) {
+  begin_call();
+  CHECK_ARG(src && dst && flags && state, "NULL pointer");
+  CHECK_ARG(world >= 1 && world <= w4a4::PEER_MAX_WORLD && rank >= 0 && rank < world, "world=%d rank=%d out of range", world, rank);
+  CHECK_ARG(rows >= 1 && row_bytes >= 2 && row_bytes % 2 == 0, "rows=%d row_bytes=%d", rows, row_bytes);
+  CHECK_ARG(src_pitch >= row_bytes && dst_pitch >= row_bytes && dst_offset >= 0, "pitches must cover a row");
+  CHECK_ARG(poll_limit >= 1, "poll_limit must be >= 1");
+  w4a4::PushParams p;
+  memset(&p, 0, sizeof p);
+  p.src = static_cast<const unsigned char*>(src);
+  p.src_pitch = src_pitch;
+  for (int i = 0; i < world; ++i) {
+    CHECK_ARG(dst[i] && flags[i], "NULL peer pointer for rank %d", i);
+    p.dst[i] = static_cast<unsigned char*>(dst[i]);
+    p.flags[i] = static_cast<unsigned int*>(flags[i]);
+  }
+  p.dst_pitch = dst_pitch; p.dst_offset = dst_offset; p.rows = rows; p.row_bytes = row_bytes;
+  p.world = world; p.rank = rank; p.state = static_cast<unsigned int*>(state); p.poll_limit = (unsigned int)poll_limit;
+  // enough blocks per destination to keep the links busy on large shards, one for a decode-sized shard
+  const long long bytes = (long long)rows * row_bytes;
+  int bpd = (int)((bytes + (64 << 10) - 1) / (64 << 10));
+  DeviceInfo* dev = nullptr;
+  int rc = current_device(&dev);
+  if (rc) return rc;
+  const int cap = (2 * dev->sm_count) / world > 0 ? (2 * dev->sm_count) / world : 1;
+  if (bpd > cap) bpd = cap;
+  if (bpd < 1) bpd = 1;
+  p.blocks_per_dst = bpd;
+  cudaError_t e = launch_ex(w4a4::peer_push_wait_kernel, dim3((unsigned)(bpd * world)), dim3(256), 0,
+                            static_cast<cudaStream_t>(stream), 1, p);
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "peer push kernel launch: %s", cudaGetErrorString(e));
+  return W4A4_OK;
+}
+
 size_t w4a4_workspace_bytes(int T, int K, int N, int nnz) {
   (void)N;
   (void)nnz;
@@ -786,6 +863,28 @@ int w4a4_fused_dense_sparse(const void* W_low, const void* W_high, const int32_t
   return w4a4_fused_dense_sparse_prepared(W_low, W_high, nullptr, nullptr, hp_row_offsets, hp_col_indices, X_s4, scale_u4,
                                           zero_u4, sum_X, scale_x, Y, T, K, N, nnz, flags, workspace, workspace_bytes,
                                           stream);
+}
+
+int w4a4_dequant_weights_fp16(const void* W_low, const void* scale_u4, const void* zero_u4, void* out_fp16, int N, int K,
+                              void* stream) {
+  begin_call();
+  int rc = check_common(1, K, N, 0);
+  if (rc) return rc;
+  CHECK_ARG(W_low && scale_u4 && zero_u4 && out_fp16, "NULL tensor pointer");
+  if (!aligned(W_low, 4) || !aligned(out_fp16, 16) || !aligned(scale_u4, 2) || !aligned(zero_u4, 2))
+    return fail(W4A4_ERR_ALIGNMENT, "dequant_weights pointer alignment");
+  DeviceInfo* dev = nullptr;
+  rc = current_device(&dev);
+  if (rc) return rc;
+  const long long words = (long long)N * (K / 8);
+  long long blocks = (words + 255) / 256;
+  if (blocks > 16LL * dev->sm_count) blocks = 16LL * dev->sm_count;
+  w4a4::dequant_weights_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint32_t*>(W_low), static_cast<const __half*>(scale_u4), static_cast<const __half*>(zero_u4),
+      static_cast<uint4*>(out_fp16), N, K);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(W4A4_ERR_LAUNCH, "dequant_weights kernel launch: %s", cudaGetErrorString(e));
+  return W4A4_OK;
 }
 
 size_t w4a4_prepared_weights_bytes(size_t packed_bytes) { return 2 * packed_bytes; }

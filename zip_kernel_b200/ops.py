@@ -311,6 +311,22 @@ def prepare_weights_cuda(packed: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def dequant_u4_to_fp16_cuda(W_low_packed: torch.Tensor, scale_u4: torch.Tensor, zero_u4: torch.Tensor) -> torch.Tensor:
+    """Dense ``(d_out, d_in)`` fp16 copy of the low-precision weights, ``((code - zero) * scale)`` in half precision:
+    the reference's ``dequant_u4_to_fp16`` (triton_kernel/dequant_w4_to_fp16.py:131-172), bit for bit."""
+    assert W_low_packed.is_cuda and W_low_packed.dtype == torch.int8 and W_low_packed.dim() == 2
+    W = W_low_packed.contiguous()
+    N, K = int(W.shape[0]), int(W.shape[1]) * 2
+    s = scale_u4.contiguous().to(torch.float16)
+    z = zero_u4.contiguous().to(torch.float16)
+    assert s.shape == (N, K // BCOL) and z.shape == (N, K // BCOL)
+    out = torch.empty((N, K), dtype=torch.float16, device=W.device)
+    with torch.cuda.device(W.device):
+        _lib.check(_L.w4a4_dequant_weights_fp16(W.data_ptr(), s.data_ptr(), z.data_ptr(), out.data_ptr(), N, K,
+                                                _lib.stream_ptr(W.device)), "dequant_weights")
+    return out
+
+
 def _prepared_ptrs(prepared, W, Wh, nnz):
     """Device pointers of the (low, high) pair made by :func:`prepare_weights_cuda`, checked against the packed arrays."""
     if prepared is None:
@@ -539,6 +555,7 @@ __all__ = [
     "reserve_workspace",
     "expand_activations_cuda",
     "fused_dense_sparse_expanded_cuda",
+    "dequant_u4_to_fp16_cuda",
     "rmsnorm_quant_cuda",
     "silu_mul_quant_cuda",
     "perm_or_none",

@@ -13,6 +13,8 @@ pass; decode and prefill differ only in which GEMM kernel the library selects.
 
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import ops
@@ -21,12 +23,47 @@ from .pack_utils import BCOL, V9WeightContainer, unpack_s4_le
 DECODE_T_THRESHOLD = 128
 
 
+# W4A16 route for long prompts (the reference's backend/dispatcher.py:228-238): a layer WITHOUT residual blocks at
+# T >= 1024 (or T >= 512 on shapes up to 4096 x 4096) is dequantised to fp16 and multiplied by a library fp16 GEMM;
+# activations are then not quantised at all, so results differ from the W4A4 arithmetic (the reference bounds the
+# difference by 2e-2 of the output range).  "off" (default here: every call is W4A4 and matches the oracle) or "auto"
+# (the reference's rule).  The dequantised copy (4 x the packed bytes) is cached on the container.
+_w4a16_policy = os.environ.get("W4A4_W4A16_FALLBACK", "off")
+
+
+def set_w4a16_fallback(policy: str) -> str:
+    """``'off'`` or ``'auto'``; returns the previous policy."""
+    global _w4a16_policy
+    if policy not in ("off", "auto"):
+        raise ValueError(f"unknown W4A16 fallback policy {policy!r}; legal values are ('off', 'auto')")
+    previous, _w4a16_policy = _w4a16_policy, policy
+    return previous
+
+
+def w4a16_eligible(W: V9WeightContainer, T: int) -> bool:
+    """The reference's eligibility rule (dispatcher.py:231-234)."""
+    return W.n_hp_blocks == 0 and (T >= 1024 or (T >= 512 and W.d_out * W.d_in <= 4096 * 4096))
+
+
+def dequant_u4_to_fp16(W: V9WeightContainer) -> torch.Tensor:
+    """``(d_out, d_in)`` fp16 weight in permuted column order, cached on the container."""
+    cached = getattr(W, "_fp16_cache", None)
+    if cached is None or cached.device != W.W_low_packed.device:
+        cached = ops.dequant_u4_to_fp16_cuda(W.W_low_packed, W.scale_u4, W.zero_u4)
+        W._fp16_cache = cached
+    return cached
+
+
 def _forward(X_fp16: torch.Tensor, W: V9WeightContainer, force=None) -> torch.Tensor:
     assert X_fp16.is_cuda and X_fp16.dtype == torch.float16
     d_in, d_out = W.d_in, W.d_out
     if X_fp16.shape[-1] != d_in:
         raise ValueError(f"X last dim ({X_fp16.shape[-1]}) must match d_in ({d_in})")
     X_2d = X_fp16.reshape(-1, d_in)
+    if _w4a16_policy == "auto" and force is None and w4a16_eligible(W, int(X_2d.shape[0])):
+        perm = ops.perm_or_none(W.perm, W)
+        Xp = X_2d if perm is None else X_2d.index_select(1, perm.to(torch.long))
+        return torch.nn.functional.linear(Xp, dequant_u4_to_fp16(W)).reshape(X_fp16.shape[:-1] + (d_out,))
     Y = ops.fused_dense_sparse_e2e_cuda(
         X_2d, W.perm, W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
         W.hp_col_indices, W.scale_u4, W.zero_u4, d_out, d_in, token_major=True, force=force,
@@ -137,5 +174,8 @@ __all__ = [
     "v9_linear_forward_silu_mul",
     "v9_linear_fakequant",
     "reconstruct_w_fakequant_fp16",
+    "set_w4a16_fallback",
+    "w4a16_eligible",
+    "dequant_u4_to_fp16",
     "DECODE_T_THRESHOLD",
 ]

@@ -47,3 +47,37 @@ def make_case(T, N, K, density, perm_seed=None, seed_offset=0, **kw):
 
 def cuda_container(W):
     return W.to(torch.device("cuda"))
+
+
+def assert_kernels_agree(Y_a, Y_b, what, W=None, q=None, names=("first", "second")):
+    """Two kernels' outputs ``(N, T)`` of the same problem within the fp16 tolerance of each other.  When they
+    are not, the message says where they differ, what the device error word holds, and - given the CPU container
+    ``W`` and the quantised activations ``q`` - how far each of them is from the oracle on the block-rows
+    concerned, so that a failure names the kernel at fault."""
+    a, b = np_(Y_a).astype(np.float32), np_(Y_b).astype(np.float32)
+    assert a.shape == b.shape, (what, a.shape, b.shape)
+    bad = np.abs(a - b) > ATOL + RTOL * np.abs(b)
+    if not bad.any():
+        return
+    from zip_kernel_b200 import _lib
+    from zip_kernel_b200.pack_utils import BROW, V9WeightContainer
+    rows, toks = np.nonzero(bad)
+    lines = [f"{what}: {int(bad.sum())} of {bad.size} outside max-abs {ATOL} + rel {RTOL}; worst |d|={np.abs(a - b).max():.4g}",
+             f"  device error word {_lib.device_error(torch.device('cuda')):#x}",
+             f"  rows {sorted(set(rows.tolist()))[:48]} tokens {sorted(set(toks.tolist()))[:48]}"]
+    if W is not None and q is not None:
+        xs4, sx, sumx = (np_(t) for t in q)
+        for br in sorted(set((rows // BROW).tolist()))[:4]:
+            r0, r1 = br * BROW, min((br + 1) * BROW, W.d_out)
+            off = W.hp_row_offsets[br:br + 2].clone()
+            b0, b1 = int(off[0]), int(off[1])
+            Ws = V9WeightContainer(
+                W_low_packed=W.W_low_packed[r0:r1].contiguous(), W_high_blocks_packed=W.W_high_blocks_packed[b0:b1].contiguous(),
+                scale_u4=W.scale_u4[r0:r1].contiguous(), zero_u4=W.zero_u4[r0:r1].contiguous(),
+                hp_row_offsets=(off - b0).to(torch.int32), hp_col_indices=W.hp_col_indices[b0:b1].contiguous(),
+                perm=W.perm, block_shape=W.block_shape, d_out=r1 - r0, d_in=W.d_in)
+            ref = oracle_fused(container_np(Ws), xs4, sumx, sx)
+            for nm, y in zip(names, (a, b)):
+                d = np.abs(y[r0:r1] - ref)
+                lines.append(f"  block-row {br}: {nm} kernel vs oracle: worst {d.max():.4g}, {int((d > ATOL + RTOL * np.abs(ref)).sum())} outside")
+    raise AssertionError("\n".join(lines))

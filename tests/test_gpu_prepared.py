@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from oracle import w4a4_oracle as O
-from helpers import assert_close_fp16, container_np, make_case, np_, oracle_fused
+from helpers import assert_close_fp16, assert_kernels_agree, container_np, make_case, np_, oracle_fused
 
 pytestmark = pytest.mark.gpu
 
@@ -173,7 +173,7 @@ def test_automatic_kernel_choice_between_64_and_255_tokens(ops, T, N, K):
             Wd.scale_u4, Wd.zero_u4, N, K)
     Ys = ops.fused_dense_sparse_e2e_cuda(*args, force="stream")
     Yt = ops.fused_dense_sparse_e2e_cuda(*args, force="tensor")
-    assert_close_fp16(np_(Yt), np_(Ys), "tensor vs stream")
+    assert_kernels_agree(Yt, Ys, "tensor vs stream", W, ops.activation_quant_cuda(X.cuda(), Wd.perm), ("tensor-core", "streaming"))
     for pr in (None, prep):
         Ya = ops.fused_dense_sparse_e2e_cuda(*args, prepared=pr)
         assert torch.equal(Ya, Ys) or torch.equal(Ya, Yt)

@@ -52,7 +52,9 @@ enum {
 #define W4A4_FLAG_OUT_TOKEN_MAJOR 0x1  /* write Y as (T, N) instead of (N, T)          */
 #define W4A4_FLAG_FORCE_STREAM    0x2  /* force the weight-streaming split-K kernel     */
 #define W4A4_FLAG_FORCE_TENSOR    0x4  /* force the tcgen05 tensor-core kernel          */
-#define W4A4_FLAG_CODES_E4M3      0x8  /* *_expanded entry points: XE holds e4m3 codes (w4a4_expand_activations_fmt) */
+#define W4A4_FLAG_CODES_E4M3      0x8  /* *_expanded entry points: XE holds W4A4_CODES_E4M3 bytes (for prepared weights) */
+#define W4A4_FLAG_CODES_E4M3_PACKED 0x10 /* *_expanded entry points: XE holds W4A4_CODES_E4M3_PACKED bytes (for packed
+                                            weights); w4a4_dump_accumulators: run the fp8 instantiation on packed weights */
 
 int w4a4_abi_version(void);
 const char* w4a4_status_string(int status);
@@ -205,18 +207,31 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
                                            const int32_t* hp_col_indices, const void* scale_u4,
                                            const void* zero_u4, void* Y, int T, int K, int N, int nnz,
                                            int flags, void* workspace, size_t workspace_bytes, void* stream);
-/* The same with activations expanded once for several linears.  The tensor-core kernel runs fp8 MMAs on
- * e4m3 codes against prepared weights.  w4a4_expand_activations_fmt with
- * W4A4_CODES_E4M3 writes the e4m3 form (same group-major, chunk-swizzled layout; inside a packed word
- * the codes keep their natural order instead of the even-then-odd order of the s8 form;
- * W4A4_CODES_S8 is what w4a4_expand_activations writes).  Pass such a buffer to
- * w4a4_fused_dense_sparse_expanded_prepared with W4A4_FLAG_CODES_E4M3 and the prepared weights.  The
- * flag alone says which bytes XE holds: prepared pointers given WITHOUT the flag (s8 codes) are
- * rejected with W4A4_ERR_BAD_ARG, and so are e4m3 codes without prepared weights for every operand in
- * use.  A call with e4m3 codes always runs the tensor-core kernel, whatever the token count (the
- * streaming kernel reads s8 codes; W4A4_FLAG_FORCE_STREAM with e4m3 codes is W4A4_ERR_BAD_ARG). */
+/* The same with activations expanded once for several linears.  w4a4_expand_activations_fmt writes the
+ * codes in one of three forms (same group-major, chunk-swizzled layout, one byte per code):
+ *   W4A4_CODES_S8           sign-extended s8, inside a packed word the four even-indexed codes then the four
+ *                           odd-indexed ones (what w4a4_expand_activations writes).  Read by the streaming
+ *                           kernel and by the tensor-core kernel's integer MMAs on the packed weights.
+ *   W4A4_CODES_E4M3         e4m3 encodings of the same integers in their natural order.  Read by fp8 MMAs
+ *                           against PREPARED weights: pass the buffer to
+ *                           w4a4_fused_dense_sparse_expanded_prepared with W4A4_FLAG_CODES_E4M3.
+ *   W4A4_CODES_E4M3_PACKED  e4m3 encodings in the even-then-odd order.  Read by fp8 MMAs against the PACKED
+ *                           weights, whose nibbles the kernel turns into e4m3 numbers on the SM with three
+ *                           logic operations per eight codes (a nibble with bit 3 flipped, alone in its
+ *                           byte, is the e4m3 value (code + 8) * 2^-9; the offset leaves with the zero-point
+ *                           term, which is why this form needs the group sums).  Pass the buffer with
+ *                           W4A4_FLAG_CODES_E4M3_PACKED and NULL prepared pointers.
+ * The flags alone say which bytes XE holds and a mismatch is W4A4_ERR_BAD_ARG, never a silent
+ * reinterpretation: prepared pointers without W4A4_FLAG_CODES_E4M3, W4A4_FLAG_CODES_E4M3 without
+ * prepared weights for every operand in use, both flags at once.  A call with e4m3 codes of either form
+ * always runs the tensor-core kernel, whatever the token count (the streaming kernel reads s8 codes;
+ * W4A4_FLAG_FORCE_STREAM with e4m3 codes is W4A4_ERR_BAD_ARG).  The entry points that expand the codes
+ * themselves pick W4A4_CODES_E4M3 when prepared weights are given, else W4A4_CODES_S8 - or
+ * W4A4_CODES_E4M3_PACKED when the environment variable W4A4_PREFILL_F8=1 is set and the call carries
+ * the group sums. */
 #define W4A4_CODES_S8   0
 #define W4A4_CODES_E4M3 1
+#define W4A4_CODES_E4M3_PACKED 2
 int w4a4_expand_activations_fmt(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
                                 int code_format, void* stream);
 int w4a4_fused_dense_sparse_expanded_prepared(const void* W_low, const void* W_high, const void* W_low_prepared,

@@ -64,6 +64,8 @@ FLAG_OUT_TOKEN_MAJOR = 0x1
 FLAG_FORCE_STREAM = 0x2
 FLAG_FORCE_TENSOR = 0x4
 FLAG_CODES_E4M3 = 0x8
+FLAG_CODES_E4M3_PACKED = 0x10
+CODES_S8, CODES_E4M3, CODES_E4M3_PACKED = 0, 1, 2
 
 _lib = None
 

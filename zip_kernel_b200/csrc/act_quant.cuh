@@ -43,7 +43,7 @@ struct QuantParams {
   int vec_ok;             // 1 when every row start is 16-byte aligned
   int C;                  // CTAs (cluster size) per token; divides K/128
   int stage_row;          // 1: perm given, C == 1: the dynamic shared memory holds the raw row, gathered while quantising
-  int fmt;                // bytes of XE: 0 = s8 codes (even/odd order), 1 = e4m3 encodings in natural order (see expand_word)
+  int fmt;                // bytes of XE: 0 = s8 codes (even/odd order), 1 = e4m3 in natural order, 2 = e4m3 in even/odd order (see expand_word)
   // Fused prologues (SRC template parameter of the kernel): the value that is quantised is a function of the input row.
   const __half* norm_w;   // SRC_RMSNORM: (K) fp16 weight of the normalisation
   float eps;              // SRC_RMSNORM: added to the mean square
@@ -131,10 +131,12 @@ __device__ __forceinline__ uint4 transform8(const QuantParams& p, const __half* 
 // One packed word (8 codes) -> 8 bytes.  fmt 0: sign-extended s8, its four even-indexed codes, then its
 // four odd-indexed ones (the order the s8 widening of the weights produces).  fmt 1: e4m3 encodings in the
 // codes' natural order (the order of the weights' table look-up and of prepared weights).
+// fmt 2: e4m3 encodings in the even-then-odd order of fmt 0 (read against packed weights widened on the SM).
 __device__ __forceinline__ uint2 expand_word(uint32_t w, int fmt = 0) {
-  if (fmt == 1) {
+  if (fmt != 0) {
     uint2 r;
     nib8_to_e4m3(w, r.x, r.y);
+    if (fmt == 2) r = make_uint2(prmt_b32(r.x, r.y, 0x6420u), prmt_b32(r.x, r.y, 0x7531u));
     return r;
   }
   return make_uint2(nib_lo_s8(w), nib_hi_s8(w));

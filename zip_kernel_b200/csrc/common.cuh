@@ -253,6 +253,16 @@ __device__ __forceinline__ void nib8_to_e4m3(uint32_t w, uint32_t& first, uint32
   second = prmt_b32(POS_LO, POS_HI, w >> 16) ^ prmt_b32(NEGC_LO, NEGC_HI, t >> 16) ^ m1;
 }
 
+// The same two nibble sets as e4m3 bytes WITHOUT a table: an e4m3 byte 0x00..0x0F (exponent field 0 or 1) has
+// the value byte * 2^-9 - the subnormals and the first binade of any binary float format are one linear
+// ramp - so a nibble moved into a byte of its own IS a float proportional to the nibble.  Flipping bit 3
+// turns the two's-complement nibble of a code c into c + 8 (0..15): four e4m3 lanes of value (c + 8) * 2^-9
+// for one and two logic operations, the cost of the s8 widening above.  The offset 8 multiplies the
+// activations' group sum and leaves with the zero-point term.
+__device__ __forceinline__ uint32_t nib_lo_off8(uint32_t w) { return (w & 0x0F0F0F0Fu) ^ 0x08080808u; }
+__device__ __forceinline__ uint32_t nib_hi_off8(uint32_t w) { return ((w >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u; }
+constexpr float OFF8_UNIT = 1.f / 512.f;          // value of the e4m3 byte 0x01
+
 // ---------------------------------------------------------------- legacy int8 MMA (decode path)
 // D(16x8,s32) += A(16x32,s8,row) * B(32x8,s8,col)
 __device__ __forceinline__ void mma_m16n8k32_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,

@@ -63,13 +63,13 @@ constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums s
 constexpr int A_COLS = BCOL / 4;                  // 32 TMEM columns hold one widened row of 128 s8
 constexpr int TMEM_COLS = 512;                    // the whole tensor memory of the SM (one CTA per SM)
 // Tensor-memory columns.  Accumulator buffers first (the MMAs run that many steps ahead of the fold), then
-// the widened weight tiles (packed weights only), then the fp32 accumulator of the zero-point term.
-// Prepared weights leave room for a third accumulator buffer.
-template <bool PREP>
+// the widened weight tiles (integer instantiation only), then the fp32 accumulator of the zero-point term.
+// The fp8 instantiations read A from shared memory and have room for a third accumulator buffer.
+template <bool A_TMEM>
 struct TmemLayout {
-  static constexpr int ACC_BUFS = PREP ? 3 : 2;
+  static constexpr int ACC_BUFS = A_TMEM ? 2 : 3;
   static constexpr int A_COL0 = ACC_BUFS * TN;
-  static constexpr int Z_COL0 = A_COL0 + (PREP ? 0 : A_BUFS * A_COLS);
+  static constexpr int Z_COL0 = A_COL0 + (A_TMEM ? A_BUFS * A_COLS : 0);
   static_assert(Z_COL0 + TN <= TMEM_COLS, "tensor memory capacity");
 };
 constexpr int ZT_BYTES = ROWS * 128;              // one tf32 operand tile of the zero-point term: 128 rows x 32 values
@@ -79,7 +79,10 @@ constexpr int ZT_BYTES = ROWS * 128;              // one tf32 operand tile of th
 #endif
 constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_UNPACK0 = 2, N_UNPACK_WARPS = 4, WARP_FOLD0 = 6;
 constexpr int N_FOLD_WARPS = W4A4_FOLD_WARPS;     // a multiple of 4: a warp reads only its quarter of the TMEM lanes
-constexpr int THREADS = (WARP_FOLD0 + N_FOLD_WARPS) * 32;
+constexpr int WARP_TMAX = WARP_FOLD0 + N_FOLD_WARPS;   // the activation copies have an issuing thread of their own
+constexpr int WARP_MMA2 = WARP_TMAX + 1;               // ... and the odd steps' MMAs too
+constexpr int THREADS = (WARP_MMA2 + 1) * 32;
+static_assert(A_BUFS == 2, "step parity = widened-weight buffer = issuing thread");
 constexpr int FOLD_THREADS = N_FOLD_WARPS * 32;
 constexpr int COLS_PER_FOLD = TN / (N_FOLD_WARPS / 4);   // a fold thread owns one row and this many tokens
 static_assert(N_FOLD_WARPS % 4 == 0 && COLS_PER_FOLD % 32 == 0, "fold warps tile the accumulator in 32-lane x 32-column pieces");
@@ -108,34 +111,54 @@ struct Params {
   int sz_vec;
   int band;                 // token tiles per band of the CTA order (>= 1)
   float sparse_weight;
+#ifdef W4A4_TRACE
+  long long* trace;         // [16 events][64 steps] clock stamps of one CTA
+  int trace_cta;
+#endif
 };
+#ifdef W4A4_TRACE
+#define TRACE(ev, n) do { if (lin == p.trace_cta && (n) < 64) p.trace[(ev) * 64 + (n)] = clock64(); } while (0)
+#else
+#define TRACE(ev, n) do { } while (0)
+#endif
 
 inline bool supported(int T, int K, int N) { return T >= 1 && K >= 128 && N >= 1; }
 
 // Three instantiations.  <F8 = false, PREP = false>: packed nibbles are copied in (8 KB per step), widened to
-// s8 on the SM, integer MMAs (kind::i8) - for activation codes the caller expanded as s8.  <F8 = true, PREP =
-// false>: the same packed copies, but the unpack warps turn every nibble into its e4m3 encoding (exact for
-// -8..7) with byte-permute table look-ups, the activation codes are e4m3 bytes too and the MMA is
-// kind::f8f6f4 with fp32 accumulators - the same integers, as floats - so the fold needs no int -> float
-// conversion.  <F8 = true, PREP = true>: the caller supplies weights prepared once as e4m3 bytes (16 KB per
-// step, the A operand as it lands): no unpack work either.
-template <bool PREP>
+// s8 on the SM, integer MMAs (kind::i8) - for activation codes the caller expanded as s8, and for calls
+// without activation group sums.  <F8 = true, PREP = false>: the same packed copies and the same three logic
+// operations per 8 codes, but the bytes the unpack warps write are read as e4m3 numbers: a nibble with bit 3
+// flipped, alone in its byte, is the e4m3 value (code + 8) * 2^-9 (nib_lo_off8), the activation codes are
+// e4m3 integers in the same even/odd order, and the MMA is kind::f8f6f4 with fp32 accumulators that hold
+// 2^-9 * (acc + 8 * sumX) exactly.  The fold then needs no int -> float conversion - the instruction that
+// bounds the integer instantiation - and the offset 8 * sumX leaves with the zero-point term, which already
+// is a product with sumX on the tensor core (dense groups), or with one extra FMA per element (the few
+// residual steps).  <F8 = true, PREP = true>: the caller supplies weights prepared once as e4m3 bytes (16 KB
+// per step, the A operand as it lands): no unpack work either.
+template <bool F8, bool PREP>
 struct SmemLayout {
-  static constexpr int W_STAGES = PREP ? 5 : 6;               // weight tiles in flight
-  static constexpr int X_STAGES = PREP ? 5 : 6;               // activation tiles in flight = depth of the "ready" / "step done" rings
+  static constexpr bool OFF8 = F8 && !PREP;                   // packed weights widened into e4m3 operand tiles in shared memory
+  static constexpr int W_STAGES = PREP ? 5 : (F8 ? 4 : 6);    // weight tiles in flight
+  static constexpr int X_STAGES = PREP ? 5 : (F8 ? 5 : 6);    // activation tiles in flight = depth of the "ready" / "step done" rings
   static constexpr int WP_BYTES = PREP ? ROWS * BCOL : ROWS * GROUP_BYTES;
+  static constexpr int AT_BYTES = ROWS * BCOL;                // one widened weight tile as an MMA operand
   static_assert(!PREP || W_STAGES == X_STAGES, "with prepared weights both copies of a step share a ring slot index");
-    static constexpr size_t wp = 0;
+  static constexpr size_t wp = 0;
   static constexpr size_t x = wp + (size_t)W_STAGES * WP_BYTES;
-  static constexpr size_t sz = x + (size_t)X_STAGES * X_BYTES;                 // float [SZ_CHUNK][128]: scale (/16 for int8 accumulators)
+  static constexpr size_t at = x + (size_t)X_STAGES * X_BYTES;                  // e4m3 [A_BUFS][128 rows][128]: widened weights (K-major, swizzled)
+  static constexpr size_t sz = at + (size_t)(OFF8 ? A_BUFS * AT_BYTES : 0);     // float [SZ_CHUNK][128]: scale (/16 for int8 accumulators)
   static constexpr size_t zb = sz + (size_t)SZ_CHUNK * ROWS * 4;                // tf32 [2][TN tokens][32]: group sums, twice (K-major, swizzled)
   static constexpr size_t za = zb + (size_t)2 * ZT_BYTES;                       // tf32 [128 rows][32]: high and low half of scale * zero
-  static constexpr size_t raw = za + (size_t)ZT_BYTES;                          // 2 x 16 bytes per (row, half): fp16 scales, zeros
+  static constexpr size_t za2 = za + (size_t)ZT_BYTES;                          // tf32 [128 rows][32]: 8 * scale in the first 16 values
+  static constexpr size_t raw = za2 + (size_t)(OFF8 ? ZT_BYTES : 0);            // 2 x 16 bytes per (row, half): fp16 scales, zeros
   static constexpr size_t sxs = raw + (size_t)2 * ROWS * 32;                    // float  [TN]
   static constexpr size_t bars = sxs + (size_t)TN * 4;
   static constexpr size_t total = bars + 256;
+  static_assert(1024 + total <= 232448, "shared memory of one SM");
 };
-inline size_t smem_bytes(bool f8) { return 1024 + (f8 ? SmemLayout<true>::total : SmemLayout<false>::total); }
+inline size_t smem_bytes(bool f8, bool prep) {
+  return 1024 + (prep ? SmemLayout<true, true>::total : f8 ? SmemLayout<true, false>::total : SmemLayout<false, false>::total);
+}
 
 // ---------------------------------------------------------------- tcgen05 wrappers
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
@@ -167,14 +190,6 @@ __device__ __forceinline__ void umma_f8(uint32_t tmem_d, uint64_t adesc, uint64_
       "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(IDESC_F8), "r"(accumulate)
-      : "memory");
-}
-// the same with the A operand in tensor memory (row = lane, four e4m3 bytes per 32-bit column)
-__device__ __forceinline__ void umma_f8_ta(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(IDESC_F8), "r"(accumulate)
       : "memory");
 }
 // kind::tf32, tf32 x tf32 -> f32, both operands K-major, M = 128, N = TN (K = 8 per instruction)
@@ -230,6 +245,17 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+// Sum of the 128 integer-valued e4m3 codes of one (group, token) line of the expanded activations (parity dump only).
+__device__ __forceinline__ int e4m3_line_sum(const int8_t* line) {
+  int s = 0;
+  for (int i = 0; i < BCOL; ++i) {
+    const uint32_t b = (uint8_t)line[i], e = (b >> 3) & 15u, m = b & 7u;
+    const int mag = e == 0 ? 0 : (int)(((8u | m) << e) >> 10);
+    s += (b & 0x80u) ? -mag : mag;
+  }
+  return s;
+}
+
 // d = a * b + c on two packed fp32 lanes
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   float2 d;
@@ -245,9 +271,10 @@ __global__ void __launch_bounds__(THREADS, 1)
 prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_wh,
                     const Params p) {
   static_assert(F8 || !PREP, "prepared weights are e4m3 bytes");
-  using SmemLayout = pre::SmemLayout<PREP>;
+  using SmemLayout = pre::SmemLayout<F8, PREP>;
   constexpr int W_STAGES = SmemLayout::W_STAGES, X_STAGES = SmemLayout::X_STAGES, WP_BYTES = SmemLayout::WP_BYTES;
-  constexpr int ACC_BUFS = TmemLayout<PREP>::ACC_BUFS, A_COL0 = TmemLayout<PREP>::A_COL0, Z_COL0 = TmemLayout<PREP>::Z_COL0;
+  constexpr int ACC_BUFS = TmemLayout<!F8>::ACC_BUFS, A_COL0 = TmemLayout<!F8>::A_COL0, Z_COL0 = TmemLayout<!F8>::Z_COL0;
+  constexpr int AT_BYTES = SmemLayout::AT_BYTES;
   static_assert(ACC_BUFS < X_STAGES, "the fold warps' arrival for step n + ACC_BUFS must fall into that step's barrier phase");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -256,6 +283,10 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   float* szs = reinterpret_cast<float*>(sm + SmemLayout::sz);
   unsigned char* zb_tiles = sm + SmemLayout::zb;
   unsigned char* za_tile = sm + SmemLayout::za;
+  unsigned char* za2_tile = sm + SmemLayout::za2;
+  unsigned char* a_tiles = sm + SmemLayout::at;
+  // packed nibbles read as e4m3 numbers: accumulators carry the offset 8 * sumX and the unit 2^-9
+  constexpr bool OFF8 = F8 && !PREP;
   float* sxs = reinterpret_cast<float*>(sm + SmemLayout::sxs);
   uint64_t* bars = reinterpret_cast<uint64_t*>(sm + SmemLayout::bars);
   uint64_t* w_full = bars;                      // [W_STAGES]
@@ -272,6 +303,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 
   grid_launch_dependents();
   const int tid = threadIdx.x;
+#ifdef W4A4_TRACE
+  const long long t_start = clock64();
+#endif
   const int warp = tid >> 5;
   const int lane = tid & 31;
   // CTAs are dispatched in the order of their linear index.  Bands of `band` token tiles are walked
@@ -311,46 +345,59 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   const int n_windows = (p.nd + SZ_CHUNK - 1) / SZ_CHUNK;     // zero-point term: one small tf32 MMA batch per window of 16 groups
 
   if (warp == WARP_TMA) {
-    // ------------------------------------------------------------ TMA producer
+    // ------------------------------------------------------------ weight copies
+    // One thread's wait / expect / copy sequence takes 300-400 clk in this kernel (a lone thread among polling
+    // warps), more than the MMAs of a step: weights and activations each have an issuing thread of their own.
     if (lane == 0) {
       bool ok = true;
-      // weights do not depend on the preceding kernel: fill the packed ring first
-      const int n_pre = min(W_STAGES, n_steps);
-      auto issue_w = [&](int n, int st) {
-        // prepared weights are the A operand as it is: the copy reports to the step's readiness barrier
-        uint64_t* bar = PREP ? &ready[st] : &w_full[st];
-        mbar_arrive_expect_tx(bar, WP_BYTES);
-        if (n < p.nd) tma_load_2d(wp_ring + st * WP_BYTES, &tm_w, n * (PREP ? BCOL : GROUP_BYTES), row0, bar);
-        else          tma_load_2d(wp_ring + st * WP_BYTES, &tm_wh, 0, (b_lo + n - p.nd) * BROW, bar);
-      };
-      for (int n = 0; n < n_pre; ++n) issue_w(n, n);
-      grid_dependency_wait();
-      int ws = 0, xs = 0;
+      int ws = 0;
       uint32_t wph = 1;
       for (int n = 0; n < n_steps && ok; ++n) {
-        if (n >= n_pre) {
+        if (n >= W_STAGES) {
           // packed tiles are released by the unpack warps, prepared tiles by the completion of the MMAs that read them
-          ok = PREP ? mbar_wait_relaxed(&done[ws], ((n - W_STAGES) / W_STAGES) & 1, SITE_PRE_WEMPTY)
-                  : mbar_wait_relaxed(&w_empty[ws], wph, SITE_PRE_WEMPTY);
+          ok = PREP ? mbar_wait(&done[ws], wph, SITE_PRE_WEMPTY) : mbar_wait(&w_empty[ws], wph, SITE_PRE_WEMPTY);
           if (!ok) break;
-          issue_w(n, ws);
         }
+        // prepared weights are the A operand as it is: the copy reports to the step's readiness barrier
+        uint64_t* bar = PREP ? &ready[ws] : &w_full[ws];
+        mbar_arrive_expect_tx(bar, WP_BYTES);
+        if (n < p.nd) tma_load_2d(wp_ring + ws * WP_BYTES, &tm_w, n * (PREP ? BCOL : GROUP_BYTES), row0, bar);
+        else          tma_load_2d(wp_ring + ws * WP_BYTES, &tm_wh, 0, (b_lo + n - p.nd) * BROW, bar);
+        TRACE(0, n);
         if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
+      }
+    }
+  } else if (warp == WARP_TMAX) {
+    // ------------------------------------------------------------ activation copies
+    if (lane == 0) {
+      bool ok = true;
+      int xs = 0;
+      uint32_t xph = 1;
+      grid_dependency_wait();                 // the expanded codes are written by the preceding kernel
+      const int8_t* src0 = p.XE + (size_t)tok0 * BCOL;
+      const size_t gstride = (size_t)p.t_pad * BCOL;
+      for (int n = 0; n < n_steps && ok; ++n) {
         // the slot is free once the MMAs of step n - X_STAGES have completed
-        if (n >= X_STAGES) ok = mbar_wait_relaxed(&done[xs], ((n - X_STAGES) / X_STAGES) & 1, SITE_PRE_XEMPTY);
+        if (n >= X_STAGES) ok = mbar_wait(&done[xs], xph, SITE_PRE_XEMPTY);
         if (!ok) break;
         const int g = n < p.nd ? n : ld_plain(p.hp_col_indices + b_lo + n - p.nd);
         mbar_arrive_expect_tx(&ready[xs], X_BYTES);
         // TN consecutive tokens of one group: contiguous and already in operand layout
-        bulk_load_1d(x_ring + xs * X_BYTES, p.XE + ((size_t)g * p.t_pad + tok0) * BCOL, X_BYTES, &ready[xs]);
-        if (++xs == X_STAGES) xs = 0;
+        bulk_load_1d(x_ring + xs * X_BYTES, src0 + g * gstride, X_BYTES, &ready[xs]);
+        TRACE(1, n);
+        if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
       }
     }
-  } else if (warp == WARP_MMA) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp == WARP_MMA || warp == WARP_MMA2) {
+    // ------------------------------------------------------------ MMA issuers
+    // Two issuing threads take the even and the odd steps.  An issuing thread is stalled while the tensor
+    // pipe's queue is full and then needs 200-300 clk for its own loop (a lone thread among polling warps):
+    // with one thread the pipe drained in between.  Steps are independent of one another - each has an
+    // accumulator buffer, operand slots and a completion barrier of its own - so their MMAs need no order.
     if (lane == 0) {
       bool ok = true;
-      int xs = 0;
+      const int par = warp == WARP_MMA ? 0 : 1;
+      int xs = par % X_STAGES;
       uint32_t xph = 0;
       int z_next = 0;
       // Z[n, t] += sum over the window's 16 groups of (scale * zero)[n, g] * sumX[t, g]: both factors
@@ -364,24 +411,32 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         const uint64_t zb_desc = smem_desc_sw128(zb_tiles + (k & 1) * ZT_BYTES);
 #pragma unroll
         for (int j = 0; j < 4; ++j) umma_tf32(tmem_base + Z_COL0, za_desc + j * 2, zb_desc + j * 2, (k > 0 || j > 0) ? 1u : 0u);
+        if (OFF8) {
+          // + sum over the window of (8 * scale)[n, g] * sumX[t, g]: the offset of the weights' e4m3 form
+          const uint64_t za2_desc = smem_desc_sw128(za2_tile);
+#pragma unroll
+          for (int j = 0; j < 2; ++j) umma_tf32(tmem_base + Z_COL0, za2_desc + j * 2, zb_desc + j * 2, 1u);
+        }
         umma_commit(z_done);
         return true;
       };
-      int buf = 0, ab = 0;
-      const uint64_t bdesc0 = smem_desc_sw128(x_ring), adesc0 = smem_desc_sw128(wp_ring);
+      int buf = par % ACC_BUFS;
+      const int ab = par;
+      const uint64_t bdesc0 = smem_desc_sw128(x_ring), adesc0 = smem_desc_sw128(wp_ring), atdesc0 = smem_desc_sw128(a_tiles);
       const uint32_t d0 = tmem_base, a0 = tmem_base + A_COL0;
       const bool with_z = p.Y != nullptr && n_windows > 0;
       int z_due = ACC_BUFS;          // step at which the next window's zero-point MMAs are issued
-      for (int n = 0; n < n_steps && ok; ++n) {
+      for (int n = par; n < n_steps && ok; n += 2) {
         // a window's tiles are ready once the fold warps have passed its boundary, which they
-        // have when they return the accumulator of the window's first step
-        if (with_z && n == z_due && z_next < n_windows) {
+        // have when they return the accumulator of the window's first step (the even thread issues them)
+        if (par == 0 && with_z && n >= z_due && z_next < n_windows) {
           ok = issue_zero_term(z_next++);
           z_due += SZ_CHUNK;
           if (!ok) break;
         }
         if (!(PREP ? mbar_wait_relaxed(&ready[xs], xph, SITE_PRE_XFULL) : mbar_wait(&ready[xs], xph, SITE_PRE_XFULL))) { ok = false; break; }
         tc_fence_after();
+        TRACE(2, n);
         const uint64_t bdesc = bdesc0 + (uint64_t)(xs * (X_BYTES >> 4));
         const uint32_t d = d0 + buf * TN, a = a0 + ab * A_COLS;
         if (PREP) {
@@ -391,10 +446,11 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           umma_f8(d, adesc + 4, bdesc + 4, 1);
           umma_f8(d, adesc + 6, bdesc + 6, 1);
         } else if (F8) {
-          umma_f8_ta(d, a, bdesc, 0);                  // K = 32 each: 8 columns of A, 32 bytes of B
-          umma_f8_ta(d, a + 8, bdesc + 2, 1);
-          umma_f8_ta(d, a + 16, bdesc + 4, 1);
-          umma_f8_ta(d, a + 24, bdesc + 6, 1);
+          const uint64_t adesc = atdesc0 + (uint64_t)(ab * (AT_BYTES >> 4));
+          umma_f8(d, adesc, bdesc, 0);
+          umma_f8(d, adesc + 2, bdesc + 2, 1);
+          umma_f8(d, adesc + 4, bdesc + 4, 1);
+          umma_f8(d, adesc + 6, bdesc + 6, 1);
         } else {
           umma_i8_ta(d, a, bdesc, 0);
           umma_i8_ta(d, a + 8, bdesc + 2, 1);
@@ -402,11 +458,13 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           umma_i8_ta(d, a + 24, bdesc + 6, 1);
         }
         umma_commit(&done[xs]);
-        if (++xs == X_STAGES) { xs = 0; xph ^= 1; }
-        if (++buf == ACC_BUFS) buf = 0;
-        ab ^= 1;
+        TRACE(3, n);
+        xs += 2;
+        if (xs >= X_STAGES) { xs -= X_STAGES; xph ^= 1; }
+        buf += 2;
+        if (buf >= ACC_BUFS) buf -= ACC_BUFS;
       }
-      while (ok && p.Y != nullptr && z_next < n_windows) ok = issue_zero_term(z_next++);
+      while (par == 0 && ok && p.Y != nullptr && z_next < n_windows) ok = issue_zero_term(z_next++);
     }
   } else if (warp < WARP_FOLD0) {
     // ------------------------------------------------------------ unpack warps
@@ -420,6 +478,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     for (int n = 0; n < (PREP ? 0 : n_steps); ++n) {     // prepared weights need no widening
       const int buf = n % A_BUFS;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&w_full[ws], wph, SITE_PRE_WFULL));
+      if (warp == WARP_UNPACK0 && lane == 0) TRACE(6, n);
       // the A buffer was last read by the MMAs of step n - 2
       if (ok && n >= A_BUFS)
         ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&done[(n - A_BUFS) % X_STAGES], ((n - A_BUFS) / X_STAGES) & 1, SITE_PRE_AEMPTY));
@@ -437,21 +496,32 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             if (F8) {
-              nib8_to_e4m3(q[e], v[(c * 4 + e) * 2], v[(c * 4 + e) * 2 + 1]);      // codes in their natural order
+              v[(c * 4 + e) * 2] = nib_lo_off8(q[e]);                                 // even codes + 8, then odd ones + 8
+              v[(c * 4 + e) * 2 + 1] = nib_hi_off8(q[e]);
             } else {
               v[(c * 4 + e) * 2] = nib_lo_x16(q[e]);                                  // even codes, then odd ones
               v[(c * 4 + e) * 2 + 1] = nib_hi_x16(q[e]);
             }
           }
         }
-        tmem_st32(a_lane + buf * A_COLS, v);
-        tc_fence_before();
+        if (F8) {
+          // the widened row as an fp8 MMA operand row: 16-byte chunk c at c ^ (row & 7) (128-byte swizzle)
+          const uint32_t dst = smem_u32(a_tiles) + buf * AT_BYTES + urow * BCOL;
+#pragma unroll
+          for (int c = 0; c < 8; ++c)
+            sts_v4(dst + ((c ^ (urow & 7)) << 4), make_uint4(v[4 * c], v[4 * c + 1], v[4 * c + 2], v[4 * c + 3]));
+          fence_proxy_async_smem();                  // this thread's row -> visible to the tensor core
+        } else {
+          tmem_st32(a_lane + buf * A_COLS, v);
+          tc_fence_before();
+        }
       }
       __syncwarp();
       if (ok && lane == 0) {
         mbar_arrive(&w_empty[ws]);
         mbar_arrive(&ready[n % X_STAGES]);
       }
+      if (warp == WARP_UNPACK0 && lane == 0) TRACE(7, n);
       if (++ws == W_STAGES) { ws = 0; wph ^= 1; }
     }
   } else {
@@ -462,7 +532,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     const int rl = quarter * 32 + lane;          // local row
     const int row = row0 + rl;
     const int c0 = chalf * COLS_PER_FOLD;
-    const uint32_t szs_a = smem_u32(szs), zb_a = smem_u32(zb_tiles), za_a = smem_u32(za_tile);
+    const uint32_t szs_a = smem_u32(szs), zb_a = smem_u32(zb_tiles), za_a = smem_u32(za_tile), za2_a = smem_u32(za2_tile);
+    // scale factor of an accumulator: 1/16 undoes the s8 widening, 512 the unit of the e4m3 bytes
+    constexpr float ACC_UNIT = OFF8 ? 512.f : (F8 ? 1.f : 0.0625f);
     grid_dependency_wait();
     for (int i = ft; i < TN; i += FOLD_THREADS)
       sxs[i] = (tok0 + i < p.T && p.scale_x) ? __half2float(ld_plain(p.scale_x + tok0 + i)) : 0.f;
@@ -532,14 +604,24 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       for (int i = 0; i < 4; ++i) {
         const float2 s2 = __half22float2(hs[i]), z2 = __half22float2(hz[i]);
         // int8 path: the accumulators carry the factor 16 of the widened nibbles
-        sts_f1(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 4, s2.x * (F8 ? 1.f : 0.0625f));
-        sts_f1(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 4, s2.y * (F8 ? 1.f : 0.0625f));
+        sts_f1(szs_a + ((lhalf * 8 + 2 * i) * ROWS + lrow) * 4, s2.x * ACC_UNIT);
+        sts_f1(szs_a + ((lhalf * 8 + 2 * i + 1) * ROWS + lrow) * 4, s2.y * ACC_UNIT);
         // scale * zero is exact in fp32 (two 11-bit significands); its upper 11 bits and the exact rest are both tf32 values
         const float c0_ = s2.x * z2.x, c1_ = s2.y * z2.y;
         chi[2 * i] = __uint_as_float(__float_as_uint(c0_) & 0xFFFFE000u);
         chi[2 * i + 1] = __uint_as_float(__float_as_uint(c1_) & 0xFFFFE000u);
         clo[2 * i] = c0_ - chi[2 * i];
         clo[2 * i + 1] = c1_ - chi[2 * i + 1];
+      }
+      if (OFF8) {
+        // 8 * scale, exact: values lhalf * 8 .. + 7 of the row (the MMAs read the first 16 values only)
+        const uint32_t rowb = za2_a + lrow * 128;
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float2 sa = __half22float2(hs[2 * q]), sb = __half22float2(hs[2 * q + 1]);
+          sts_v4(rowb + (((lhalf * 2 + q) ^ (lrow & 7)) << 4),
+                 make_uint4(__float_as_uint(8.f * sa.x), __float_as_uint(8.f * sa.y), __float_as_uint(8.f * sb.x), __float_as_uint(8.f * sb.y)));
+        }
       }
       // operand row = weight row: values lhalf * 8 .. + 7 (upper halves) and 16 + lhalf * 8 .. (rests)
       const uint32_t rowa = za_a + lrow * 128;
@@ -572,19 +654,20 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (lane == 0) mbar_arrive(z_full);
       }
       float f = 0.f;
-      int blk = 0;
+      int blk = 0, gcol = n;
       if (is_dense) {
         f = lds_f1(szs_a + ((n % SZ_CHUNK) * ROWS + rl) * 4);
       } else {
         blk = b_lo + n - p.nd;
+        gcol = ld_plain(p.hp_col_indices + blk);
         if (p.scale_u4 && row < p.N)
-          f = __half2float(ld_plain(p.scale_u4 + (size_t)row * p.ng + ld_plain(p.hp_col_indices + blk))) *
-              (F8 ? 1.f : 0.0625f) * p.sparse_weight;
+          f = __half2float(ld_plain(p.scale_u4 + (size_t)row * p.ng + gcol)) * ACC_UNIT * p.sparse_weight;
       }
       const int buf = n % ACC_BUFS;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&done[n % X_STAGES], (n / X_STAGES) & 1, SITE_PRE_ACCFULL));
       if (!ok) continue;
       tc_fence_after();
+      if (ft == 0) TRACE(4, n);
       const f32x2_t f2 = pack_f32x2(f, f);
 #pragma unroll
       for (int cc = 0; cc < COLS_PER_FOLD; cc += 32) {
@@ -592,11 +675,39 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * TN + c0 + cc, a);
         // y += acc * (scale / 16): the zero-point term is accumulated by the tensor core (see the MMA thread)
 #pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          f32x2_t v;
-          if (F8) asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(a[i]), "r"(a[i + 1]));     // fp32 accumulators: the integers as floats
-          else v = cvt_s32x2_f32x2(a[i], a[i + 1]);
-          y2[(cc + i) >> 1] = fma_f32x2(v, f2, y2[(cc + i) >> 1]);
+        if (OFF8 && (!is_dense || DUMP)) {
+          // A residual step is outside the zero-point windows: take its offset 8 * sumX out here, exactly
+          // (accumulator and sum are small multiples of 2^-9).  The parity dump does the same on every step.
+          const int tile0 = (tok0 + c0 + cc) >> 4, n_tiles = (p.T + 15) >> 4;
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            if (tile0 + h >= n_tiles || gcol >= p.ng) continue;
+            float sv[16];
+            if (p.sumxf != nullptr) {
+              const float4* line = reinterpret_cast<const float4*>(p.sumxf + ((size_t)(tile0 + h) * p.ng + gcol) * 16);
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const float4 s4 = ld_plain(line + q);
+                sv[q * 4] = s4.x; sv[q * 4 + 1] = s4.y; sv[q * 4 + 2] = s4.z; sv[q * 4 + 3] = s4.w;
+              }
+            } else {
+              // only a dump launch comes without the sums: add up the group's codes (any order)
+#pragma unroll 1
+              for (int e = 0; e < 16; ++e) sv[e] = (float)e4m3_line_sum(p.XE + ((size_t)gcol * p.t_pad + (tile0 + h) * 16 + e) * BCOL);
+            }
+#pragma unroll
+            for (int e = 0; e < 16; ++e)
+              a[h * 16 + e] = __float_as_uint(__fmaf_rn(sv[e], -8.f * OFF8_UNIT, __uint_as_float(a[h * 16 + e])));
+          }
+        }
+        if (!(OFF8 && DUMP && is_dense)) {       // (a dump launch writes no output: its dense steps keep the corrected values for the dump only)
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            f32x2_t v;
+            if (F8) asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(a[i]), "r"(a[i + 1]));     // fp32 accumulators: the integers as floats
+            else v = cvt_s32x2_f32x2(a[i], a[i + 1]);
+            y2[(cc + i) >> 1] = fma_f32x2(v, f2, y2[(cc + i) >> 1]);
+          }
         }
         if (DUMP) {
 #pragma unroll
@@ -607,12 +718,12 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
             if (is_dense) {
               const size_t idx = ((size_t)n * p.N + row) * p.T + tok;
               if (p.acc_dump && row < p.N) {
-                if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = F8 ? (int)__uint_as_float(a[i]) : ((int)a[i]) >> 4;
+                if (idx < (size_t)p.ng * p.N * p.T) p.acc_dump[idx] = F8 ? (int)(__uint_as_float(a[i]) * (OFF8 ? 512.f : 1.f)) : ((int)a[i]) >> 4;
                 else record_error(SITE_PRE_DUMP, 1);
               }
             } else if (p.acc_hi_dump) {
               const size_t idx = ((size_t)blk * BROW + rl) * p.T + tok;
-              if (blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = F8 ? (int)__uint_as_float(a[i]) : ((int)a[i]) >> 4;
+              if (blk < p.nnz && idx < (size_t)p.nnz * BROW * p.T) p.acc_hi_dump[idx] = F8 ? (int)(__uint_as_float(a[i]) * (OFF8 ? 512.f : 1.f)) : ((int)a[i]) >> 4;
               else record_error(SITE_PRE_DUMP, 2);
             }
           }
@@ -622,6 +733,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       __syncwarp();
       // the buffer is free again: it will be written by step n + ACC_BUFS
       if (lane == 0 && n + ACC_BUFS < n_steps) mbar_arrive(&ready[(n + ACC_BUFS) % X_STAGES]);
+      if (ft == 0) TRACE(5, n);
     }
 
     // ---------------------------------------------------------- zero-point term
@@ -676,6 +788,9 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   // common exit: every role falls through to here, then the allocating warp frees TMEM
   tc_fence_before();
   __syncthreads();
+#ifdef W4A4_TRACE
+  if (tid == 0) { TRACE(8, 0); if (lin == p.trace_cta) p.trace[8 * 64 + 1] = t_start; }
+#endif
   if (warp == WARP_MMA) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);

@@ -80,14 +80,12 @@ cudaError_t set_kernel_attributes() {
   set(dec::decode_gemm_kernel<1, true>, dec::smem_bytes(1));
   set(dec::decode_gemm_kernel<2, true>, dec::smem_bytes(2));
   set(dec::decode_gemm_kernel<4, true>, dec::smem_bytes(4));
-  set(pre::prefill_gemm_kernel<false, false, false>, pre::smem_bytes(false));
-  set(pre::prefill_gemm_kernel<true, false, false>, pre::smem_bytes(false));
-  set(pre::prefill_gemm_kernel<false, true, true>, pre::smem_bytes(true));
-  set(pre::prefill_gemm_kernel<true, true, true>, pre::smem_bytes(true));
-#ifdef W4A4_F8_ON_PACKED
-  set(pre::prefill_gemm_kernel<false, true, false>, pre::smem_bytes(false));
-  set(pre::prefill_gemm_kernel<true, true, false>, pre::smem_bytes(false));
-#endif
+  set(pre::prefill_gemm_kernel<false, false, false>, pre::smem_bytes(false, false));
+  set(pre::prefill_gemm_kernel<true, false, false>, pre::smem_bytes(false, false));
+  set(pre::prefill_gemm_kernel<false, true, true>, pre::smem_bytes(true, true));
+  set(pre::prefill_gemm_kernel<true, true, true>, pre::smem_bytes(true, true));
+  set(pre::prefill_gemm_kernel<false, true, false>, pre::smem_bytes(true, false));
+  set(pre::prefill_gemm_kernel<true, true, false>, pre::smem_bytes(true, false));
   set(pp::prefill_pair_gemm_kernel<false, false, false>, pp::smem_bytes(false));
   set(pp::prefill_pair_gemm_kernel<true, false, false>, pp::smem_bytes(false));
   set(pp::prefill_pair_gemm_kernel<false, true, true>, pp::smem_bytes(true));
@@ -255,7 +253,7 @@ struct GemmArgs {
   int T, K, N, nnz, flags;
   bool do_dense;
   float sparse_weight;
-  int xe_fmt;              // bytes of the expanded codes: 0 = s8, 1 = e4m3 (goes with prepared weights)
+  int xe_fmt;              // bytes of the expanded codes: W4A4_CODES_S8 / _E4M3 (prepared weights) / _E4M3_PACKED
   void* ws;
   size_t ws_bytes;
   cudaStream_t stream;
@@ -393,6 +391,16 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   return W4A4_OK;
 }
 
+// Packed weights read as e4m3 numbers by fp8 MMAs when the library expands the activation codes itself and
+// the call carries their group sums: W4A4_PREFILL_F8=1.  Off by default: measured slower than the integer
+// MMAs on s8 codes (gate_up, 4096 tokens: 1397 against 1175 us) - both are bound by the unpack warps'
+// hand-over, and this form adds 16 KB of shared-memory stores per step.  Read on every call: tests compare
+// the two in one process.
+bool f8_on_packed() {
+  const char* e = getenv("W4A4_PREFILL_F8");
+  return e ? atoi(e) != 0 : false;
+}
+
 // True when the call carries prepared weights for every operand it uses.
 bool has_prepared(const GemmArgs& a) {
   const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
@@ -400,30 +408,33 @@ bool has_prepared(const GemmArgs& a) {
          (a.W_low_prep != nullptr || a.W_high_prep != nullptr);
 }
 
+#ifdef W4A4_TRACE
+static long long* g_trace_ptr = nullptr;
+#endif
 int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   using namespace w4a4;
   GemmArgs a = a_in;
   const bool prep = has_prepared(a);
-  // Prepared weights exist only as e4m3 and take fp8 MMAs.  Packed weights take integer MMAs on s8 codes:
-  // turning nibbles into e4m3 on the SM (12 permute / logic operations per 8 codes) is slower than widening
-  // them to s8 (3 per 8 codes) plus the int -> float conversion in the fold (measured: gate_up M=8192 3027
-  // against 2430 us).  That third instantiation is compiled only with -DW4A4_F8_ON_PACKED (A/B builds); it
-  // then runs when the caller hands in e4m3 codes without prepared weights, or with W4A4_PREFILL_F8=1.
-#ifdef W4A4_F8_ON_PACKED
-  static const bool env_f8 = getenv("W4A4_PREFILL_F8") && atoi(getenv("W4A4_PREFILL_F8")) != 0;
-#else
-  const bool env_f8 = false;
-#endif
-  const bool f8 = a.XE != nullptr ? a.xe_fmt == 1 : (prep || env_f8);
+  // The expanded codes say which instantiation runs: e4m3 in natural order goes with prepared weights (fp8
+  // MMAs on bytes as they land), e4m3 in even/odd order with packed weights read as e4m3 numbers (fp8
+  // MMAs, see nib_lo_off8), s8 with packed weights widened to s8 (integer MMAs).  When the library expands
+  // the codes itself it picks the e4m3 form that matches the weights; the integer instantiation remains for
+  // callers' s8 codes and for calls that carry no activation group sums (the e4m3 form of packed weights
+  // has an offset that only the sums can take out).
   const bool dump = a.acc_dump || a.acc_hi_dump;
   const bool has_sparse = a.nnz > 0 && a.sparse_weight != 0.f;
-  if (prep && !f8)
-    return fail(W4A4_ERR_BAD_ARG, "prepared weights need activation codes expanded as e4m3 (W4A4_FLAG_CODES_E4M3)");
-#ifndef W4A4_F8_ON_PACKED
-  if (f8 && !prep)
-    return fail(W4A4_ERR_BAD_ARG, "e4m3 activation codes need prepared weights (w4a4_prepare_weights) for every operand in use");
-#endif
-  a.xe_fmt = f8 ? 1 : 0;
+  if (a.XE == nullptr)
+    a.xe_fmt = prep ? W4A4_CODES_E4M3
+                    : ((dump ? (a.flags & W4A4_FLAG_CODES_E4M3_PACKED) != 0 : (a.sum_X != nullptr && f8_on_packed()))
+                           ? W4A4_CODES_E4M3_PACKED : W4A4_CODES_S8);
+  if (prep && a.xe_fmt != W4A4_CODES_E4M3)
+    return fail(W4A4_ERR_BAD_ARG, "prepared weights need activation codes expanded as W4A4_CODES_E4M3 (W4A4_FLAG_CODES_E4M3)");
+  if (!prep && a.xe_fmt == W4A4_CODES_E4M3)
+    return fail(W4A4_ERR_BAD_ARG, "W4A4_CODES_E4M3 activation codes need prepared weights (w4a4_prepare_weights) for every "
+                                  "operand in use; packed weights read W4A4_CODES_E4M3_PACKED or W4A4_CODES_S8");
+  const bool f8 = a.xe_fmt != W4A4_CODES_S8;
+  if (f8 && !prep && !dump && a.XE != nullptr && a.sumxf == nullptr)
+    return fail(W4A4_ERR_BAD_ARG, "W4A4_CODES_E4M3_PACKED activation codes need the group sums (sumxf)");
   if (!a.do_dense && !has_sparse) return fail(W4A4_ERR_BAD_ARG, "neither a dense nor a residual operand was given");
   const int ng = a.K / BCOL;
   const int row_tiles = (a.N + pre::ROWS - 1) / pre::ROWS;
@@ -467,7 +478,7 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   p.t_pad = xe_t_pad(a.T);
   p.scale_u4 = static_cast<const __half*>(a.scale_u4);
   p.zero_u4 = static_cast<const __half*>(a.zero_u4);
-  p.sumxf = a.do_dense ? sumxf : nullptr;
+  p.sumxf = (a.do_dense || (f8 && !prep)) ? sumxf : nullptr;
   p.scale_x = static_cast<const __half*>(a.scale_x);
   p.Y = static_cast<__half*>(a.Y);
   if (a.flags & W4A4_FLAG_OUT_TOKEN_MAJOR) {
@@ -484,6 +495,16 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
   p.sparse_on = has_sparse ? 1 : 0;
   p.sz_vec = (ng % 8 == 0 && aligned(a.scale_u4, 16) && aligned(a.zero_u4, 16)) ? 1 : 0;
   p.sparse_weight = has_sparse ? a.sparse_weight : 0.f;
+#ifdef W4A4_TRACE
+  {
+    static long long* g_trace = nullptr;
+    if (!g_trace) { cudaMalloc(&g_trace, 16 * 64 * 8); }
+    cudaMemsetAsync(g_trace, 0, 16 * 64 * 8, a.stream);
+    p.trace = g_trace;
+    p.trace_cta = getenv("W4A4_TRACE_CTA") ? atoi(getenv("W4A4_TRACE_CTA")) : 1000;
+    g_trace_ptr = g_trace;
+  }
+#endif
   // W4A4_PREFILL_BAND overrides the band height of the CTA order (A/B runs)
   static const int env_band = getenv("W4A4_PREFILL_BAND") ? atoi(getenv("W4A4_PREFILL_BAND")) : 0;
   p.band = env_band > 0 ? env_band : 16;
@@ -503,12 +524,10 @@ int launch_prefill(const GemmArgs& a_in, DeviceInfo* dev) {
              : (dump ? pp::prefill_pair_gemm_kernel<true, false, false> : pp::prefill_pair_gemm_kernel<false, false, false>);
     e = launch_ex(kern, dim3(2 * ((row_tiles + 1) / 2), tok_tiles, 1), dim3(pp::THREADS), smem, a.stream, 2, tm_w, tm_wh, p);
   } else {
-    const size_t smem = pre::smem_bytes(prep);
+    const size_t smem = pre::smem_bytes(f8, prep);
     void (*kern)(const CUtensorMap, const CUtensorMap, const pre::Params) =
         prep ? (dump ? pre::prefill_gemm_kernel<true, true, true> : pre::prefill_gemm_kernel<false, true, true>)
-#ifdef W4A4_F8_ON_PACKED
         : f8 ? (dump ? pre::prefill_gemm_kernel<true, true, false> : pre::prefill_gemm_kernel<false, true, false>)
-#endif
              : (dump ? pre::prefill_gemm_kernel<true, false, false> : pre::prefill_gemm_kernel<false, false, false>);
     e = launch_ex(kern, dim3(row_tiles, tok_tiles, 1), dim3(pre::THREADS), smem, a.stream, 1, tm_w, tm_wh, p);
   }
@@ -611,7 +630,7 @@ int run_gemm(GemmArgs& a) {
   if (!aligned(a.W_low_prep, 16) || !aligned(a.W_high_prep, 16))
     return fail(W4A4_ERR_ALIGNMENT, "weight pointers must be 16-byte aligned");
   // e4m3 codes exist only for the tensor-core kernel: such a call goes there whatever the token count
-  if (a.XE != nullptr && a.xe_fmt != 0) {
+  if ((a.XE != nullptr && a.xe_fmt != 0) || ((a.acc_dump || a.acc_hi_dump) && (a.flags & W4A4_FLAG_CODES_E4M3_PACKED))) {
     if (a.flags & W4A4_FLAG_FORCE_STREAM) return fail(W4A4_ERR_BAD_ARG, "the streaming path reads s8 expanded codes");
     return launch_prefill(a, dev);
   }
@@ -665,7 +684,17 @@ __global__ void selftest_wait_kernel(uint32_t polls) {
   }
 }
 
+#ifdef W4A4_TRACE
+long long* trace_ptr() { return g_trace_ptr; }
+#endif
 }  // namespace
+
+#ifdef W4A4_TRACE
+extern "C" int w4a4_debug_trace(long long* dst) {
+  if (!trace_ptr()) return 1;
+  return (int)cudaMemcpy(dst, trace_ptr(), 16 * 64 * 8, cudaMemcpyDeviceToHost);
+}
+#endif
 
 // ===================================================================== C ABI
 extern "C" {
@@ -730,7 +759,8 @@ int fused_prologue_quant(int src, const void* X, long long ldx, long long min_ld
                          int code_format, int T, int K, void* stream) {
   int rc = check_common(T, K, 1, 0);
   if (rc) return rc;
-  CHECK_ARG(code_format == W4A4_CODES_S8 || code_format == W4A4_CODES_E4M3, "unknown code format %d", code_format);
+  CHECK_ARG(code_format == W4A4_CODES_S8 || code_format == W4A4_CODES_E4M3 || code_format == W4A4_CODES_E4M3_PACKED,
+            "unknown code format %d", code_format);
   CHECK_ARG(X && scale_x, "NULL tensor pointer");
   CHECK_ARG((X_s4 != nullptr) == (sum_X != nullptr), "X_s4 and sum_X go together");
   CHECK_ARG((XE != nullptr) == (sumxf != nullptr), "XE and sumxf go together");
@@ -939,7 +969,8 @@ int w4a4_expand_activations(const void* X_s4, const int32_t* sum_X, void* XE, fl
 int w4a4_expand_activations_fmt(const void* X_s4, const int32_t* sum_X, void* XE, float* sumxf, int T, int K,
                                 int code_format, void* stream) {
   begin_call();
-  CHECK_ARG(code_format == W4A4_CODES_S8 || code_format == W4A4_CODES_E4M3, "unknown code format %d", code_format);
+  CHECK_ARG(code_format == W4A4_CODES_S8 || code_format == W4A4_CODES_E4M3 || code_format == W4A4_CODES_E4M3_PACKED,
+            "unknown code format %d", code_format);
   int rc = check_common(T, K, 1, 0);
   if (rc) return rc;
   CHECK_ARG(X_s4 && XE && (sum_X == nullptr || sumxf != nullptr), "NULL tensor pointer");
@@ -975,14 +1006,17 @@ int w4a4_fused_dense_sparse_expanded_prepared(const void* W_low, const void* W_h
   GemmArgs a{};
   a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
   a.do_dense = true; a.nnz = nnz; a.sparse_weight = 16.f;
-  // The caller says which bytes XE holds.  e4m3 codes are read only by the tensor-core kernel on prepared
-  // weights; s8 codes go with the packed arrays, so prepared pointers given with s8 codes are an error
-  // rather than a silent reinterpretation of the bytes.
+  // The caller says which bytes XE holds.  Natural-order e4m3 codes are read only against prepared weights,
+  // even/odd-order e4m3 codes and s8 codes only against the packed arrays; a mismatch is an error rather than
+  // a silent reinterpretation of the bytes.
+  CHECK_ARG((flags & W4A4_FLAG_CODES_E4M3) == 0 || (flags & W4A4_FLAG_CODES_E4M3_PACKED) == 0,
+            "W4A4_FLAG_CODES_E4M3 and W4A4_FLAG_CODES_E4M3_PACKED exclude each other");
+  a.xe_fmt = (flags & W4A4_FLAG_CODES_E4M3) ? W4A4_CODES_E4M3
+             : (flags & W4A4_FLAG_CODES_E4M3_PACKED) ? W4A4_CODES_E4M3_PACKED : W4A4_CODES_S8;
   if (!has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
-  a.xe_fmt = (flags & W4A4_FLAG_CODES_E4M3) ? W4A4_CODES_E4M3 : W4A4_CODES_S8;
   if (has_prepared(a) && a.xe_fmt != W4A4_CODES_E4M3)
-    return fail(W4A4_ERR_BAD_ARG, "prepared weights were passed with s8 activation codes: expand with W4A4_CODES_E4M3 and set "
-                                  "W4A4_FLAG_CODES_E4M3, or pass NULL prepared pointers");
+    return fail(W4A4_ERR_BAD_ARG, "prepared weights were passed with activation codes for packed weights: expand with "
+                                  "W4A4_CODES_E4M3 and set W4A4_FLAG_CODES_E4M3, or pass NULL prepared pointers");
   a.W_low = W_low; a.W_high = W_high; a.hp_row_offsets = hp_row_offsets; a.hp_col_indices = hp_col_indices;
   a.XE = XE; a.sumxf = sumxf; a.scale_u4 = scale_u4; a.zero_u4 = zero_u4; a.scale_x = scale_x; a.Y = Y;
   a.T = T; a.K = K; a.N = N; a.nnz = nnz; a.flags = flags;
@@ -1063,13 +1097,10 @@ int w4a4_fused_quant_dense_sparse_prepared(const void* X, long long ldx, const i
   a.W_low_prep = W_low_prepared; a.W_high_prep = W_high_prepared;
   const bool tensor = wants_tensor_path(T, K, N, flags, dev->sm_count, has_prepared(a));
   if (!tensor || !has_prepared(a)) a.W_low_prep = a.W_high_prep = nullptr;
-  // the tensor-core kernel reads e4m3 codes when it runs fp8 MMAs (prepared weights), s8 codes otherwise
-#ifdef W4A4_F8_ON_PACKED
-  static const bool env_f8 = getenv("W4A4_PREFILL_F8") && atoi(getenv("W4A4_PREFILL_F8")) != 0;
-#else
-  const bool env_f8 = false;
-#endif
-  a.xe_fmt = (tensor && (has_prepared(a) || env_f8)) ? 1 : 0;
+  // the tensor-core kernel runs fp8 MMAs on e4m3 codes (natural order against prepared weights, even/odd
+  // order against packed ones); the streaming kernel reads s8 codes
+  a.xe_fmt = !tensor ? W4A4_CODES_S8
+             : has_prepared(a) ? W4A4_CODES_E4M3 : (f8_on_packed() ? W4A4_CODES_E4M3_PACKED : W4A4_CODES_S8);
   rc = launch_quant(X, ldx, perm, nullptr, ws + wl.scale_x, nullptr, ws + wl.xe, reinterpret_cast<float*>(ws + wl.sumxf),
                     T, K, s, dev->sm_count, a.xe_fmt);
   if (rc) return rc;
@@ -1120,8 +1151,8 @@ int w4a4_fused_dense_sparse_noalloc(const void* W_low, const void* W_high, const
                 T, K, NOALLOC_MAX_T, NOALLOC_MAX_K);
   if (!aligned(X_s4, 4)) return fail(W4A4_ERR_ALIGNMENT, "X_s4 must be 4-byte aligned");
   // this entry point always runs the weight-streaming kernel on s8 codes it expands itself
-  CHECK_ARG((flags & (W4A4_FLAG_FORCE_TENSOR | W4A4_FLAG_CODES_E4M3)) == 0,
-            "w4a4_fused_dense_sparse_noalloc accepts neither W4A4_FLAG_FORCE_TENSOR nor W4A4_FLAG_CODES_E4M3");
+  CHECK_ARG((flags & (W4A4_FLAG_FORCE_TENSOR | W4A4_FLAG_CODES_E4M3 | W4A4_FLAG_CODES_E4M3_PACKED)) == 0,
+            "w4a4_fused_dense_sparse_noalloc accepts neither W4A4_FLAG_FORCE_TENSOR nor W4A4_FLAG_CODES_E4M3[_PACKED]");
   void* scratch = nullptr;
   rc = noalloc_scratch_address(&scratch);      // first call on a device resolves the address
   if (rc) return rc;

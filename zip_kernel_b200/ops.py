@@ -95,7 +95,21 @@ def perm_or_none(perm: torch.Tensor, cache_on=None):
     return val
 
 
-def _fused_prologue(which: str, X2: torch.Tensor, K: int, perm, norm_weight, eps: float, expanded: bool, e4m3: bool):
+def _code_format(e4m3) -> int:
+    """``False``: s8 codes; ``True``: e4m3 bytes for prepared weights; ``"packed"``: e4m3 bytes in the
+    order packed weights are read in (see include/w4a4_b200.h, W4A4_CODES_*)."""
+    if isinstance(e4m3, str):
+        if e4m3 != "packed":
+            raise ValueError(f"e4m3 must be False, True or 'packed', got {e4m3!r}")
+        return _lib.CODES_E4M3_PACKED
+    return _lib.CODES_E4M3 if e4m3 else _lib.CODES_S8
+
+
+def _code_flag(e4m3) -> int:
+    return (0, _lib.FLAG_CODES_E4M3, _lib.FLAG_CODES_E4M3_PACKED)[_code_format(e4m3)]
+
+
+def _fused_prologue(which: str, X2: torch.Tensor, K: int, perm, norm_weight, eps: float, expanded: bool, e4m3):
     T = int(X2.shape[0])
     dev = X2.device
     scale_x = torch.empty((T,), dtype=torch.float16, device=dev)
@@ -116,10 +130,10 @@ def _fused_prologue(which: str, X2: torch.Tensor, K: int, perm, norm_weight, eps
         if which == "rmsnorm":
             w = norm_weight.to(device=dev, dtype=torch.float16).contiguous()
             _lib.check(_L.w4a4_rmsnorm_quant(X2.data_ptr(), X2.stride(0) if T > 1 else K, w.data_ptr(), float(eps), pp, *outs,
-                                             1 if e4m3 else 0, T, K, _lib.stream_ptr(dev)), "rmsnorm_quant")
+                                             _code_format(e4m3), T, K, _lib.stream_ptr(dev)), "rmsnorm_quant")
         else:
             _lib.check(_L.w4a4_silu_mul_quant(X2.data_ptr(), X2.stride(0) if T > 1 else 2 * K, pp, *outs,
-                                              1 if e4m3 else 0, T, K, _lib.stream_ptr(dev)), "silu_mul_quant")
+                                              _code_format(e4m3), T, K, _lib.stream_ptr(dev)), "silu_mul_quant")
     return ret
 
 
@@ -130,7 +144,7 @@ def _rows(X: torch.Tensor, width: int) -> torch.Tensor:
     return X2
 
 
-def rmsnorm_quant_cuda(X_fp16, norm_weight, eps, perm, *, expanded: bool = False, e4m3: bool = False):
+def rmsnorm_quant_cuda(X_fp16, norm_weight, eps, perm, *, expanded: bool = False, e4m3=False):
     """RMSNorm and activation quantisation in one launch: quantises
     ``fp16(fp16(x * rsqrt(mean(x^2) + eps)) * norm_weight)``.  Returns ``(X_s4, scale_x, sum_X)`` like
     :func:`activation_quant_cuda`, or with ``expanded=True`` ``(XE, sumxf, scale_x)`` in the layout
@@ -144,7 +158,7 @@ def rmsnorm_quant_cuda(X_fp16, norm_weight, eps, perm, *, expanded: bool = False
     return _fused_prologue("rmsnorm", _rows(X_fp16, K), K, perm, norm_weight, eps, expanded, e4m3)
 
 
-def silu_mul_quant_cuda(gate_up_fp16, perm, *, expanded: bool = False, e4m3: bool = False):
+def silu_mul_quant_cuda(gate_up_fp16, perm, *, expanded: bool = False, e4m3=False):
     """``silu(gate) * up`` and activation quantisation in one launch.  ``gate_up_fp16 (..., 2K)`` holds the
     gate in its first K columns and the up projection in the last K (the output of a fused gate/up
     linear); the quantised tensor is ``fp16(fp16(silu(gate)) * up)`` of width K.  Returns as
@@ -364,13 +378,14 @@ def fused_dense_sparse_cuda_int4(
     return Y
 
 
-def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor, *, e4m3: bool = False):
+def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor, *, e4m3=False):
     """Quantised activations in the layout the GEMM kernels read: returns
     ``(XE, sumxf)`` - an opaque int8 buffer of expanded codes (group-major, see
     include/w4a4_b200.h) and ``(ceil(T/16), K/128, 16)`` fp32 group sums.  Build once
     and reuse across the linears that share an input (no counterpart in the
     reference).  ``e4m3=True`` writes the codes as e4m3 bytes, the form that goes
-    with weights from :func:`prepare_weights_cuda`."""
+    with weights from :func:`prepare_weights_cuda`; ``e4m3="packed"`` writes the e4m3 form the
+    tensor-core kernel reads against the packed weights."""
     assert X_s4.is_cuda and X_s4.dtype == torch.int8 and sum_X.dtype == torch.int32
     T, K = int(X_s4.shape[0]), int(X_s4.shape[1]) * 2
     X = X_s4.contiguous()
@@ -379,7 +394,7 @@ def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor, *, e4m3: bo
     sumxf = torch.zeros(((T + 15) // 16, K // BCOL, 16), dtype=torch.float32, device=X.device)
     with torch.cuda.device(X.device):
         _lib.check(_L.w4a4_expand_activations_fmt(X.data_ptr(), sm.data_ptr(), XE.data_ptr(), sumxf.data_ptr(),
-                                                  T, K, 1 if e4m3 else 0, _lib.stream_ptr(X.device)),
+                                                  T, K, _code_format(e4m3), _lib.stream_ptr(X.device)),
                    "expand_activations")
     return XE, sumxf
 
@@ -387,12 +402,12 @@ def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor, *, e4m3: bo
 def fused_dense_sparse_expanded_cuda(
     W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices,
     XE, sumxf, scale_u4, zero_u4, scale_x, d_out, d_in,
-    *, token_major: bool = False, force: Optional[str] = None, prepared=None, e4m3: bool = False,
+    *, token_major: bool = False, force: Optional[str] = None, prepared=None, e4m3=False,
 ) -> torch.Tensor:
     """:func:`fused_dense_sparse_cuda_int4` on activations already expanded by
-    :func:`expand_activations_cuda`; a single kernel launch.  ``e4m3=True`` says that ``XE``
-    was expanded with ``e4m3=True``; such codes go with ``prepared`` weights and always run the
-    tensor-core kernel.  ``prepared`` weights with s8 codes (``e4m3=False``) raise ``ValueError``:
+    :func:`expand_activations_cuda`; a single kernel launch.  ``e4m3`` repeats what ``XE`` was
+    expanded with: ``True`` goes with ``prepared`` weights, ``"packed"`` with the packed arrays
+    (no ``prepared``); both always run the tensor-core kernel.  A mismatch raises ``ValueError``:
     the bytes of ``XE`` are never reinterpreted silently."""
     d_out, d_in = int(d_out), int(d_in)
     T = int(scale_x.shape[0])
@@ -415,7 +430,7 @@ def fused_dense_sparse_expanded_cuda(
         _lib.check(_L.w4a4_fused_dense_sparse_expanded_prepared(
             W.data_ptr(), Wh.data_ptr() if nnz else None, plo, phi, ro.data_ptr(), ci.data_ptr() if nnz else None,
             XE.data_ptr(), sumxf.data_ptr(), s.data_ptr(), z.data_ptr(), sx.data_ptr(), Y.data_ptr(),
-            T, d_in, d_out, nnz, _flags(token_major, force) | (_lib.FLAG_CODES_E4M3 if e4m3 else 0),
+            T, d_in, d_out, nnz, _flags(token_major, force) | _code_flag(e4m3),
             ws.data_ptr(), ws.numel(), _lib.stream_ptr(W.device)), "fused_dense_sparse_expanded")
     return Y
 
@@ -506,9 +521,10 @@ def fused_quant_dense_sparse_cuda_int4(
 
 
 def dump_accumulators(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indices, X_s4,
-                      d_out, d_in, *, force: Optional[str] = None, prepared=None):
+                      d_out, d_in, *, force: Optional[str] = None, prepared=None, e4m3_packed: bool = False):
     """Parity aid: the exact int32 accumulators of the MMA path, ``acc (ng, d_out,
-    T)`` per group and ``acc_hi (nnz, 128, T)`` per residual block."""
+    T)`` per group and ``acc_hi (nnz, 128, T)`` per residual block.  ``e4m3_packed=True`` runs the
+    tensor-core kernel's fp8 instantiation on the packed weights (offset taken out, integers again)."""
     d_out, d_in = int(d_out), int(d_in)
     T = int(X_s4.shape[0])
     dev = X_s4.device
@@ -529,7 +545,8 @@ def dump_accumulators(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col
             ro.data_ptr() if nnz else None,
             ci.data_ptr() if nnz else None,
             X.data_ptr(), acc.data_ptr(), acc_hi.data_ptr() if nnz else None, T, d_in, d_out, nnz,
-            _flags(False, force), ws.data_ptr(), ws.numel(), _lib.stream_ptr(dev)), "dump_accumulators")
+            _flags(False, force) | (_lib.FLAG_CODES_E4M3_PACKED if e4m3_packed else 0), ws.data_ptr(), ws.numel(),
+            _lib.stream_ptr(dev)), "dump_accumulators")
     return acc, acc_hi
 
 

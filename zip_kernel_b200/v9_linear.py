@@ -71,17 +71,20 @@ def _forward(X_fp16: torch.Tensor, W: V9WeightContainer, force=None) -> torch.Te
     return Y.reshape(X_fp16.shape[:-1] + (d_out,))
 
 
-def _gemm_on_expanded(quantised, W: V9WeightContainer, lead_shape, e4m3: bool) -> torch.Tensor:
+def _gemm_on_expanded(quantised, W: V9WeightContainer, lead_shape, e4m3) -> torch.Tensor:
     XE, sumxf, scale_x = quantised
     Y = ops.fused_dense_sparse_expanded_cuda(
         W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets, W.hp_col_indices, XE, sumxf, W.scale_u4,
-        W.zero_u4, scale_x, W.d_out, W.d_in, token_major=True, prepared=W.prepared if e4m3 else None, e4m3=e4m3)
+        W.zero_u4, scale_x, W.d_out, W.d_in, token_major=True, prepared=W.prepared if e4m3 is True else None, e4m3=e4m3)
     return Y.reshape(tuple(lead_shape) + (W.d_out,))
 
 
-def _wants_e4m3(W: V9WeightContainer, T: int) -> bool:
-    # prepared weights serve the many-token kernel; below its threshold the packed arrays are streamed
-    return W.prepared is not None and T >= 256
+def _wants_e4m3(W: V9WeightContainer, T: int):
+    # the many-token kernel runs fp8 MMAs: on the prepared copy when the container has one, else on the packed
+    # arrays; below its threshold the packed arrays are streamed against s8 codes
+    if T < 256:
+        return False
+    return True if W.prepared is not None else "packed"
 
 
 def v9_linear_forward_rmsnorm(X_fp16: torch.Tensor, norm_weight: torch.Tensor, eps: float,

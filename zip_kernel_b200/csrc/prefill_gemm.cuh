@@ -56,7 +56,14 @@ namespace pre {
 
 constexpr int ROWS = 128;                 // MMA M
 constexpr int TN = 128;                   // tokens per CTA = MMA N
-constexpr int A_BUFS = 2;                 // widened weight tiles in tensor memory
+constexpr int A_BUFS = 2;                 // widened weight tiles in flight (the paired kernel, and the e4m3 tiles in shared memory)
+#ifndef W4A4_A_BUFS_TMEM
+#define W4A4_A_BUFS_TMEM 4
+#endif
+// Widened s8 tiles in tensor memory (integer instantiation).  A tile is free again only once the MMAs that read
+// it have COMPLETED - hundreds of clocks after they were issued while the fold warps keep the SM busy - so
+// with two tiles the unpack warps and the tensor pipe took turns: four tiles let the unpack warps run ahead.
+constexpr int A_BUFS_TMEM = W4A4_A_BUFS_TMEM;
 constexpr int X_BYTES = TN * BCOL;                // 16384
 constexpr int MAX_STAGES = 6;
 constexpr int SZ_CHUNK = 16;                      // groups of scale/zero/sums staged at a time
@@ -69,7 +76,7 @@ template <bool A_TMEM>
 struct TmemLayout {
   static constexpr int ACC_BUFS = A_TMEM ? 2 : 3;
   static constexpr int A_COL0 = ACC_BUFS * TN;
-  static constexpr int Z_COL0 = A_COL0 + (A_TMEM ? A_BUFS * A_COLS : 0);
+  static constexpr int Z_COL0 = A_COL0 + (A_TMEM ? A_BUFS_TMEM * A_COLS : 0);
   static_assert(Z_COL0 + TN <= TMEM_COLS, "tensor memory capacity");
 };
 constexpr int ZT_BYTES = ROWS * 128;              // one tf32 operand tile of the zero-point term: 128 rows x 32 values
@@ -82,7 +89,7 @@ constexpr int N_FOLD_WARPS = W4A4_FOLD_WARPS;     // a multiple of 4: a warp rea
 constexpr int WARP_TMAX = WARP_FOLD0 + N_FOLD_WARPS;   // the activation copies have an issuing thread of their own
 constexpr int WARP_MMA2 = WARP_TMAX + 1;               // ... and the odd steps' MMAs too
 constexpr int THREADS = (WARP_MMA2 + 1) * 32;
-static_assert(A_BUFS == 2, "step parity = widened-weight buffer = issuing thread");
+static_assert(A_BUFS % 2 == 0 && A_BUFS_TMEM % 2 == 0, "an issuing thread takes every other step");
 constexpr int FOLD_THREADS = N_FOLD_WARPS * 32;
 constexpr int COLS_PER_FOLD = TN / (N_FOLD_WARPS / 4);   // a fold thread owns one row and this many tokens
 static_assert(N_FOLD_WARPS % 4 == 0 && COLS_PER_FOLD % 32 == 0, "fold warps tile the accumulator in 32-lane x 32-column pieces");
@@ -275,6 +282,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
   constexpr int W_STAGES = SmemLayout::W_STAGES, X_STAGES = SmemLayout::X_STAGES, WP_BYTES = SmemLayout::WP_BYTES;
   constexpr int ACC_BUFS = TmemLayout<!F8>::ACC_BUFS, A_COL0 = TmemLayout<!F8>::A_COL0, Z_COL0 = TmemLayout<!F8>::Z_COL0;
   constexpr int AT_BYTES = SmemLayout::AT_BYTES;
+  constexpr int N_A = F8 ? A_BUFS : A_BUFS_TMEM;           // widened weight tiles in flight
+  static_assert(N_A < X_STAGES, "the completion barrier of the step a tile was last read in must not have been reused");
   static_assert(ACC_BUFS < X_STAGES, "the fold warps' arrival for step n + ACC_BUFS must fall into that step's barrier phase");
   extern __shared__ unsigned char smem_raw[];
   unsigned char* sm = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -421,7 +430,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         return true;
       };
       int buf = par % ACC_BUFS;
-      const int ab = par;
+      int ab = par;                   // widened weight tile of the step: step % N_A
       const uint64_t bdesc0 = smem_desc_sw128(x_ring), adesc0 = smem_desc_sw128(wp_ring), atdesc0 = smem_desc_sw128(a_tiles);
       const uint32_t d0 = tmem_base, a0 = tmem_base + A_COL0;
       const bool with_z = p.Y != nullptr && n_windows > 0;
@@ -463,6 +472,8 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (xs >= X_STAGES) { xs -= X_STAGES; xph ^= 1; }
         buf += 2;
         if (buf >= ACC_BUFS) buf -= ACC_BUFS;
+        ab += 2;
+        if (ab >= N_A) ab -= N_A;
       }
       while (par == 0 && ok && p.Y != nullptr && z_next < n_windows) ok = issue_zero_term(z_next++);
     }
@@ -476,12 +487,12 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
     int ws = 0;
     uint32_t wph = 0;
     for (int n = 0; n < (PREP ? 0 : n_steps); ++n) {     // prepared weights need no widening
-      const int buf = n % A_BUFS;
+      const int buf = n % N_A;
       if (ok) ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&w_full[ws], wph, SITE_PRE_WFULL));
       if (warp == WARP_UNPACK0 && lane == 0) TRACE(6, n);
       // the A buffer was last read by the MMAs of step n - 2
-      if (ok && n >= A_BUFS)
-        ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&done[(n - A_BUFS) % X_STAGES], ((n - A_BUFS) / X_STAGES) & 1, SITE_PRE_AEMPTY));
+      if (ok && n >= N_A)
+        ok = __all_sync(0xffffffffu, mbar_wait_relaxed(&done[(n - N_A) % X_STAGES], ((n - N_A) / X_STAGES) & 1, SITE_PRE_AEMPTY));
       if (ok) {
         tc_fence_after();
         // the row's 64 packed bytes: four 16-byte chunks, stored at chunk ^ ((row >> 1) & 3) by the 64-byte swizzle

@@ -180,6 +180,14 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void grid_dependency_wait() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
 }
+// The same for a thread that goes on to read the preceding kernel's output with asynchronous copies
+// (cp.async.bulk / TMA read through the async proxy; the preceding kernel wrote through the generic proxy).
+// A kernel boundary orders the two proxies; a programmatic dependency is not documented to, so the
+// cross-proxy fence is stated explicitly.  Once per issuing thread and launch.
+__device__ __forceinline__ void grid_dependency_wait_for_async_reads() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("fence.proxy.async.global;" ::: "memory");
+}
 __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }

@@ -258,7 +258,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
         b_lo = o0 + (int)((long long)rank * (o1 - o0) / S);
         b_hi = o0 + (int)((long long)(rank + 1) * (o1 - o0) / S);
       }
-      grid_dependency_wait();
+      grid_dependency_wait_for_async_reads();
       int st = 0, n = 0;
       uint32_t ph = 1;                     // parity the empty barrier is waited on
       for (int j = d_lo; j < d_hi && ok; ++j, ++n) {

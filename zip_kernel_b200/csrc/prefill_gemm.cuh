@@ -382,7 +382,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       bool ok = true;
       int xs = 0;
       uint32_t xph = 1;
-      grid_dependency_wait();                 // the expanded codes are written by the preceding kernel
+      grid_dependency_wait_for_async_reads();                 // the expanded codes are written by the preceding kernel
       const int8_t* src0 = p.XE + (size_t)tok0 * BCOL;
       const size_t gstride = (size_t)p.t_pad * BCOL;
       for (int n = 0; n < n_steps && ok; ++n) {

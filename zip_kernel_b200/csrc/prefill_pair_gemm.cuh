@@ -254,7 +254,7 @@ prefill_pair_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_
         }
       };
       for (int n = 0; n < n_pre; ++n) issue_w(n, n);       // weights do not depend on the preceding kernel
-      grid_dependency_wait();
+      grid_dependency_wait_for_async_reads();
       int st = 0;
       uint32_t wph = 1;
       for (int n = 0; n < n_steps && ok; ++n) {

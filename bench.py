@@ -61,8 +61,8 @@ WINDOWS = 3
 NCU_TRAFFIC = {
     ("decode", "packed"): (30.49e6, "decode_gemm_kernel<1|2,false>, mean of the 12 launches", "2026-11-25"),
     ("gate_up_m16", "packed"): (65.82e6, "decode_gemm_kernel<2,false>", "2026-11-25"),
-    ("prefill_gate_up", "prepared"): (225.9e6, "prefill_gemm_kernel<false,true,true>", "2026-11-25"),
-    ("prefill_gate_up", "packed"): (153.2e6, "prefill_gemm_kernel<false,false,false>", "2026-11-25"),
+    ("prefill_gate_up", "prepared"): (226.5e6, "prefill_gemm_kernel<false,true,true>", "2026-11-25"),
+    ("prefill_gate_up", "packed"): (155.0e6, "prefill_gemm_kernel<false,false,false>", "2026-11-25"),
 }
 
 

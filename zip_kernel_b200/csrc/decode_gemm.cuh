@@ -411,9 +411,12 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           const uint32_t wrow_a = slot + r_a * (2 * GROUP_BYTES) + tig * 16;
           const uint32_t wrow_b = slot + r_b * (2 * GROUP_BYTES) + tig * 16;
           const uint32_t sums = sumx_a + st * 2 * SUMX_BYTES;
+          // the wide instantiation (four MMA tiles per pass) reads a group's weight fragments when it gets to
+          // the group: both groups' fragments at once do not fit its register budget
+          constexpr bool LATE_W = NT > 2;
           uint4 wa[2], wb[2];
 #pragma unroll
-          for (int h = 0; h < 2; ++h) {
+          for (int h = 0; h < (LATE_W ? 1 : 2); ++h) {
             wa[h] = lds_v4(wrow_a + h * GROUP_BYTES);
             wb[h] = lds_v4(wrow_b + h * GROUP_BYTES);
           }
@@ -424,7 +427,11 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           // group gg of the step, MMA tiles of tokens in bunches of NTH: A fragments are widened once per group
 #pragma unroll
           for (int gg = 0; gg < 2; ++gg) {
-            const AFrag fa = unpack_a(wa[gg], wb[gg]);
+            if (LATE_W && gg == 1) {
+              wa[0] = lds_v4(wrow_a + GROUP_BYTES);
+              wb[0] = lds_v4(wrow_b + GROUP_BYTES);
+            }
+            const AFrag fa = LATE_W ? unpack_a(wa[0], wb[0]) : unpack_a(wa[gg], wb[gg]);
             const float2 sza = gg ? sza1 : sza0, szb = gg ? szb1 : szb0;
 #pragma unroll
             for (int hh = 0; hh < HALVES; ++hh) {

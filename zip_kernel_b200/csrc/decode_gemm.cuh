@@ -303,6 +303,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
 
     const uint32_t stage_a = smem_u32(stage_buf), sumx_a = smem_u32(sumx_ring), szs_a = smem_u32(szs);
 
+    const uint32_t runtime_zero = (uint32_t)p.ng >> 31;      // 0, unknown to the compiler (see the slot hand-back)
     float2 y[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) y[nt][0] = y[nt][1] = make_float2(0.f, 0.f);
@@ -448,8 +449,19 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
                                                       : make_float2(0.f, 0.f);
               }
               if (gg == 1 && hh == HALVES - 1) {
+                // Hand the slot back - but only once the loads from it have RETURNED.  Issuing them first is
+                // not enough: the arrival overtook shared-memory loads still in flight, the producer's next
+                // copy then landed under them, and about one launch in ten of a long, two-CTAs-per-SM shape
+                // folded one group with the group sums of four steps on (seen as 16-row x 16-token patches
+                // off by a fraction of a step; found by matching the error against candidate operands).  The
+                // arrival's address therefore depends on the last registers loaded from the slot (`dep & 0`
+                // with a zero the compiler cannot see): it issues when they are ready, and a warp's earlier
+                // shared-memory loads have returned by then.  (The slot's next writer is the copy engine - another
+                // proxy - so a release by this thread orders nothing for it; fence.proxy.async before the
+                // arrival also cures it and costs 4 % of the decode sweep, this costs 1.5 %.)
+                const uint32_t dep = q1[NTH - 1].w ^ __float_as_uint(sx[NTH - 1].y);     // the loads issued last
                 __syncwarp();
-                if (lane == 0) mbar_arrive(&empty[st]);      // every shared-memory read of this slot is done
+                if (lane == 0) mbar_arrive_after(&empty[st], dep, runtime_zero);
               }
               int acc[NTH][4];
               group_mma<NTH>(acc, fa, q0, q1);
@@ -499,8 +511,9 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
               sx[nt] = make_float2(0.f, 0.f);
             }
             if (hh == HALVES - 1) {
+              const uint32_t dep = q1[NTH - 1].w;                                       // as in the dense branch
               __syncwarp();
-              if (lane == 0) mbar_arrive(&empty[st]);
+              if (lane == 0) mbar_arrive_after(&empty[st], dep, runtime_zero);
             }
             int acc[NTH][4];
             group_mma<NTH>(acc, fa, q0, q1);

@@ -551,9 +551,21 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
       sxs[i] = (tok0 + i < p.T && p.scale_x) ? __half2float(ld_plain(p.scale_x + tok0 + i)) : 0.f;
     asm volatile("bar.sync 1, %0;" ::"n"(FOLD_THREADS) : "memory");
 
-    f32x2_t y2[COLS_PER_FOLD / 2];      // the thread's row x COLS_PER_FOLD tokens, two tokens per register pair
+    // The thread's row x COLS_PER_FOLD tokens.  On prepared weights the accumulators arrive as floats in single
+    // registers and the fold is one scalar FMA per element: pairing them up for fma.rn.f32x2 costs two register
+    // moves per pair, as many issue slots as the FMAs (measured: -15 % kernel time without them).  The
+    // integer instantiation converts two accumulators at a time into a register pair anyway and keeps the
+    // packed FMAs (scalar ones: +6 %).
+    constexpr bool SCALAR_FOLD = PREP;
+    float yf[SCALAR_FOLD ? COLS_PER_FOLD : 1];
+    f32x2_t y2[SCALAR_FOLD ? 1 : COLS_PER_FOLD / 2];      // two tokens per register pair
+    if (SCALAR_FOLD) {
 #pragma unroll
-    for (int i = 0; i < COLS_PER_FOLD / 2; ++i) y2[i] = 0ull;
+      for (int i = 0; i < COLS_PER_FOLD; ++i) yf[i] = 0.f;
+    } else {
+#pragma unroll
+      for (int i = 0; i < COLS_PER_FOLD / 2; ++i) y2[i] = 0ull;
+    }
 
     // Scale/zero/sums windows of 16 groups.  The next window travels as cp.async
     // copies while the current one is folded, so it occupies no registers: thread ft
@@ -714,10 +726,15 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
         if (!(OFF8 && DUMP && is_dense)) {       // (a dump launch writes no output: its dense steps keep the corrected values for the dump only)
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            f32x2_t v;
-            if (F8) asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(a[i]), "r"(a[i + 1]));     // fp32 accumulators: the integers as floats
-            else v = cvt_s32x2_f32x2(a[i], a[i + 1]);
-            y2[(cc + i) >> 1] = fma_f32x2(v, f2, y2[(cc + i) >> 1]);
+            if (SCALAR_FOLD) {
+              yf[cc + i] = __fmaf_rn(__uint_as_float(a[i]), f, yf[cc + i]);                  // fp32 accumulators: the integers as floats
+              yf[cc + i + 1] = __fmaf_rn(__uint_as_float(a[i + 1]), f, yf[cc + i + 1]);
+            } else {
+              f32x2_t v;
+              if (F8) asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "r"(a[i]), "r"(a[i + 1]));
+              else v = cvt_s32x2_f32x2(a[i], a[i + 1]);
+              y2[(cc + i) >> 1] = fma_f32x2(v, f2, y2[(cc + i) >> 1]);
+            }
           }
         }
         if (DUMP) {
@@ -760,9 +777,14 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           tmem_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + Z_COL0 + c0 + cc, z);
 #pragma unroll
           for (int i = 0; i < 32; i += 2) {
-            f32x2_t zz;
-            asm("mov.b64 %0, {%1, %2};" : "=l"(zz) : "r"(z[i]), "r"(z[i + 1]));
-            y2[(cc + i) >> 1] = fma_f32x2(zz, minus1, y2[(cc + i) >> 1]);
+            if (SCALAR_FOLD) {
+              yf[cc + i] = __fsub_rn(yf[cc + i], __uint_as_float(z[i]));
+              yf[cc + i + 1] = __fsub_rn(yf[cc + i + 1], __uint_as_float(z[i + 1]));
+            } else {
+              f32x2_t zz;
+              asm("mov.b64 %0, {%1, %2};" : "=l"(zz) : "r"(z[i]), "r"(z[i + 1]));
+              y2[(cc + i) >> 1] = fma_f32x2(zz, minus1, y2[(cc + i) >> 1]);
+            }
           }
         }
       }
@@ -779,7 +801,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           __align__(16) __half2 h[4];
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            const float2 v = unpack_f32x2(y2[(i >> 1) + k]);
+            const float2 v = SCALAR_FOLD ? make_float2(yf[i + 2 * k], yf[i + 2 * k + 1]) : unpack_f32x2(y2[(i >> 1) + k]);
             h[k] = __floats2half2_rn(v.x * sxs[c0 + i + 2 * k], v.y * sxs[c0 + i + 2 * k + 1]);
           }
           *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<uint4*>(h);
@@ -790,7 +812,7 @@ prefill_gemm_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_const
           const int tok = tok0 + c0 + i;
           if (tok < p.T)
             p.Y[(size_t)row * p.y_stride_n + (size_t)tok * p.y_stride_t] =
-                __float2half_rn(((i & 1) ? unpack_f32x2(y2[i >> 1]).y : unpack_f32x2(y2[i >> 1]).x) * sxs[c0 + i]);
+                __float2half_rn((SCALAR_FOLD ? yf[i] : (i & 1) ? unpack_f32x2(y2[i >> 1]).y : unpack_f32x2(y2[i >> 1]).x) * sxs[c0 + i]);
         }
       }
     }

@@ -290,8 +290,15 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
     // ------------------------------------------------------------ consumers
     const int gid = lane >> 2;
     const int tig = lane & 3;
-    const int r_a = warp * 16 + gid;      // local rows of this thread's fragments
+    // Local rows of this thread's fragments.  Which weight row feeds MMA row `gid` is free (the epilogue
+    // writes row r_a), so the two rows a quarter-warp reads together are chosen to differ in bit 0 and in
+    // bit 2: a dense tile (128-byte rows, 16-byte chunks stored at chunk ^ (row & 7) by the tensor map's
+    // 128-byte swizzle) and a residual block (64-byte rows, unswizzled) are then both read without bank
+    // conflicts - rows 0,5 | 1,4 | 2,7 | 3,6.
+    const int r_a = warp * 16 + ((0x63724150u >> (4 * gid)) & 7);
     const int r_b = r_a + 8;
+    const int w_off0 = r_a * (2 * GROUP_BYTES) + ((tig ^ (r_a & 7)) << 4);          // group 2j of a dense step
+    const int w_off1 = r_a * (2 * GROUP_BYTES) + (((4 + tig) ^ (r_a & 7)) << 4);    // group 2j + 1
 
     // Per-thread constant offsets inside a slot.  An activation tile is a stack of
     // 128-byte lines (one per token) whose 16-byte chunks sit at chunk ^ (token & 7);
@@ -409,8 +416,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (consumed / STAGES) & 1, SITE_DEC_FULL));
           if (!ok) continue;
           const uint32_t slot = stage_a + st * STAGE_BYTES;
-          const uint32_t wrow_a = slot + r_a * (2 * GROUP_BYTES) + tig * 16;
-          const uint32_t wrow_b = slot + r_b * (2 * GROUP_BYTES) + tig * 16;
+          const uint32_t wrow[2] = {slot + w_off0, slot + w_off1};     // row b: eight rows (1 KB) further on
           const uint32_t sums = sumx_a + st * 2 * SUMX_BYTES;
           // the wide instantiation (four MMA tiles per pass) reads a group's weight fragments when it gets to
           // the group: both groups' fragments at once do not fit its register budget
@@ -418,8 +424,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           uint4 wa[2], wb[2];
 #pragma unroll
           for (int h = 0; h < (LATE_W ? 1 : 2); ++h) {
-            wa[h] = lds_v4(wrow_a + h * GROUP_BYTES);
-            wb[h] = lds_v4(wrow_b + h * GROUP_BYTES);
+            wa[h] = lds_v4(wrow[h]);
+            wb[h] = lds_v4(wrow[h] + 8 * 2 * GROUP_BYTES);
           }
           const float2 sza0 = lds_f2(szs_a + ((g & (SZ_CHUNK - 1)) * ROWS + r_a) * 8);
           const float2 szb0 = lds_f2(szs_a + ((g & (SZ_CHUNK - 1)) * ROWS + r_b) * 8);
@@ -429,8 +435,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
 #pragma unroll
           for (int gg = 0; gg < 2; ++gg) {
             if (LATE_W && gg == 1) {
-              wa[0] = lds_v4(wrow_a + GROUP_BYTES);
-              wb[0] = lds_v4(wrow_b + GROUP_BYTES);
+              wa[0] = lds_v4(wrow[1]);
+              wb[0] = lds_v4(wrow[1] + 8 * 2 * GROUP_BYTES);
             }
             const AFrag fa = LATE_W ? unpack_a(wa[0], wb[0]) : unpack_a(wa[gg], wb[gg]);
             const float2 sza = gg ? sza1 : sza0, szb = gg ? szb1 : szb0;

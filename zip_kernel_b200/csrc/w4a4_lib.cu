@@ -347,10 +347,11 @@ int launch_decode(const GemmArgs& a, DeviceInfo* dev) {
   if (!aligned(XE, 16)) return fail(W4A4_ERR_ALIGNMENT, "expanded activations must be 16-byte aligned");
 
   CUtensorMap tm_low;
-  // dense weights: 128 rows x two groups (128 bytes) per copy; unused (but valid) when the dense part is off
+  // dense weights: 128 rows x two groups (128 bytes) per copy, 16-byte chunks of a row stored at chunk ^ (row & 7);
+  // unused (but valid) when the dense part is off
   int rc = make_map(&tm_low, a.do_dense ? a.W_low : a.W_high, a.do_dense ? (uint64_t)a.K / 2 : 64,
                     a.do_dense ? (uint64_t)a.N : (uint64_t)a.nnz * BROW, a.do_dense ? 2 * GROUP_BYTES : GROUP_BYTES,
-                    dec::ROWS, CU_TENSOR_MAP_SWIZZLE_NONE);
+                    dec::ROWS, a.do_dense ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
 
   dec::Params p;

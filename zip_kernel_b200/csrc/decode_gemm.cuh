@@ -297,8 +297,8 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
     // conflicts - rows 0,5 | 1,4 | 2,7 | 3,6.
     const int r_a = warp * 16 + ((0x63724150u >> (4 * gid)) & 7);
     const int r_b = r_a + 8;
-    const int w_off0 = r_a * (2 * GROUP_BYTES) + ((tig ^ (r_a & 7)) << 4);          // group 2j of a dense step
-    const int w_off1 = r_a * (2 * GROUP_BYTES) + (((4 + tig) ^ (r_a & 7)) << 4);    // group 2j + 1
+    // group 2j of a dense step; group 2j + 1 sits at chunk (4 + tig) ^ (r_a & 7): the same address with bit 6 flipped
+    const int w_off = r_a * (2 * GROUP_BYTES) + ((tig ^ (r_a & 7)) << 4);
 
     // Per-thread constant offsets inside a slot.  An activation tile is a stack of
     // 128-byte lines (one per token) whose 16-byte chunks sit at chunk ^ (token & 7);
@@ -416,7 +416,7 @@ decode_gemm_kernel(const __grid_constant__ CUtensorMap tm_low, const Params p) {
           if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&full[st], (consumed / STAGES) & 1, SITE_DEC_FULL));
           if (!ok) continue;
           const uint32_t slot = stage_a + st * STAGE_BYTES;
-          const uint32_t wrow[2] = {slot + w_off0, slot + w_off1};     // row b: eight rows (1 KB) further on
+          const uint32_t wrow[2] = {slot + w_off, (slot + w_off) ^ GROUP_BYTES};     // row b: eight rows (1 KB) further on
           const uint32_t sums = sumx_a + st * 2 * SUMX_BYTES;
           // the wide instantiation (four MMA tiles per pass) reads a group's weight fragments when it gets to
           // the group: both groups' fragments at once do not fit its register budget

@@ -283,7 +283,22 @@ def test_host_staged_batch_graph(ops):
         torch.cuda.synchronize()
         for Xh, Wc, Yh in reqs:
             assert torch.equal(Yh, v9_linear.v9_linear_forward(Xh.cuda(), Wc).cpu())
+    # the same batch as an object a serving loop holds: same cached graph, usable after the cache is cleared
+    assert isinstance(backend.v9_linear_host_batch_graph(reqs, n_streams=3), backend.HostBatchGraph)   # the cached one
+    batch = backend.v9_linear_host_batch_graph(reqs)                     # default: a branch per request (up to 12)
+    assert batch.n_requests == len(reqs) and backend.v9_linear_host_batch_graph(reqs) is batch
     backend.clear_cuda_graph_cache()
+    for Xh, _, Yh in reqs:
+        Xh.mul_(3.0)
+        Yh.zero_()
+    batch.replay()
+    torch.cuda.synchronize()
+    for Xh, Wc, Yh in reqs:
+        assert torch.equal(Yh, v9_linear.v9_linear_forward(Xh.cuda(), Wc).cpu())
+    with pytest.raises(ValueError):                       # pageable buffers are refused when a batch is captured
+        backend.v9_linear_host_batch_graph([(reqs[0][0].clone(), reqs[0][1], reqs[0][2])])
+    with pytest.raises(ValueError):
+        backend.v9_linear_host_batch_graph([])
 
 
 def test_quant_every_fp16_value_against_many_scales(ops):

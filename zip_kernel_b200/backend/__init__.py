@@ -11,7 +11,7 @@ from .weight_loader import (CutlassPackValidationError, CutlassV9Tensors,
 from .graph_cache import (clear_cuda_graph_cache, cuda_graph_cache_stats, get_cuda_graph_policy,
                           prewarm_cuda_graph_cache, set_cuda_graph_policy,
                           v9_linear_forward_cuda_graph, v9_linear_forward_host_graph,
-                          v9_linear_forward_host_graph_many)
+                          v9_linear_forward_host_graph_many, v9_linear_host_batch_graph, HostBatchGraph)
 from .policy import get_backend_status, set_backend_policy
 from .registry import BackendKernel
 
@@ -48,6 +48,8 @@ __all__ = [
     "v9_linear_forward_cuda_graph",
     "v9_linear_forward_host_graph",
     "v9_linear_forward_host_graph_many",
+    "v9_linear_host_batch_graph",
+    "HostBatchGraph",
     "set_cuda_graph_policy",
     "get_cuda_graph_policy",
     "prewarm_cuda_graph_cache",

@@ -117,8 +117,25 @@ def ptr(t) -> int:
     return None if t is None else t.data_ptr()
 
 
+_raw_current_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_NO_SWITCH = contextlib.nullcontext()
+
+
 def stream_ptr(device) -> int:
+    """Handle of the current stream of ``device`` (the capture stream during a graph capture)."""
+    if _raw_current_stream is not None:
+        idx = getattr(device, "index", device)
+        return _raw_current_stream(torch.cuda.current_device() if idx is None else idx)
     return torch.cuda.current_stream(device).cuda_stream
+
+
+def on_device(device):
+    """Context that makes ``device`` current; free when it already is (a torch.cuda.device block costs
+    several microseconds per eager call otherwise)."""
+    idx = device.index
+    if idx is None or idx == torch.cuda.current_device():
+        return _NO_SWITCH
+    return torch.cuda.device(device)
 
 
 # ---------------------------------------------------------------------------

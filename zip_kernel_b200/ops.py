@@ -21,6 +21,14 @@ from . import _lib
 from .nvtx_shim import traced
 from .pack_utils import BCOL, BROW
 
+
+def _cd(t: torch.Tensor, dtype) -> torch.Tensor:
+    """``t`` as a contiguous tensor of ``dtype``; the tensor itself when it already is one (the usual
+    case: a no-op ``.to`` still costs most of a microsecond per argument and call)."""
+    if t.dtype is not dtype:
+        t = t.to(dtype)
+    return t if t.is_contiguous() else t.contiguous()
+
 _L = _lib.load()
 
 
@@ -59,14 +67,14 @@ def activation_quant_cuda(
     X_2d = X_fp16.reshape(T, D)
     if X_2d.stride(-1) != 1 or (T > 1 and X_2d.stride(0) < D):
         X_2d = X_2d.contiguous()          # row-strided inputs (a column slice of a wider tensor) go to the kernel as they are
-    perm_i32 = perm.to(device=X_2d.device, dtype=torch.int32).contiguous()
+    perm_i32 = _cd(perm if perm.device == X_2d.device else perm.to(X_2d.device), torch.int32)
     dev = X_2d.device
     X_s4 = torch.empty((T, D // 2), dtype=torch.int8, device=dev)
     scale_x = torch.empty((T,), dtype=torch.float16, device=dev)
     sum_X = torch.empty((T, D // bcol), dtype=torch.int32, device=dev)
     if T == 0:
         return X_s4, scale_x, sum_X
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         _lib.check(_L.w4a4_activation_quant(
             X_2d.data_ptr(), X_2d.stride(0) if T > 1 else D, perm_i32.data_ptr(), X_s4.data_ptr(),
             scale_x.data_ptr(), sum_X.data_ptr(), int(T), int(D), _lib.stream_ptr(dev),
@@ -87,7 +95,7 @@ def perm_or_none(perm: torch.Tensor, cache_on=None):
         tag, val = cache_on._perm_arg
         if tag == perm.data_ptr():
             return val
-    p32 = perm.to(torch.int32).contiguous()
+    p32 = _cd(perm, torch.int32)
     ident = bool(torch.equal(p32, torch.arange(p32.numel(), dtype=torch.int32, device=p32.device)))
     val = None if ident else p32
     if cache_on is not None:
@@ -126,7 +134,7 @@ def _fused_prologue(which: str, X2: torch.Tensor, K: int, perm, norm_weight, eps
     if T == 0:
         return ret
     pp = None if perm is None else perm.data_ptr()
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         if which == "rmsnorm":
             w = norm_weight.to(device=dev, dtype=torch.float16).contiguous()
             _lib.check(_L.w4a4_rmsnorm_quant(X2.data_ptr(), X2.stride(0) if T > 1 else K, w.data_ptr(), float(eps), pp, *outs,
@@ -187,8 +195,8 @@ def _prep_dense(W_low_packed, X_s4, scale_u4, zero_u4, sum_X, scale_x):
     assert sum_X.shape == (T, ng)
     assert scale_x.shape == (T,)
     return (W_low_packed.contiguous(), X_s4.contiguous(),
-            scale_u4.contiguous().to(torch.float16), zero_u4.contiguous().to(torch.float16),
-            sum_X.contiguous().to(torch.int32), scale_x.contiguous().to(torch.float16),
+            _cd(scale_u4, torch.float16), _cd(zero_u4, torch.float16),
+            _cd(sum_X, torch.int32), _cd(scale_x, torch.float16),
             int(T), int(d_in), int(d_out))
 
 
@@ -216,7 +224,7 @@ def dense_gemm_cuda_int4(W_low_packed, X_s4, scale_u4, zero_u4, sum_X, scale_x,
     Y = _out(N, T, W.device, token_major)
     if T == 0:
         return Y
-    with torch.cuda.device(W.device):
+    with _lib.on_device(W.device):
         ws = _lib.workspace(W.device, T, K, N, 0)
         _lib.check(_L.w4a4_dense_gemm(
             W.data_ptr(), X.data_ptr(), s.data_ptr(), z.data_ptr(), sm.data_ptr(), sx.data_ptr(),
@@ -251,14 +259,14 @@ def sparse_gemm_cuda_int4(W_high_blocks_packed, hp_row_offsets, hp_col_indices,
     if nnz == 0 or T == 0:
         return torch.zeros((T, d_out) if token_major else (d_out, T), dtype=torch.float16, device=dev)
     Wh = W_high_blocks_packed.contiguous()
-    ro = hp_row_offsets.contiguous().to(torch.int32)
-    ci = hp_col_indices.contiguous().to(torch.int32)
+    ro = _cd(hp_row_offsets, torch.int32)
+    ci = _cd(hp_col_indices, torch.int32)
     X = X_s4.contiguous()
-    s = scale_u4.contiguous().to(torch.float16)
-    sx = scale_x.contiguous().to(torch.float16)
+    s = _cd(scale_u4, torch.float16)
+    sx = _cd(scale_x, torch.float16)
     _check_bsr(ro, ci, d_out, d_in, nnz)
     Y = _out(d_out, T, dev, token_major)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         ws = _lib.workspace(dev, T, d_in, d_out, nnz)
         _lib.check(_L.w4a4_sparse_gemm(
             Wh.data_ptr(), ro.data_ptr(), ci.data_ptr(), X.data_ptr(), s.data_ptr(), sx.data_ptr(),
@@ -302,12 +310,12 @@ def _prep_fused(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col_indic
     if W_high_blocks_packed.numel() == 0:
         W_high_blocks_packed = torch.zeros((0, BROW, BCOL // 2), dtype=torch.int8,
                                            device=W_low_packed.device)
-    ro = hp_row_offsets.contiguous().to(torch.int32)
-    ci = hp_col_indices.contiguous().to(torch.int32)
+    ro = _cd(hp_row_offsets, torch.int32)
+    ci = _cd(hp_col_indices, torch.int32)
     _check_bsr(ro, ci, d_out, d_in, int(W_high_blocks_packed.shape[0]))
     return (W_low_packed.contiguous(), W_high_blocks_packed.contiguous(), ro, ci, X_s4.contiguous(),
-            scale_u4.contiguous().to(torch.float16), zero_u4.contiguous().to(torch.float16),
-            sum_X.contiguous().to(torch.int32), scale_x.contiguous().to(torch.float16), T, d_in, d_out)
+            _cd(scale_u4, torch.float16), _cd(zero_u4, torch.float16),
+            _cd(sum_X, torch.int32), _cd(scale_x, torch.float16), T, d_in, d_out)
 
 
 def prepare_weights_cuda(packed: torch.Tensor) -> torch.Tensor:
@@ -319,7 +327,7 @@ def prepare_weights_cuda(packed: torch.Tensor) -> torch.Tensor:
     src = packed.contiguous()
     out = torch.empty(src.shape[:-1] + (src.shape[-1] * 2,), dtype=torch.uint8, device=src.device)
     if src.numel():
-        with torch.cuda.device(src.device):
+        with _lib.on_device(src.device):
             _lib.check(_L.w4a4_prepare_weights(src.data_ptr(), out.data_ptr(), src.numel(),
                                                _lib.stream_ptr(src.device)), "prepare_weights")
     return out
@@ -331,11 +339,11 @@ def dequant_u4_to_fp16_cuda(W_low_packed: torch.Tensor, scale_u4: torch.Tensor, 
     assert W_low_packed.is_cuda and W_low_packed.dtype == torch.int8 and W_low_packed.dim() == 2
     W = W_low_packed.contiguous()
     N, K = int(W.shape[0]), int(W.shape[1]) * 2
-    s = scale_u4.contiguous().to(torch.float16)
-    z = zero_u4.contiguous().to(torch.float16)
+    s = _cd(scale_u4, torch.float16)
+    z = _cd(zero_u4, torch.float16)
     assert s.shape == (N, K // BCOL) and z.shape == (N, K // BCOL)
     out = torch.empty((N, K), dtype=torch.float16, device=W.device)
-    with torch.cuda.device(W.device):
+    with _lib.on_device(W.device):
         _lib.check(_L.w4a4_dequant_weights_fp16(W.data_ptr(), s.data_ptr(), z.data_ptr(), out.data_ptr(), N, K,
                                                 _lib.stream_ptr(W.device)), "dequant_weights")
     return out
@@ -367,7 +375,7 @@ def fused_dense_sparse_cuda_int4(
     if T == 0:
         return Y
     nnz = int(Wh.shape[0])
-    with torch.cuda.device(W.device):
+    with _lib.on_device(W.device):
         ws = _lib.workspace(W.device, T, K, N, nnz)
         plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
         _lib.check(_L.w4a4_fused_dense_sparse_prepared(
@@ -392,7 +400,7 @@ def expand_activations_cuda(X_s4: torch.Tensor, sum_X: torch.Tensor, *, e4m3=Fal
     sm = sum_X.contiguous()
     XE = torch.empty((int(_L.w4a4_expanded_codes_bytes(T, K)),), dtype=torch.int8, device=X.device)
     sumxf = torch.zeros(((T + 15) // 16, K // BCOL, 16), dtype=torch.float32, device=X.device)
-    with torch.cuda.device(X.device):
+    with _lib.on_device(X.device):
         _lib.check(_L.w4a4_expand_activations_fmt(X.data_ptr(), sm.data_ptr(), XE.data_ptr(), sumxf.data_ptr(),
                                                   T, K, _code_format(e4m3), _lib.stream_ptr(X.device)),
                    "expand_activations")
@@ -417,14 +425,14 @@ def fused_dense_sparse_expanded_cuda(
     W = W_low_packed.contiguous()
     nnz = int(W_high_blocks_packed.shape[0]) if W_high_blocks_packed.numel() else 0
     Wh = W_high_blocks_packed.contiguous()
-    ro = hp_row_offsets.contiguous().to(torch.int32)
-    ci = hp_col_indices.contiguous().to(torch.int32)
+    ro = _cd(hp_row_offsets, torch.int32)
+    ci = _cd(hp_col_indices, torch.int32)
     _check_bsr(ro, ci, d_out, d_in, nnz)
-    s = scale_u4.contiguous().to(torch.float16)
-    z = zero_u4.contiguous().to(torch.float16)
-    sx = scale_x.contiguous().to(torch.float16)
+    s = _cd(scale_u4, torch.float16)
+    z = _cd(zero_u4, torch.float16)
+    sx = _cd(scale_x, torch.float16)
     Y = _out(d_out, T, W.device, token_major)
-    with torch.cuda.device(W.device):
+    with _lib.on_device(W.device):
         ws = _lib.workspace(W.device, T, d_in, d_out, nnz)
         plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
         _lib.check(_L.w4a4_fused_dense_sparse_expanded_prepared(
@@ -463,22 +471,24 @@ def fused_dense_sparse_e2e_cuda(
     d_out, d_in = int(d_out), int(d_in)
     if X_fp16.shape[-1] != d_in:
         raise ValueError(f"X last dim ({X_fp16.shape[-1]}) must match d_in ({d_in})")
-    X2 = X_fp16.reshape(-1, d_in).contiguous()
+    X2 = X_fp16 if X_fp16.dim() == 2 else X_fp16.reshape(-1, d_in)
+    if not X2.is_contiguous():
+        X2 = X2.contiguous()
     T = int(X2.shape[0])
     dev = W_low_packed.device
     W = W_low_packed.contiguous()
     Wh = W_high_blocks_packed.contiguous()
     nnz = int(Wh.shape[0]) if Wh.numel() else 0
-    ro = hp_row_offsets.contiguous().to(torch.int32)
-    ci = hp_col_indices.contiguous().to(torch.int32)
+    ro = _cd(hp_row_offsets, torch.int32)
+    ci = _cd(hp_col_indices, torch.int32)
     _check_bsr(ro, ci, d_out, d_in, nnz)
-    s = scale_u4.contiguous().to(torch.float16)
-    z = zero_u4.contiguous().to(torch.float16)
-    perm_i32 = perm.to(device=dev, dtype=torch.int32).contiguous()
+    s = _cd(scale_u4, torch.float16)
+    z = _cd(zero_u4, torch.float16)
+    perm_i32 = _cd(perm if perm.device == dev else perm.to(dev), torch.int32)
     Y = _out(d_out, T, dev, token_major)
     if T == 0:
         return Y
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         ws = _lib.workspace(dev, T, d_in, d_out, nnz)
         plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
         _lib.check(_L.w4a4_fused_quant_dense_sparse_prepared(
@@ -535,9 +545,9 @@ def dump_accumulators(W_low_packed, W_high_blocks_packed, hp_row_offsets, hp_col
     X = X_s4.contiguous()
     # converted copies stay referenced until the call has been issued
     Wh = W_high_blocks_packed.contiguous() if nnz else None
-    ro = hp_row_offsets.contiguous().to(torch.int32) if nnz else None
-    ci = hp_col_indices.contiguous().to(torch.int32) if nnz else None
-    with torch.cuda.device(dev):
+    ro = _cd(hp_row_offsets, torch.int32) if nnz else None
+    ci = _cd(hp_col_indices, torch.int32) if nnz else None
+    with _lib.on_device(dev):
         ws = _lib.workspace(dev, T, d_in, d_out, nnz)
         plo, phi = _prepared_ptrs(prepared, W, Wh, nnz)
         _lib.check(_L.w4a4_dump_accumulators_prepared(

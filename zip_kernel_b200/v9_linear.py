@@ -59,7 +59,7 @@ def _forward(X_fp16: torch.Tensor, W: V9WeightContainer, force=None) -> torch.Te
     d_in, d_out = W.d_in, W.d_out
     if X_fp16.shape[-1] != d_in:
         raise ValueError(f"X last dim ({X_fp16.shape[-1]}) must match d_in ({d_in})")
-    X_2d = X_fp16.reshape(-1, d_in)
+    X_2d = X_fp16 if X_fp16.dim() == 2 else X_fp16.reshape(-1, d_in)
     if _w4a16_policy == "auto" and force is None and w4a16_eligible(W, int(X_2d.shape[0])):
         perm = ops.perm_or_none(W.perm, W)
         Xp = X_2d if perm is None else X_2d.index_select(1, perm.to(torch.long))
@@ -68,7 +68,7 @@ def _forward(X_fp16: torch.Tensor, W: V9WeightContainer, force=None) -> torch.Te
         X_2d, W.perm, W.W_low_packed, W.W_high_blocks_packed, W.hp_row_offsets,
         W.hp_col_indices, W.scale_u4, W.zero_u4, d_out, d_in, token_major=True, force=force,
         prepared=W.prepared)
-    return Y.reshape(X_fp16.shape[:-1] + (d_out,))
+    return Y if X_fp16.dim() == 2 else Y.reshape(X_fp16.shape[:-1] + (d_out,))
 
 
 def _gemm_on_expanded(quantised, W: V9WeightContainer, lead_shape, e4m3) -> torch.Tensor:
